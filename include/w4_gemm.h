@@ -1,0 +1,158 @@
+/*
+ * C ABI of the B200 weight-only quantised GEMM (W4A16 / W8A16).
+ *
+ * Every entry point is plain C: pointers, sizes, ints. Nothing here allocates device memory,
+ * keeps a caller's pointer after the call returns, synchronises the stream or throws; every
+ * function that can fail returns a W4Status (0 = success, negative = error) and
+ * w4_status_string() names it.
+ *
+ * What each entry point stands in for in TensorRT-LLM (paths inside that project):
+ *   w4_gemm_launch           - weight_only::kernel_launcher(arch, Params&, stream)
+ *                              (cpp/tensorrt_llm/kernels/weightOnlyBatchedGemv/kernelLauncher.h:31)
+ *                              and CutlassFpAIntBGemmRunnerInterface::gemm(...)
+ *                              (cpp/tensorrt_llm/kernels/cutlass_kernels/fpA_intB_gemm/fpA_intB_gemm.h:62-79),
+ *                              i.e. the body of WeightOnlyQuantMatmulPlugin::enqueue
+ *                              (cpp/tensorrt_llm/plugins/weightOnlyQuantMatmulPlugin/weightOnlyQuantMatmulPlugin.cpp:283-339)
+ *                              and WeightOnlyGroupwiseQuantMatmulPlugin::enqueue
+ *                              (cpp/tensorrt_llm/plugins/weightOnlyGroupwiseQuantMatmulPlugin/weightOnlyGroupwiseQuantMatmulPlugin.cpp:407-495).
+ *   W4GemmParams             - weight_only::Params
+ *                              (cpp/tensorrt_llm/kernels/weightOnlyBatchedGemv/common.h:64-102).
+ *   w4_gemm_workspace_bytes  - CutlassFpAIntBGemmRunner::getWorkspaceSize (fpA_intB_gemm_template.h:577-581)
+ *                              plus the smoothed-activation buffer the groupwise plugin adds
+ *                              (weightOnlyGroupwiseQuantMatmulPlugin.cpp:377-379).
+ *   w4_gemm_select_regime    - GemmPluginProfiler::getBestConfig, the reference's per-M choice
+ *                              between its CUDA-core GEMV and a CUTLASS tactic
+ *                              (cpp/tensorrt_llm/plugins/common/gemmPluginProfiler.cpp:221-250).
+ *   w4_symmetric_quantize    - symmetric_quantize<ComputeType, WeightType>
+ *                              (cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:652-762).
+ *   w4_preprocess_weights    - preprocess_weights_for_mixed_gemm (cutlass_preprocessors.cpp:564-615).
+ *   w4_pack_int4 / w4_unpack_int4
+ *                            - pack_int8_tensor_to_packed_int4 / unpack_int4_packed_tensor_to_int8
+ *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:284-353).
+ */
+#ifndef W4_GEMM_H
+#define W4_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C"
+{
+#endif
+
+    typedef enum W4Status
+    {
+        W4_OK = 0,
+        W4_ERR_NULL_POINTER = -1,   /* a mandatory pointer is null */
+        W4_ERR_BAD_SHAPE = -2,      /* m/n/k violate the layout's divisibility rules */
+        W4_ERR_BAD_GROUP = -3,      /* group_size not in {0, 64, 128} or does not divide k */
+        W4_ERR_BAD_DTYPE = -4,      /* act_dtype / weight_bits not supported */
+        W4_ERR_MISALIGNED = -5,     /* a pointer misses the alignment the kernels need */
+        W4_ERR_UNSUPPORTED = -6,    /* valid in the reference, not built here (e.g. W4A8 FP8 alpha) */
+        W4_ERR_WORKSPACE = -7,      /* workspace missing or smaller than w4_gemm_workspace_bytes() */
+        W4_ERR_CUDA = -8,           /* a CUDA runtime call failed; see cudaGetLastError() */
+        W4_ERR_BAD_REGIME = -9,     /* regime not valid for this shape */
+        W4_ERR_DEVICE_TIMEOUT = -10 /* a bounded device-side wait expired (reported by w4_gemm_device_status) */
+    } W4Status;
+
+    /* Activation / scale / output element type (one type for all of them, as in the plugins). */
+    enum
+    {
+        W4_DTYPE_FP16 = 0,
+        W4_DTYPE_BF16 = 1
+    };
+
+    /* Which kernel family runs. AUTO applies w4_gemm_select_regime(). */
+    enum
+    {
+        W4_REGIME_AUTO = 0,
+        W4_REGIME_GEMV = 1, /* streaming decode kernel, any m (re-streams the weights every 16 rows) */
+        W4_REGIME_GEMM = 2  /* tcgen05 tensor-core kernel */
+    };
+
+    /* quant_algo bits of the groupwise plugin (weightOnlyGroupwiseQuantMatmulPlugin.cpp:33-37). */
+    enum
+    {
+        W4_ALGO_BIAS = 1,
+        W4_ALGO_ZERO = 2,
+        W4_ALGO_PRE_QUANT_SCALE = 4,
+        W4_ALGO_FP8_ALPHA = 8,
+        W4_ALGO_INT8_WEIGHT = 16
+    };
+
+    /*
+     * out[m, n] = alpha * sum_k (act[m, k] * act_scale[k]) * (q[k, n] * scales[g(k), n] + zeros[g(k), n]) + bias[n]
+     *
+     *   act        [m, k] row-major, fp16 or bf16 (act_dtype)            device, mandatory
+     *   act_scale  [k] same type, AWQ pre-quant scale                     device, optional (NULL = ones)
+     *   weight     the bytes produced by w4_preprocess_weights / w4_symmetric_quantize
+     *              ([k, n*weight_bits/8] int8)                             device, mandatory
+     *   scales     [k/group_size, n] (group_size 64/128) or [n] (group_size 0), same type as act
+     *   zeros      same shape as scales, already multiplied by the scale as the reference expects
+     *              (tensorrt_llm/quantization/functional.py:1010-1014)    device, optional
+     *   bias       [n]                                                    device, optional
+     *   out        [m, n] row-major, same type as act                     device, mandatory
+     *   n          the real number of output features (not the packed extent)
+     *   workspace  scratch of at least w4_gemm_workspace_bytes(); may be NULL when that is 0
+     */
+    typedef struct W4GemmParams
+    {
+        const void* act;
+        const void* act_scale;
+        const void* weight;
+        const void* scales;
+        const void* zeros;
+        const void* bias;
+        void* out;
+        float alpha;
+        int m;
+        int n;
+        int k;
+        int group_size;  /* 0 (per output column), 64 or 128 */
+        int weight_bits; /* 4 or 8 */
+        int act_dtype;   /* W4_DTYPE_* */
+        int regime;      /* W4_REGIME_* */
+        void* workspace;
+        size_t workspace_bytes;
+    } W4GemmParams;
+
+    int w4_gemm_version(void);
+    const char* w4_status_string(int status);
+
+    /* Validates p without touching the device; the same checks w4_gemm_launch runs first. */
+    int w4_gemm_validate(const W4GemmParams* p);
+
+    /* Enqueues the GEMM on `stream` (a cudaStream_t; NULL = default stream). m == 0 is a no-op. */
+    int w4_gemm_launch(const W4GemmParams* p, void* stream);
+
+    /* Bytes of scratch w4_gemm_launch needs for this problem in the regime it would pick. */
+    size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
+        int has_act_scale, int regime);
+
+    /* W4_REGIME_GEMV or W4_REGIME_GEMM for this shape. */
+    int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits);
+
+    /* Reads and clears the device-side status word of the current device (synchronises the
+     * device). 0, or W4_ERR_DEVICE_TIMEOUT when a kernel gave up a bounded wait. */
+    int w4_gemm_device_status(void);
+
+    /* ---- host-side (CPU) weight preparation, bit-exact with the reference ---- */
+
+    /* weight: fp32 [k, n] row-major. processed / unprocessed: [k, n*bits/8] bytes (unprocessed may
+     * be NULL). scales: fp32 [n], the unrounded per-column scale amax * 2^-(bits-1); round it to
+     * fp16 / bf16 (nearest even) for the device. */
+    int w4_symmetric_quantize(int8_t* processed, int8_t* unprocessed, float* scales, const float* weight, size_t k,
+        size_t n, int bits);
+
+    /* in: [k, n*bits/8] row-major two's-complement weights (int4: even column in the low nibble). */
+    int w4_preprocess_weights(int8_t* out, const int8_t* in, size_t k, size_t n, int bits);
+
+    int w4_pack_int4(int8_t* packed, const int8_t* unpacked, size_t num_packed_bytes);
+    void w4_unpack_int4(int8_t* unpacked, const int8_t* packed, size_t num_packed_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* W4_GEMM_H */

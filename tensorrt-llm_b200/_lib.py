@@ -1,0 +1,79 @@
+"""ctypes binding of libw4gemm.so (the C ABI in include/w4_gemm.h).
+
+The library is built in-tree by csrc/build.sh. There is no CPU or PyTorch fallback: if the shared
+object is missing the import of any GPU entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libw4gemm.so")
+
+W4_OK = 0
+W4_DTYPE_FP16, W4_DTYPE_BF16 = 0, 1
+W4_REGIME_AUTO, W4_REGIME_GEMV, W4_REGIME_GEMM = 0, 1, 2
+# quant_algo bits of the groupwise plugin
+BIAS, ZERO, PRE_QUANT_SCALE, FP8_ALPHA, INT8_WEIGHT = 1, 2, 4, 8, 16
+
+EXPORTS = (
+    "w4_gemm_version", "w4_status_string", "w4_gemm_validate", "w4_gemm_launch", "w4_gemm_workspace_bytes",
+    "w4_gemm_select_regime", "w4_gemm_device_status", "w4_symmetric_quantize", "w4_preprocess_weights",
+    "w4_pack_int4", "w4_unpack_int4",
+)
+
+
+class W4GemmParams(ctypes.Structure):
+    _fields_ = [
+        ("act", ctypes.c_void_p), ("act_scale", ctypes.c_void_p), ("weight", ctypes.c_void_p),
+        ("scales", ctypes.c_void_p), ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("alpha", ctypes.c_float), ("m", ctypes.c_int), ("n", ctypes.c_int),
+        ("k", ctypes.c_int), ("group_size", ctypes.c_int), ("weight_bits", ctypes.c_int),
+        ("act_dtype", ctypes.c_int), ("regime", ctypes.c_int), ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+class W4Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: {status_string(status)} (status {status})")
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with tensorrt-llm_b200/csrc/build.sh "
+                "(there is no fallback path)")
+        l = ctypes.CDLL(LIB_PATH)
+        l.w4_status_string.restype = ctypes.c_char_p
+        l.w4_status_string.argtypes = [ctypes.c_int]
+        l.w4_gemm_validate.argtypes = [ctypes.POINTER(W4GemmParams)]
+        l.w4_gemm_launch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
+        l.w4_gemm_workspace_bytes.restype = ctypes.c_size_t
+        l.w4_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 8
+        l.w4_gemm_select_regime.argtypes = [ctypes.c_int] * 5
+        l.w4_symmetric_quantize.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                            ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]
+        l.w4_preprocess_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,
+                                            ctypes.c_int]
+        l.w4_pack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+        l.w4_unpack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+        l.w4_unpack_int4.restype = None
+        _lib = l
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().w4_status_string(int(status)).decode()
+
+
+def check(status: int, where: str):
+    if status != W4_OK:
+        raise W4Error(status, where)

@@ -1,0 +1,207 @@
+// The C ABI declared in include/w4_gemm.h: argument validation, the M-based regime choice and
+// dispatch into the two kernel families. Nothing here allocates or synchronises.
+#include <mutex>
+
+#include "w4_common.cuh"
+#include "w4_internal.h"
+
+namespace w4
+{
+
+DeviceInfo const& current_device_info()
+{
+    static DeviceInfo infos[64];
+    static std::mutex mu;
+    static DeviceInfo invalid;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return invalid;
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo& d = infos[dev];
+    if (d.device != dev)
+    {
+        int sms = 0, smem = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess
+            || cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+            return invalid;
+        d.num_sms = sms;
+        d.max_smem_optin = smem;
+        d.device = dev;
+    }
+    return d;
+}
+
+// ------------------------------------------------------------------------------------------------
+// act[m, k] * scale[k] -> out, rounded to the element type. Counterpart of the reference's
+// apply_per_channel_scale (cpp/tensorrt_llm/kernels/preQuantScaleKernel.cu:43-95); used in front
+// of the tensor-core kernel only (the decode kernel fuses the product into its activation load).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void pre_quant_scale_kernel(uint4* out, uint4 const* act, uint4 const* scale, size_t total_vec, int k_vec)
+{
+    using P = Pair<T>;
+    size_t const stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec; i += stride)
+    {
+        uint4 a = act[i];
+        uint4 const s = __ldg(scale + (i % k_vec));
+        a.x = P::mul(a.x, s.x);
+        a.y = P::mul(a.y, s.y);
+        a.z = P::mul(a.z, s.z);
+        a.w = P::mul(a.w, s.w);
+        out[i] = a;
+    }
+}
+
+int launch_pre_quant_scale(void* out, void const* act, void const* scale, int m, int k, int act_dtype,
+    cudaStream_t stream)
+{
+    DeviceInfo const& dev = current_device_info();
+    if (dev.num_sms <= 0)
+        return W4_ERR_CUDA;
+    size_t const total_vec = size_t(m) * k / 8;
+    int const threads = 256;
+    size_t blocks = (total_vec + threads - 1) / threads;
+    size_t const cap = size_t(dev.num_sms) * 8;
+    if (blocks > cap)
+        blocks = cap;
+    if (blocks == 0)
+        return W4_OK;
+    if (act_dtype == W4_DTYPE_FP16)
+        pre_quant_scale_kernel<__half><<<unsigned(blocks), threads, 0, stream>>>(static_cast<uint4*>(out),
+            static_cast<uint4 const*>(act), static_cast<uint4 const*>(scale), total_vec, k / 8);
+    else
+        pre_quant_scale_kernel<__nv_bfloat16><<<unsigned(blocks), threads, 0, stream>>>(static_cast<uint4*>(out),
+            static_cast<uint4 const*>(act), static_cast<uint4 const*>(scale), total_vec, k / 8);
+    return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
+}
+
+} // namespace w4
+
+namespace
+{
+
+bool aligned16(void const* p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+int resolve_regime(W4GemmParams const& p)
+{
+    if (p.regime == W4_REGIME_GEMV || p.regime == W4_REGIME_GEMM)
+        return p.regime;
+    return w4_gemm_select_regime(p.m, p.n, p.k, p.group_size, p.weight_bits);
+}
+
+} // namespace
+
+extern "C"
+{
+
+    int w4_gemm_version(void)
+    {
+        return 100;
+    }
+
+    const char* w4_status_string(int status)
+    {
+        switch (status)
+        {
+        case W4_OK: return "ok";
+        case W4_ERR_NULL_POINTER: return "a mandatory pointer is null";
+        case W4_ERR_BAD_SHAPE: return "unsupported shape (need k % 64 == 0 and n % 64 == 0 (int4) / n % 32 == 0 (int8))";
+        case W4_ERR_BAD_GROUP: return "group_size must be 0, 64 or 128 and divide k";
+        case W4_ERR_BAD_DTYPE: return "act_dtype must be fp16/bf16 and weight_bits 4 or 8";
+        case W4_ERR_MISALIGNED: return "pointers must be 16-byte aligned";
+        case W4_ERR_UNSUPPORTED: return "valid in the reference but not supported by this library";
+        case W4_ERR_WORKSPACE: return "workspace missing or too small";
+        case W4_ERR_CUDA: return "CUDA runtime error";
+        case W4_ERR_BAD_REGIME: return "regime not valid for this problem";
+        case W4_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        default: return "unknown status";
+        }
+    }
+
+    int w4_gemm_validate(const W4GemmParams* p)
+    {
+        if (!p)
+            return W4_ERR_NULL_POINTER;
+        if (p->act_dtype != W4_DTYPE_FP16 && p->act_dtype != W4_DTYPE_BF16)
+            return W4_ERR_BAD_DTYPE;
+        if (p->weight_bits != 4 && p->weight_bits != 8)
+            return W4_ERR_BAD_DTYPE;
+        if (p->m < 0 || p->n <= 0 || p->k <= 0)
+            return W4_ERR_BAD_SHAPE;
+        // k: whole 64-wide tiles (fpA_intB_gemm_template.h:191-196 of the reference); n: what the
+        // reference's own preprocessing accepts (cutlass_preprocessors.cpp:280-283).
+        if (p->k % 64 != 0 || (p->n * p->weight_bits / 8) % 32 != 0)
+            return W4_ERR_BAD_SHAPE;
+        if (p->group_size != 0 && p->group_size != 64 && p->group_size != 128)
+            return W4_ERR_BAD_GROUP;
+        if (p->group_size != 0 && p->k % p->group_size != 0)
+            return W4_ERR_BAD_GROUP;
+        if (p->regime != W4_REGIME_AUTO && p->regime != W4_REGIME_GEMV && p->regime != W4_REGIME_GEMM)
+            return W4_ERR_BAD_REGIME;
+        if (p->m == 0)
+            return W4_OK;
+        if (!p->act || !p->weight || !p->scales || !p->out)
+            return W4_ERR_NULL_POINTER;
+        if (!aligned16(p->act) || !aligned16(p->weight) || !aligned16(p->scales) || !aligned16(p->out)
+            || !aligned16(p->act_scale) || !aligned16(p->zeros) || !aligned16(p->bias) || !aligned16(p->workspace))
+            return W4_ERR_MISALIGNED;
+        size_t const need = w4_gemm_workspace_bytes(p->m, p->n, p->k, p->group_size, p->weight_bits, p->act_dtype,
+            p->act_scale != nullptr, p->regime);
+        if (need > 0 && (!p->workspace || p->workspace_bytes < need))
+            return W4_ERR_WORKSPACE;
+        return W4_OK;
+    }
+
+    int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits)
+    {
+        (void) n;
+        (void) k;
+        (void) group_size;
+        (void) weight_bits;
+        // The decode kernel re-streams the weights once per 16 rows; the tensor-core kernel pays
+        // for a 128-row tile however small m is. They cross between m = 32 and m = 64.
+        return m <= 32 ? W4_REGIME_GEMV : W4_REGIME_GEMM;
+    }
+
+    size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
+        int has_act_scale, int regime)
+    {
+        (void) act_dtype;
+        if (m <= 0)
+            return 0;
+        int r = regime;
+        if (r != W4_REGIME_GEMV && r != W4_REGIME_GEMM)
+            r = w4_gemm_select_regime(m, n, k, group_size, weight_bits);
+        if (r == W4_REGIME_GEMV)
+            return 0;
+        return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale);
+    }
+
+    int w4_gemm_launch(const W4GemmParams* p, void* stream)
+    {
+        int const rc = w4_gemm_validate(p);
+        if (rc != W4_OK)
+            return rc;
+        if (p->m == 0)
+            return W4_OK;
+        cudaStream_t const s = static_cast<cudaStream_t>(stream);
+        if (resolve_regime(*p) == W4_REGIME_GEMV)
+            return w4::launch_gemv(*p, s);
+        return w4::launch_gemm_tc(*p, s);
+    }
+
+    int w4_gemm_device_status(void)
+    {
+        int v = 0, zero = 0;
+        if (cudaMemcpyFromSymbol(&v, w4::g_device_status, sizeof(int)) != cudaSuccess)
+            return W4_ERR_CUDA;
+        if (v != 0 && cudaMemcpyToSymbol(w4::g_device_status, &zero, sizeof(int)) != cudaSuccess)
+            return W4_ERR_CUDA;
+        return v;
+    }
+
+} // extern "C"

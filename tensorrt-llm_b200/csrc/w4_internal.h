@@ -1,0 +1,35 @@
+// Internal interfaces between the C ABI (w4_api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/w4_gemm.h"
+
+namespace w4
+{
+
+struct DeviceInfo
+{
+    int device = -1;
+    int num_sms = 0;
+    int max_smem_optin = 0;
+};
+
+// Cached per-device properties of the current device (thread-safe, no allocation).
+DeviceInfo const& current_device_info();
+
+// Streaming decode kernel: handles any m by passes of at most 16 rows. Returns a W4Status.
+int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
+
+// tcgen05 tensor-core kernel. Returns a W4Status.
+int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream);
+size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale);
+
+// out[m, k] = act[m, k] * scale[k], rounded to the element type (the reference's
+// apply_per_channel_scale, cpp/tensorrt_llm/kernels/preQuantScaleKernel.cu:43-95).
+int launch_pre_quant_scale(void* out, void const* act, void const* scale, int m, int k, int act_dtype,
+    cudaStream_t stream);
+
+} // namespace w4

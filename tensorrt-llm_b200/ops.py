@@ -1,0 +1,281 @@
+"""GPU entry points of the weight-only GEMM, mirroring the reference's operator boundary.
+
+* ``weight_only_quant_matmul`` / ``weight_only_groupwise_quant_matmul``: functional form with the
+  argument order of the reference's graph emitters
+  (tensorrt_llm/quantization/functional.py:216-256 and :259-347 of TensorRT-LLM).
+* ``WeightOnlyQuantMatmulPlugin`` / ``WeightOnlyGroupwiseQuantMatmulPlugin``: the same fields,
+  tensor order, workspace contract and ``enqueue`` behaviour as the TensorRT plugins
+  (cpp/tensorrt_llm/plugins/weightOnlyQuantMatmulPlugin/weightOnlyQuantMatmulPlugin.cpp:283-339,
+  cpp/tensorrt_llm/plugins/weightOnlyGroupwiseQuantMatmulPlugin/weightOnlyGroupwiseQuantMatmulPlugin.cpp:189-201,407-495).
+
+Everything funnels into ``w4_gemm_launch`` of libw4gemm.so on the tensors' CUDA stream. torch is
+used for device memory and streams only; there is no torch/CPU compute fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import struct
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import (BIAS, FP8_ALPHA, INT8_WEIGHT, PRE_QUANT_SCALE, W4_DTYPE_BF16, W4_DTYPE_FP16, W4_REGIME_AUTO,
+                   W4_REGIME_GEMM, W4_REGIME_GEMV, ZERO, W4GemmParams)
+
+# nvinfer1::DataType values used by the plugins' type_id field
+TRT_HALF, TRT_BF16 = 1, 7
+# WeightTypeId of the per-channel plugin (weightOnlyQuantMatmulPlugin.h:38-42)
+WEIGHT_TYPE_INT8, WEIGHT_TYPE_INT4 = 1, 2
+
+_DTYPES = {torch.float16: W4_DTYPE_FP16, torch.bfloat16: W4_DTYPE_BF16}
+_TRT_TO_TORCH = {TRT_HALF: torch.float16, TRT_BF16: torch.bfloat16}
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _require_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def select_regime(m: int, n: int, k: int, group_size: int, weight_bits: int) -> int:
+    return _lib.lib().w4_gemm_select_regime(m, n, k, group_size, weight_bits)
+
+
+def workspace_bytes(m: int, n: int, k: int, group_size: int, weight_bits: int, dtype: torch.dtype,
+                    has_act_scale: bool, regime: int = W4_REGIME_AUTO) -> int:
+    return int(_lib.lib().w4_gemm_workspace_bytes(m, n, k, group_size, weight_bits, _DTYPES[dtype],
+                                                  int(has_act_scale), regime))
+
+
+def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, group_size: int, zeros=None,
+             bias=None, act_scale=None, alpha: float = 1.0, regime: int = W4_REGIME_AUTO, workspace=None,
+             stream: Optional[int] = None) -> None:
+    """Thin wrapper of w4_gemm_launch: borrows every pointer, allocates nothing, returns at once."""
+    m = act.numel() // k if k else 0
+    params = W4GemmParams(
+        act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros),
+        bias=_p(bias), out=_p(out), alpha=float(alpha), m=m, n=n, k=k, group_size=group_size,
+        weight_bits=weight_bits, act_dtype=_DTYPES[act.dtype], regime=regime, workspace=_p(workspace),
+        workspace_bytes=workspace.numel() * workspace.element_size() if workspace is not None else 0)
+    if stream is None:
+        stream = torch.cuda.current_stream(act.device).cuda_stream
+    with torch.cuda.device(act.device):
+        rc = _lib.lib().w4_gemm_launch(ctypes.byref(params), ctypes.c_void_p(stream))
+    _lib.check(rc, "w4_gemm_launch")
+
+
+def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime):
+    for name, t in (("act", act), ("weight", weight), ("scales", scales)):
+        _require_cuda(t, name)
+    if act.dtype not in _DTYPES:
+        raise RuntimeError("activations must be float16 or bfloat16")
+    for name, t in (("scales", scales), ("zeros", zeros), ("bias", bias), ("pre_quant_scale", act_scale)):
+        if t is not None:
+            _require_cuda(t, name)
+            if t.dtype != act.dtype:
+                raise RuntimeError(f"{name} must have the activation dtype")
+    k = act.shape[-1]
+    # weight bytes per row of the [K, N*bits/8] tensor, whatever dtype it is viewed as
+    row_bytes = weight.shape[-1] * weight.element_size()
+    if weight.dim() != 2 or weight.shape[0] != k:
+        raise RuntimeError("weight must be 2-D with K rows")
+    n = row_bytes * 8 // weight_bits
+    out = torch.empty(act.shape[:-1] + (n,), dtype=act.dtype, device=act.device)
+    m = act.numel() // k
+    if m == 0:
+        return out
+    ws_bytes = workspace_bytes(m, n, k, group_size, weight_bits, act.dtype, act_scale is not None, regime)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=act.device) if ws_bytes else None
+    gemm_raw(act, weight, scales, out, n=n, k=k, weight_bits=weight_bits, group_size=group_size, zeros=zeros,
+             bias=bias, act_scale=act_scale, alpha=alpha, regime=regime, workspace=ws)
+    return out
+
+
+def weight_only_quant_matmul(act: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor,
+                             weight_type_id: int, regime: int = W4_REGIME_AUTO) -> torch.Tensor:
+    """Per-channel W8A16 / W4A16: act [.., K] x weight int8 [K, N*bits/8] (preprocessed) with
+    scales [N]. weight_type_id: 1 = int8, 2 = int4."""
+    if weight_type_id not in (WEIGHT_TYPE_INT8, WEIGHT_TYPE_INT4):
+        raise RuntimeError(f"wTypeId={weight_type_id} is not supported")
+    bits = 8 if weight_type_id == WEIGHT_TYPE_INT8 else 4
+    return _run(act, weight, scales, None, None, None, 1.0, bits, 0, regime)
+
+
+def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zeros, bias, alpha: float,
+                                       quant_algo: int, group_size: int,
+                                       regime: int = W4_REGIME_AUTO) -> torch.Tensor:
+    """Groupwise W4A16 / W8A16 (GPTQ / AWQ). quant_algo bits: 1 bias, 2 zero, 4 pre-quant scale,
+    8 fp8 alpha (W4A8, not supported), 16 int8 weight. Optional tensors must be present exactly
+    when their bit is set. The weight may be viewed as the activation dtype, as the plugin takes it."""
+    if quant_algo & FP8_ALPHA:
+        raise RuntimeError("W4A8 (FP8_ALPHA) is not supported by this library")
+    if group_size not in (64, 128):
+        raise RuntimeError("group_size must be 64 or 128")
+    for bit, t, name in ((PRE_QUANT_SCALE, pre_quant_scale, "pre_quant_scale"), (ZERO, zeros, "zeros"),
+                         (BIAS, bias, "bias")):
+        if bool(quant_algo & bit) != (t is not None):
+            raise RuntimeError(f"{name} must be given exactly when its quant_algo bit is set")
+    bits = 8 if quant_algo & INT8_WEIGHT else 4
+    return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime)
+
+
+class _PluginBase:
+    """What both TensorRT plugins share: the activation type, one output, borrowed pointers."""
+
+    plugin_namespace = "tensorrt_llm"
+    plugin_version = "1"
+
+    def __init__(self, type_id: int):
+        if type_id not in _TRT_TO_TORCH:
+            raise RuntimeError("Unsupported data type")
+        self.type_id = type_id
+        self.dtype = _TRT_TO_TORCH[type_id]
+        self.dims = None  # (minM, maxM, n, k) once configured
+
+    def get_nb_outputs(self) -> int:
+        return 1
+
+    def get_output_data_type(self, index: int = 0):
+        assert index == 0
+        return self.dtype
+
+    def supports_format_combination(self, pos: int, dtypes: Sequence[torch.dtype]) -> bool:
+        raise NotImplementedError
+
+
+class WeightOnlyQuantMatmulPlugin(_PluginBase):
+    """Mirror of plugin "WeightOnlyQuantMatmul" v1: fields type_id, weight_type_id; inputs
+    [act T[.., K], weight int8 [K, N*bits/8], scales T[N]]; output T[.., N]."""
+
+    plugin_type = "WeightOnlyQuantMatmul"
+
+    def __init__(self, type_id: int, weight_type_id: int):
+        super().__init__(type_id)
+        if weight_type_id not in (WEIGHT_TYPE_INT8, WEIGHT_TYPE_INT4):
+            raise RuntimeError("Unsupported weight type")
+        self.weight_type_id = weight_type_id
+        self.bits = 8 if weight_type_id == WEIGHT_TYPE_INT8 else 4
+
+    def supports_format_combination(self, pos, dtypes):
+        # input 1 (weight) is int8; everything else has the plugin's type (.cpp:229-253)
+        return dtypes[pos] == (torch.int8 if pos == 1 else self.dtype)
+
+    def get_output_dimensions(self, act_shape, weight_shape):
+        return tuple(act_shape[:-1]) + (weight_shape[1] * (2 if self.bits == 4 else 1),)
+
+    def configure_plugin(self, min_m, max_m, n, k):
+        self.dims = (min_m, max_m, n, k)
+
+    def get_workspace_size(self, max_m=None) -> int:
+        if self.dims is None:
+            return 0
+        _, mm, n, k = self.dims
+        return workspace_bytes(max_m or mm, n, k, 0, self.bits, self.dtype, False)
+
+    def enqueue(self, inputs, outputs, workspace=None, stream=None, regime=W4_REGIME_AUTO) -> int:
+        """Returns 0 on success and a non-zero status instead of raising, as the noexcept
+        reference enqueue does."""
+        try:
+            act, weight, scales = inputs
+            k = act.shape[-1]
+            n = weight.shape[1] * (2 if self.bits == 4 else 1)
+            if act.numel() == 0:
+                return 0
+            gemm_raw(act, weight, scales, outputs[0], n=n, k=k, weight_bits=self.bits, group_size=0,
+                     regime=regime, workspace=workspace, stream=stream)
+            return 0
+        except _lib.W4Error as e:
+            return e.status
+
+    def serialize(self) -> bytes:
+        d = self.dims or (0, 0, 0, 0)
+        # type, weightTypeId, GemmDims{minM, maxM, n, k}, then an empty tactic map (count = 0)
+        return struct.pack("<ii4qi", self.type_id, self.weight_type_id, *d, 0)
+
+    @classmethod
+    def deserialize(cls, blob: bytes):
+        t, w, a, b, c, d, _ = struct.unpack("<ii4qi", blob[:struct.calcsize("<ii4qi")])
+        self = cls(t, w)
+        self.dims = (a, b, c, d)
+        return self
+
+
+class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
+    """Mirror of plugin "WeightOnlyGroupwiseQuantMatmul" v1: fields type_id, quant_algo, group_size,
+    alpha; inputs [act, (pre_quant_scale), weight (viewed as T), scales, (zeros), (bias)]."""
+
+    plugin_type = "WeightOnlyGroupwiseQuantMatmul"
+
+    def __init__(self, type_id: int, quant_algo: int, group_size: int, alpha: float = 1.0):
+        super().__init__(type_id)
+        if quant_algo & FP8_ALPHA:
+            raise RuntimeError("W4A8 (FP8_ALPHA) is not supported by this library")
+        if group_size not in (64, 128):
+            raise RuntimeError("group_size must be 64 or 128")
+        self.quant_algo, self.group_size, self.alpha = quant_algo, group_size, float(alpha)
+        # input index math of the reference's init() (.cpp:197-201)
+        self.pre_quant_scale_idx = 1 if quant_algo & PRE_QUANT_SCALE else 0
+        self.weight_idx = self.pre_quant_scale_idx + 1
+        self.scales_idx = self.weight_idx + 1
+        self.zeros_idx = self.scales_idx + 1 if quant_algo & ZERO else self.scales_idx
+        self.bias_idx = self.zeros_idx + 1 if quant_algo & BIAS else self.zeros_idx
+        self.bits = 8 if quant_algo & INT8_WEIGHT else 4
+
+    @property
+    def nb_inputs(self) -> int:
+        return self.bias_idx + 1
+
+    def supports_format_combination(self, pos, dtypes):
+        return dtypes[pos] == self.dtype  # every tensor, weight included, carries the plugin type
+
+    def _real_n(self, weight) -> int:
+        return weight.shape[1] * weight.element_size() * 8 // self.bits
+
+    def get_output_dimensions(self, act_shape, weight):
+        return tuple(act_shape[:-1]) + (self._real_n(weight),)
+
+    def configure_plugin(self, min_m, max_m, n, k):
+        self.dims = (min_m, max_m, n, k)
+
+    def get_workspace_size(self, max_m=None) -> int:
+        if self.dims is None:
+            return 0
+        _, mm, n, k = self.dims
+        return workspace_bytes(max_m or mm, n, k, self.group_size, self.bits, self.dtype,
+                               bool(self.quant_algo & PRE_QUANT_SCALE))
+
+    def enqueue(self, inputs, outputs, workspace=None, stream=None, regime=W4_REGIME_AUTO) -> int:
+        try:
+            if len(inputs) != self.nb_inputs:
+                return _lib.lib().w4_gemm_validate(None)
+            act = inputs[0]
+            weight = inputs[self.weight_idx]
+            if act.numel() == 0:
+                return 0
+            gemm_raw(act, weight, inputs[self.scales_idx], outputs[0], n=self._real_n(weight), k=act.shape[-1],
+                     weight_bits=self.bits, group_size=self.group_size,
+                     zeros=inputs[self.zeros_idx] if self.quant_algo & ZERO else None,
+                     bias=inputs[self.bias_idx] if self.quant_algo & BIAS else None,
+                     act_scale=inputs[self.pre_quant_scale_idx] if self.quant_algo & PRE_QUANT_SCALE else None,
+                     alpha=self.alpha, regime=regime, workspace=workspace, stream=stream)
+            return 0
+        except _lib.W4Error as e:
+            return e.status
+
+    def serialize(self) -> bytes:
+        d = self.dims or (0, 0, 0, 0)
+        return struct.pack("<iiif4qi", self.type_id, self.quant_algo, self.group_size, self.alpha, *d, 0)
+
+    @classmethod
+    def deserialize(cls, blob: bytes):
+        fmt = "<iiif4qi"
+        t, q, g, al, a, b, c, d, _ = struct.unpack(fmt, blob[:struct.calcsize(fmt)])
+        self = cls(t, q, g, al)
+        self.dims = (a, b, c, d)
+        return self

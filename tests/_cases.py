@@ -1,0 +1,52 @@
+"""Seeded synthetic problems shared by the CPU and GPU tests (test infrastructure)."""
+from __future__ import annotations
+
+import torch
+
+import tensorrt_llm_b200 as pkg
+from tensorrt_llm_b200 import quantize
+from oracle import woq_oracle as oracle
+
+
+def make_problem(m, n, k, bits, group, dtype, zero=False, bias=False, prequant=False, seed=0,
+                 act_scale=1.0, scale_lo=0.001, scale_hi=0.02):
+    """Random integer weights in the full int range, scales ~U(scale_lo, scale_hi), zeros
+    ~U(-0.1, 0.1), activations ~N(0, 1)*act_scale. group 0 = one scale per column."""
+    g = torch.Generator().manual_seed(seed)
+    lo, hi = (-8, 8) if bits == 4 else (-128, 128)
+    q = torch.randint(lo, hi, (k, n), dtype=torch.int8, generator=g)
+    packed = quantize.pack_int8_tensor_to_packed_int4(q) if bits == 4 else q
+    qt = torch.quint4x2 if bits == 4 else torch.int8
+    processed = quantize.preprocess_weights_for_mixed_gemm(packed.contiguous(), qt, torch.float16)
+    rows = 1 if group == 0 else k // group
+    shape = (n,) if group == 0 else (rows, n)
+    scales = (torch.rand(shape, generator=g) * (scale_hi - scale_lo) + scale_lo).to(dtype)
+    zeros = ((torch.rand(shape, generator=g) * 0.2 - 0.1).to(dtype)) if zero else None
+    b = torch.randn((n,), generator=g).to(dtype) if bias else None
+    ps = (torch.rand((k,), generator=g) + 0.5).to(dtype) if prequant else None
+    act = (torch.randn((m, k), generator=g) * act_scale).to(dtype)
+    return dict(m=m, n=n, k=k, bits=bits, group=group, dtype=dtype, q=q, packed=packed, processed=processed,
+                scales=scales, zeros=zeros, bias=b, ps=ps, act=act)
+
+
+def oracle_out(p, alpha=1.0):
+    return oracle.kernel_rounding_ref(p["act"], p["q"], p["scales"], zeros=p["zeros"], bias=p["bias"],
+                                      pre_quant_scale=p["ps"], group_size=p["group"], alpha=alpha)
+
+
+def run_gpu(p, regime=0, alpha=1.0, device="cuda"):
+    """Through the public op (and so through the C ABI)."""
+    d = lambda t: None if t is None else t.to(device)
+    if p["group"] == 0:
+        assert p["zeros"] is None and p["bias"] is None and p["ps"] is None and alpha == 1.0
+        return pkg.ops.weight_only_quant_matmul(d(p["act"]), d(p["processed"]), d(p["scales"]),
+                                                1 if p["bits"] == 8 else 2, regime=regime).cpu()
+    algo = (pkg.INT8_WEIGHT if p["bits"] == 8 else 0) | (pkg.ZERO if p["zeros"] is not None else 0) \
+        | (pkg.BIAS if p["bias"] is not None else 0) | (pkg.PRE_QUANT_SCALE if p["ps"] is not None else 0)
+    return pkg.ops.weight_only_groupwise_quant_matmul(
+        d(p["act"]), d(p["ps"]), d(p["processed"]), d(p["scales"]), d(p["zeros"]), d(p["bias"]), alpha, algo,
+        p["group"], regime=regime).cpu()
+
+
+def max_err(out, ref):
+    return float((out.to(torch.float64) - ref.to(torch.float64)).abs().max())
