@@ -5,5 +5,5 @@ here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 out="$here/../libw4gemm.so"
 nvcc -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a \
      -Xcompiler -fPIC,-O3,-pthread ${W4_NVCC_EXTRA:-} \
-     -shared "$here/w4_lib.cu" "$here/w4_preprocess.cpp" -o "$out" -lcuda
+     -shared "$here/w4_lib.cu" "$here/w4_preprocess.cpp" -o "$out"
 echo "built $out"

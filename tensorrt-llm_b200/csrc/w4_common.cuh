@@ -85,6 +85,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, void const* src, uint32_t by
                  : "memory");
 }
 
+// 2-D tiled TMA load (tensor map in kernel parameter / constant space). c0 = innermost coordinate
+// (its byte offset must be a multiple of 16), c1 = row. Out-of-range parts of the box read as zero
+// and still count towards the transaction bytes.
+__device__ __forceinline__ void tma_load_2d(void* dst, void const* tensor_map, int c0, int c1, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(smem_u32(dst)),
+        "l"(tensor_map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -2,20 +2,17 @@
 //
 // Replaces weight_only::kernel of the reference project
 // (cpp/tensorrt_llm/kernels/weightOnlyBatchedGemv/kernel.h:31-120) and, for m >= 5 / m >= 16, the
-// small-M CUTLASS tactics it falls back to. Same math: the dequantised weight is
-// round_T(fma(q, scale, zero)) (utility.h:157-162), the pre-quant scale product is rounded to T
-// (utility.h:116), alpha * acc + bias is formed in fp32 (utility.h:256-266). Unlike the reference
-// the dot product itself is accumulated in fp32.
+// small-M CUTLASS tactics it falls back to.
 //
 // Design (B200): one persistent CTA per SM owns a contiguous range of "interleaved rows" of the
 // preprocessed weight (one interleaved row = IL adjacent output columns x all of K = 2K bytes, see
 // below), so every CTA streams one contiguous slab of HBM. A producer warp moves that slab into a
-// shared-memory ring with bulk (TMA-engine) copies, hundreds of KB in flight per SM from the first
-// cycle; 16 consumer warps split K, pull 16-byte chunks out of the ring with 128-bit shared loads,
-// convert and dequantise in registers and feed mma.sync (weights as the 16-row A operand, the m <= 8
-// activation rows as the 8-column B operand), accumulating in fp32. Partial sums of the 16 warps
-// are combined through shared memory in a fixed order (deterministic), then alpha/bias are applied
-// and the result stored.
+// shared-memory ring with bulk (TMA-engine) copies, ~190 KB in flight per SM from the first cycle
+// (its spare lanes prefetch the CTA's scale/zero lines into L2); 16 consumer warps split K, pull
+// 16-byte chunks out of the ring with 128-bit shared loads and feed mma.sync (weights as the 16-row
+// A operand, the m <= 8 activation rows as the 8-column B operand), accumulating in fp32. Partial
+// sums of the 16 warps are combined through shared memory in a fixed order (deterministic) once
+// per batch of column groups, then alpha/bias are applied and the result stored.
 //
 // Weight layout consumed (preprocess_weights_for_mixed_gemm on sm_100,
 // cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:564-615): interleaved row R
@@ -23,21 +20,37 @@
 // one 64-wide k tile, split into IL column segments; every aligned 16-byte chunk holds CK = 32
 // (int4) / 16 (int8) consecutive k of one column in the order
 // { 2j+8q+e : register j = 0..3, pair q, element e }, with the nibbles/bytes of each 32-bit
-// register pre-shuffled for the converters in w4_common.cuh. Because a dot product does not care
-// about the order of k, each thread treats the chunk it loaded as its own mma fragment and the
-// activation fragment is simply loaded in the matching order.
+// register pre-shuffled. Because a dot product does not care about the order of k, each thread
+// treats the chunk it loaded as its own mma fragment and the activation fragment is simply loaded
+// in the matching order.
+//
+// Arithmetic. Two variants, chosen per problem:
+//  * EXACT (int4 with group size 64): as the reference's kernels, the dequantised weight is
+//    round_T(fma(q, scale, zero)) (weightOnlyBatchedGemv/utility.h:157-162) and that is what is
+//    multiplied; the sum is kept in fp32 (the reference GEMV keeps it in T).
+//  * FOLDED (everything else): within one scale group sum_k a_k (q_k s + z) = s * sum_k a_k q_k +
+//    z * sum_k a_k, so the tensor cores multiply the activations with the raw biased integers,
+//    placed into the mantissa of a magic constant C by a single logic op (C + u, exact), and the
+//    scale, the zero and the -(C + bias) * sum_k a_k correction are applied to the fp32 group sum.
+//    No per-weight floating-point instruction is left. The weight is not rounded to T first, so
+//    the result is closer to real arithmetic than the reference's; it stays far inside the 1e-2 *
+//    max|ref| bound this path is held to.
+// In both, the pre-quant scale product is rounded to T (utility.h:116) and alpha * acc + bias is
+// formed in fp32 (utility.h:256-266).
 #include "w4_common.cuh"
 #include "w4_internal.h"
+#include "w4_tma.h"
 
 namespace w4
 {
-
 namespace gemv
 {
 
-constexpr int kWarps = 16;                       // consumer warps
-constexpr int kConsumerThreads = kWarps * 32;    // 512
-constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kWarps = 16;                      // consumer warps
+constexpr int kConsumerThreads = kWarps * 32;   // 512
+constexpr int kThreads = kConsumerThreads;      // no dedicated producer: see issue_tile()
+constexpr int kRedBytes = 16 * 1024;            // shared memory for cross-warp partial sums
+constexpr int kScaleBoxCols = 24;               // columns per scale/zero box: 16 + slack to start on a 16-byte boundary
 
 template <int BITS, int MB>
 struct Cfg
@@ -51,7 +64,54 @@ struct Cfg
     static constexpr int ROW_STRIDE = 2 * KP;           // bytes of one interleaved row inside a tile
     static constexpr int TILE_BYTES = RPG * ROW_STRIDE; // 32 KB (MB = 1) or 16 KB (MB = 2)
     static constexpr int AREGS = CK / 2;                // activation pair registers per chunk
-    static constexpr int RED_FLOATS = 2 * kWarps * MB * 4 * 32;
+};
+
+// Constants of the FOLDED variant. The biased integer u = q + BIAS is turned into the T value
+// MAGIC + u. PLANES == 2 (bf16 + int8, whose 8-bit payload does not fit a bf16 mantissa) splits
+// every byte into two nibbles: the low-nibble plane meets activations scaled by 1/16, so the unit
+// sum is S = (1/16) sum a u + MAGIC (1 + 1/16) sum a.
+template <typename T, int BITS>
+struct Fold;
+template <>
+struct Fold<__half, 4>
+{
+    static constexpr uint32_t MAGIC2 = 0x64006400u; // {1024, 1024}
+    static constexpr float SCALE = 1.f, CORR = 1024.f + 8.f;
+    static constexpr int PLANES = 1;
+};
+template <>
+struct Fold<__nv_bfloat16, 4>
+{
+    static constexpr uint32_t MAGIC2 = 0x43004300u; // {128, 128}
+    static constexpr float SCALE = 1.f, CORR = 128.f + 8.f;
+    static constexpr int PLANES = 1;
+};
+template <>
+struct Fold<__half, 8>
+{
+    static constexpr uint32_t MAGIC2 = 0x64646464u; // prmt source: 0x64 high bytes -> 1024 + byte
+    static constexpr float SCALE = 1.f, CORR = 1024.f + 128.f;
+    static constexpr int PLANES = 1;
+};
+template <>
+struct Fold<__nv_bfloat16, 8>
+{
+    static constexpr uint32_t MAGIC2 = 0x43004300u;
+    static constexpr float SCALE = 16.f, CORR = 17.f * 128.f + 128.f;
+    static constexpr int PLANES = 2;
+};
+
+template <typename T>
+struct Consts;
+template <>
+struct Consts<__half>
+{
+    static constexpr uint32_t ONE2 = 0x3c003c00u, SIXTEENTH2 = 0x2c002c00u;
+};
+template <>
+struct Consts<__nv_bfloat16>
+{
+    static constexpr uint32_t ONE2 = 0x3f803f80u, SIXTEENTH2 = 0x3d803d80u;
 };
 
 struct Args
@@ -64,12 +124,16 @@ struct Args
     void const* bias;
     void* out;
     float alpha;
-    int m; // rows handled by this launch (<= 8 * MB)
+    int m;           // rows handled by this launch (<= 8 * MB)
     int n;
     int k;
-    int group; // group size; k for per-channel
-    int num_rows; // n / IL
+    int group_shift; // log2(group size); 31 for per-channel (k >> 31 == 0)
+    int num_groups;  // rows of the scale tensor (1 for per-channel)
+    int num_rows;    // n / IL
     int num_slots;
+    int slot_bytes;       // tile bytes + scale/zero boxes, multiple of 128
+    int groups_per_panel; // scale rows delivered with every tile (1 for per-channel)
+    int box_stride;       // bytes between the scale box and the zero box (multiple of 128)
 };
 
 // Shared flag: once any wait in the CTA timed out, every later wait returns at once.
@@ -87,18 +151,25 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(Args const a)
+__device__ __forceinline__ void prefetch_l2(void const* p)
+{
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros)
 {
     using C = Cfg<BITS, MB>;
     using P = Pair<T>;
+    using F = Fold<T, BITS>;
+    constexpr int PLANES = FOLD ? F::PLANES : 1;
     extern __shared__ __align__(128) uint8_t smem[];
 
     uint8_t* ring = smem;
-    float* red = reinterpret_cast<float*>(smem + size_t(a.num_slots) * C::TILE_BYTES);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(red + C::RED_FLOATS);
-    uint64_t* empty_bar = full_bar + a.num_slots;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + a.num_slots);
+    float* red = reinterpret_cast<float*>(smem + size_t(a.num_slots) * a.slot_bytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(a.num_slots) * a.slot_bytes + kRedBytes);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(full_bar + a.num_slots);
 
     int const tid = threadIdx.x;
     int const warp = tid >> 5, lane = tid & 31;
@@ -108,45 +179,50 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(Args const a)
     int const r1 = int((int64_t(a.num_rows) * (blockIdx.x + 1)) / gridDim.x);
     int const num_cg = (r1 - r0 + C::RPG - 1) / C::RPG;
     int const num_panels = (a.k + C::KP - 1) / C::KP;
-    int const num_tiles = num_cg * num_panels;
     size_t const row_bytes = size_t(2) * a.k;
+
+    int* done = const_cast<int*>(abort_flag) + 1; // per slot: warps that finished reading it
+    int const num_tiles = num_cg * num_panels;
+
+    // Starts the bulk copies of tile i (column group i / num_panels, k panel i % num_panels) into
+    // its ring slot. Called by one thread: thread 0 for the first num_slots tiles, afterwards by
+    // whichever warp was the last to finish reading the slot's previous tile, so nobody ever waits
+    // for a slot to drain and no warp is set aside as a producer.
+    auto issue_tile = [&](int i, int slot)
+    {
+        int const cg = i / num_panels, panel = i - cg * num_panels;
+        int const row_first = r0 + cg * C::RPG;
+        int const rows = min(C::RPG, r1 - row_first);
+        int const kp_len = min(C::KP, a.k - panel * C::KP);
+        uint32_t const bytes = 2u * kp_len;
+        uint32_t const box_bytes = uint32_t(a.groups_per_panel) * kScaleBoxCols * 2;
+        mbar_expect_tx(&full_bar[slot], bytes * rows + box_bytes * (HAS_ZERO ? 2 : 1));
+        uint8_t* dst = ring + size_t(slot) * a.slot_bytes;
+        uint8_t const* src = a.weight + size_t(row_first) * row_bytes + size_t(panel) * C::ROW_STRIDE;
+        for (int r = 0; r < rows; ++r)
+            bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
+        // The scale / zero rows of this panel for the group's columns travel with the tile, from
+        // the 8-column boundary at or below the group's first column.
+        int const col_aligned = (row_first * C::IL) & ~7;
+        int const grow = a.group_shift >= 31 ? 0 : panel * a.groups_per_panel;
+        tma_load_2d(dst + C::TILE_BYTES, &tm_scales, col_aligned, grow, &full_bar[slot]);
+        if (HAS_ZERO)
+            tma_load_2d(dst + C::TILE_BYTES + a.box_stride, &tm_zeros, col_aligned, grow, &full_bar[slot]);
+    };
 
     if (tid == 0)
     {
         for (int s = 0; s < a.num_slots; ++s)
         {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kWarps);
+            done[s] = 0;
         }
         *abort_flag = 0;
         mbar_fence_init();
+        for (int i = 0; i < min(a.num_slots, num_tiles); ++i)
+            issue_tile(i, i);
     }
     __syncthreads();
-
-    if (warp == kWarps)
-    {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0)
-        {
-            for (int i = 0; i < num_tiles; ++i)
-            {
-                int const slot = i % a.num_slots, use = i / a.num_slots;
-                if (use > 0 && !wait_or_abort(&empty_bar[slot], (use - 1) & 1, abort_flag))
-                    break;
-                int const cg = i / num_panels, panel = i - cg * num_panels;
-                int const row_first = r0 + cg * C::RPG;
-                int const rows = min(C::RPG, r1 - row_first);
-                int const kp_len = min(C::KP, a.k - panel * C::KP);
-                uint32_t const bytes = 2u * kp_len;
-                mbar_expect_tx(&full_bar[slot], bytes * rows);
-                uint8_t* dst = ring + size_t(slot) * C::TILE_BYTES;
-                uint8_t const* src = a.weight + size_t(row_first) * row_bytes + size_t(panel) * C::ROW_STRIDE;
-                for (int r = 0; r < rows; ++r)
-                    bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
-            }
-        }
-        return;
-    }
 
     // ---------------------------------------------------------------------- consumers
     int const g = lane >> 2, t = lane & 3;
@@ -159,56 +235,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(Args const a)
     int const segA = (colA / C::IL) * C::ROW_STRIDE + (colA % C::IL) * (128 / C::IL);
     int const segB = (colB / C::IL) * C::ROW_STRIDE + (colB % C::IL) * (128 / C::IL);
 
-    uint16_t const* scales = static_cast<uint16_t const*>(a.scales);
-    uint16_t const* zeros = static_cast<uint16_t const*>(a.zeros);
     T const* act = static_cast<T const*>(a.act);
     T const* act_scale = static_cast<T const*>(a.act_scale);
 
     uint32_t afrag[C::UPW][MB][C::AREGS];
-    uint32_t s_cur[C::UPW], z_cur[C::UPW], s_nxt[C::UPW], z_nxt[C::UPW];
+    uint32_t afrag_lo[PLANES == 2 ? C::UPW : 1][MB][PLANES == 2 ? C::AREGS : 1]; // activations / 16
+    float asum[C::UPW][MB][2]; // FOLDED: sum of this unit's activations for rows 2t, 2t+1
 
-    // (scale, zero) words of this thread's two columns for tile i: low half = column A.
-    auto load_scales = [&](int i, uint32_t(&s)[C::UPW], uint32_t(&z)[C::UPW])
+    // (scale, zero) words of this thread's two columns (low half = column A) for unit j, read from
+    // the boxes that arrived with the tile. FOLDED applies them to the unit's sum, so the group is
+    // that of the unit; EXACT applies them to the thread's own chunk.
+    auto read_scales = [&](int j, int cg, uint8_t const* tile, uint32_t& s, uint32_t& z)
     {
-        int const cg = i / num_panels, panel = i - cg * num_panels;
+        int const kk = (j * kWarps + warp) * C::UK + (FOLD ? 0 : t * C::CK);
         int const col_base = (r0 + cg * C::RPG) * C::IL;
-        bool const va = (r0 + cg * C::RPG + colA / C::IL) < r1;
-        bool const vb = (r0 + cg * C::RPG + colB / C::IL) < r1;
-#pragma unroll
-        for (int j = 0; j < C::UPW; ++j)
+        int const coff = col_base - (col_base & ~7);
+        uint16_t const* sc = reinterpret_cast<uint16_t const*>(tile + C::TILE_BYTES)
+            + (kk >> a.group_shift) * kScaleBoxCols + coff;
+        uint16_t const* zr = sc + a.box_stride / 2;
+        z = 0;
+        if (BITS == 4)
         {
-            int const k0 = panel * C::KP + (j * kWarps + warp) * C::UK + t * C::CK;
-            s[j] = 0;
-            z[j] = 0;
-            if (k0 < a.k)
-            {
-                size_t const base = size_t(k0 / a.group) * a.n + col_base;
-                if (BITS == 4)
-                {
-                    if (va) // columns A and B share an interleaved row for int4
-                    {
-                        s[j] = __ldg(reinterpret_cast<uint32_t const*>(scales + base + colA));
-                        if (HAS_ZERO)
-                            z[j] = __ldg(reinterpret_cast<uint32_t const*>(zeros + base + colA));
-                    }
-                }
-                else
-                {
-                    uint32_t sa = va ? __ldg(scales + base + colA) : 0u;
-                    uint32_t sb = vb ? __ldg(scales + base + colB) : 0u;
-                    s[j] = sa | (sb << 16);
-                    if (HAS_ZERO)
-                    {
-                        uint32_t za = va ? __ldg(zeros + base + colA) : 0u;
-                        uint32_t zb = vb ? __ldg(zeros + base + colB) : 0u;
-                        z[j] = za | (zb << 16);
-                    }
-                }
-            }
+            s = *reinterpret_cast<uint32_t const*>(sc + colA);
+            if (HAS_ZERO)
+                z = *reinterpret_cast<uint32_t const*>(zr + colA);
+        }
+        else
+        {
+            s = uint32_t(sc[colA]) | (uint32_t(sc[colB]) << 16);
+            if (HAS_ZERO)
+                z = uint32_t(zr[colA]) | (uint32_t(zr[colB]) << 16);
         }
     };
 
-    // Activation fragments of this warp's units for one k panel, in chunk order.
+    // Activation fragments of this warp's units for one k panel, in chunk order; FOLDED also
+    // needs the per-unit activation sums, obtained with an all-ones A fragment.
     auto load_act = [&](int panel)
     {
 #pragma unroll
@@ -241,132 +302,265 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(Args const a)
                     afrag[j][mb][4 * v + 2] = x.z;
                     afrag[j][mb][4 * v + 3] = x.w;
                 }
+                if (FOLD)
+                {
+                    constexpr uint32_t one = Consts<T>::ONE2;
+                    uint32_t const ones[4] = {one, one, one, one};
+                    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int i = 0; i < C::AREGS / 2; ++i)
+                    {
+                        // same (b0, b1) pairing as the main loop; any pairing covers all of k once
+                        int const lo = BITS == 4 ? (i >> 1) + 8 * (i & 1) : i;
+                        P::mma(sum, ones, afrag[j][mb][lo], afrag[j][mb][lo + 4]);
+                    }
+                    asum[j][mb][0] = sum[0];
+                    asum[j][mb][1] = sum[1];
+                    if (PLANES == 2)
+                    {
+#pragma unroll
+                        for (int i = 0; i < C::AREGS; ++i)
+                            afrag_lo[j][mb][i] = P::mul(afrag[j][mb][i], Consts<T>::SIXTEENTH2);
+                    }
+                }
             }
         }
     };
 
-    if (num_tiles > 0)
-    {
-        load_scales(0, s_nxt, z_nxt);
-        load_act(0);
-    }
+    float acc[MB][4]; // running sums of the current column group
 
-    bool ok = true;
-    int i = 0;
-    for (int cg = 0; cg < num_cg; ++cg)
+    // One warp unit (16 columns x UK k) out of the tile in shared memory.
+    auto process_unit = [&](int j, int cg, uint8_t const* tile)
     {
-        float acc[MB][4];
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                acc[mb][c] = 0.f;
+        uint32_t s_word, z_word;
+        read_scales(j, cg, tile, s_word, z_word);
+        // Chunk of this thread inside the row piece: k offset kk -> 128-byte line kk/64, 16-byte
+        // slot (kk%64)/CK inside the column segment.
+        int const kk = (j * kWarps + warp) * C::UK + t * C::CK;
+        int const off = (kk >> 6) * 128 + ((kk & 63) / C::CK) * 16;
+        uint4 const wa = *reinterpret_cast<uint4 const*>(tile + segA + off);
+        uint4 const wb = *reinterpret_cast<uint4 const*>(tile + segB + off);
+        uint32_t const ra[4] = {wa.x, wa.y, wa.z, wa.w};
+        uint32_t const rb[4] = {wb.x, wb.y, wb.z, wb.w};
 
-        for (int panel = 0; panel < num_panels; ++panel, ++i)
+        if (FOLD)
         {
+            constexpr uint32_t kMagic = F::MAGIC2;
+            float S[2][MB][4]; // two independent accumulation chains
 #pragma unroll
-            for (int j = 0; j < C::UPW; ++j)
+            for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        S[ch][mb][c] = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj)
             {
-                s_cur[j] = s_nxt[j];
-                z_cur[j] = z_nxt[j];
-            }
-            if (i + 1 < num_tiles)
-                load_scales(i + 1, s_nxt, z_nxt);
-            if (num_panels > 1 && i > 0)
-                load_act(panel);
-
-            int const slot = i % a.num_slots, use = i / a.num_slots;
-            if (ok)
-                ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
-            uint8_t const* tile = ring + size_t(slot) * C::TILE_BYTES;
-
-#pragma unroll
-            for (int j = 0; j < C::UPW; ++j)
-            {
-                // Chunk of this thread inside the row piece: k offset kk -> 128-byte line kk/64,
-                // 16-byte slot (kk%64)/CK inside the column segment.
-                int const kk = (j * kWarps + warp) * C::UK + t * C::CK;
-                int const off = (kk >> 6) * 128 + ((kk & 63) / C::CK) * 16;
-                uint4 const wa = *reinterpret_cast<uint4 const*>(tile + segA + off);
-                uint4 const wb = *reinterpret_cast<uint4 const*>(tile + segB + off);
-                uint32_t const ra[4] = {wa.x, wa.y, wa.z, wa.w};
-                uint32_t const rb[4] = {wb.x, wb.y, wb.z, wb.w};
-                uint32_t const sA = prmt(s_cur[j], s_cur[j], 0x1010u), sB = prmt(s_cur[j], s_cur[j], 0x3232u);
-                uint32_t const zA = prmt(z_cur[j], z_cur[j], 0x1010u), zB = prmt(z_cur[j], z_cur[j], 0x3232u);
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj)
+                if (BITS == 4)
                 {
-                    if (BITS == 4)
+                    uint32_t xa[4], xb[4];
+#pragma unroll
+                    for (int p = 0; p < 4; ++p)
                     {
-                        uint32_t qa[4], qb[4];
-                        cvt_int4x8<T>(ra[jj], qa);
-                        cvt_int4x8<T>(rb[jj], qb);
-#pragma unroll
-                        for (int p = 0; p < 4; ++p)
-                        {
-                            qa[p] = HAS_ZERO ? P::fma(qa[p], sA, zA) : P::mul(qa[p], sA);
-                            qb[p] = HAS_ZERO ? P::fma(qb[p], sB, zB) : P::mul(qb[p], sB);
-                        }
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                        {
-                            uint32_t const frag[4] = {qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1]};
-#pragma unroll
-                            for (int mb = 0; mb < MB; ++mb)
-                                P::mma(acc[mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
-                        }
+                        xa[p] = lop3_and_or(ra[jj] >> (4 * p), 0x000f000fu, kMagic);
+                        xb[p] = lop3_and_or(rb[jj] >> (4 * p), 0x000f000fu, kMagic);
                     }
-                    else
-                    {
-                        uint32_t qa[2], qb[2];
-                        cvt_int8x4<T>(ra[jj], qa);
-                        cvt_int8x4<T>(rb[jj], qb);
 #pragma unroll
-                        for (int p = 0; p < 2; ++p)
-                        {
-                            qa[p] = HAS_ZERO ? P::fma(qa[p], sA, zA) : P::mul(qa[p], sA);
-                            qb[p] = HAS_ZERO ? P::fma(qb[p], sB, zB) : P::mul(qb[p], sB);
-                        }
-                        uint32_t const frag[4] = {qa[0], qb[0], qa[1], qb[1]};
+                    for (int h = 0; h < 2; ++h)
+                    {
+                        uint32_t const frag[4] = {xa[2 * h], xb[2 * h], xa[2 * h + 1], xb[2 * h + 1]};
 #pragma unroll
                         for (int mb = 0; mb < MB; ++mb)
-                            P::mma(acc[mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                            P::mma(S[h][mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
+                    }
+                }
+                else if (PLANES == 1)
+                {
+                    uint32_t const frag[4] = {prmt(ra[jj], kMagic, 0x4240u), prmt(rb[jj], kMagic, 0x4240u),
+                        prmt(ra[jj], kMagic, 0x4341u), prmt(rb[jj], kMagic, 0x4341u)};
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                        P::mma(S[jj & 1][mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                }
+                else
+                {
+                    // nibble planes of the bytes: (byte0, byte2) and (byte1, byte3) pairs
+                    uint32_t const lo[4] = {lop3_and_or(ra[jj], 0x000f000fu, kMagic),
+                        lop3_and_or(rb[jj], 0x000f000fu, kMagic), lop3_and_or(ra[jj] >> 8, 0x000f000fu, kMagic),
+                        lop3_and_or(rb[jj] >> 8, 0x000f000fu, kMagic)};
+                    uint32_t const hi[4] = {lop3_and_or(ra[jj] >> 4, 0x000f000fu, kMagic),
+                        lop3_and_or(rb[jj] >> 4, 0x000f000fu, kMagic), lop3_and_or(ra[jj] >> 12, 0x000f000fu, kMagic),
+                        lop3_and_or(rb[jj] >> 12, 0x000f000fu, kMagic)};
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                    {
+                        int const jl = PLANES == 2 ? j : 0, ml = PLANES == 2 ? mb : 0;
+                        int const i0 = PLANES == 2 ? jj : 0, i1 = PLANES == 2 ? jj + 4 : 0;
+                        P::mma(S[0][mb], lo, afrag_lo[jl][ml][i0], afrag_lo[jl][ml][i1]);
+                        P::mma(S[1][mb], hi, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&empty_bar[slot]);
+            // scale, zero and magic-constant correction on the fp32 group sums
+            float const sA = P::to_float(uint16_t(s_word & 0xffffu)) , sB = P::to_float(uint16_t(s_word >> 16));
+            float zA = 0.f, zB = 0.f;
+            if (HAS_ZERO)
+            {
+                zA = P::to_float(uint16_t(z_word & 0xffffu));
+                zB = P::to_float(uint16_t(z_word >> 16));
+            }
+            float const cA = fmaf(-F::CORR, sA, zA), cB = fmaf(-F::CORR, sB, zB);
+            float const mA = sA * F::SCALE, mB = sB * F::SCALE;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+            {
+                acc[mb][0] = fmaf(mA, S[0][mb][0] + S[1][mb][0], fmaf(cA, asum[j][mb][0], acc[mb][0]));
+                acc[mb][1] = fmaf(mA, S[0][mb][1] + S[1][mb][1], fmaf(cA, asum[j][mb][1], acc[mb][1]));
+                acc[mb][2] = fmaf(mB, S[0][mb][2] + S[1][mb][2], fmaf(cB, asum[j][mb][0], acc[mb][2]));
+                acc[mb][3] = fmaf(mB, S[0][mb][3] + S[1][mb][3], fmaf(cB, asum[j][mb][1], acc[mb][3]));
+            }
+        }
+        else
+        {
+            uint32_t const sA = prmt(s_word, s_word, 0x1010u), sB = prmt(s_word, s_word, 0x3232u);
+            uint32_t const zA = prmt(z_word, z_word, 0x1010u), zB = prmt(z_word, z_word, 0x3232u);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj)
+            {
+                if (BITS == 4)
+                {
+                    uint32_t qa[4], qb[4];
+                    cvt_int4x8<T>(ra[jj], qa);
+                    cvt_int4x8<T>(rb[jj], qb);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p)
+                    {
+                        qa[p] = HAS_ZERO ? P::fma(qa[p], sA, zA) : P::mul(qa[p], sA);
+                        qb[p] = HAS_ZERO ? P::fma(qb[p], sB, zB) : P::mul(qb[p], sB);
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                    {
+                        uint32_t const frag[4] = {qa[2 * h], qb[2 * h], qa[2 * h + 1], qb[2 * h + 1]};
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb)
+                            P::mma(acc[mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
+                    }
+                }
+                else
+                {
+                    uint32_t qa[2], qb[2];
+                    cvt_int8x4<T>(ra[jj], qa);
+                    cvt_int8x4<T>(rb[jj], qb);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p)
+                    {
+                        qa[p] = HAS_ZERO ? P::fma(qa[p], sA, zA) : P::mul(qa[p], sA);
+                        qb[p] = HAS_ZERO ? P::fma(qb[p], sB, zB) : P::mul(qb[p], sB);
+                    }
+                    uint32_t const frag[4] = {qa[0], qb[0], qa[1], qb[1]};
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                        P::mma(acc[mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                }
+            }
+        }
+    };
+
+    // Partial sums in shared memory: [cg in batch][warp][mb][c][g * MT + t], only the lanes whose
+    // rows exist (t < MT) are stored.
+    int const MT = MB == 2 ? 4 : (a.m + 1) >> 1;
+    int const per_cg = kWarps * MB * 4 * 8 * MT;
+    int const batch = max(1, (kRedBytes / 4) / per_cg);
+
+    if (num_cg > 0)
+        load_act(0);
+
+    bool ok = true;
+    int slot = 0, use = 0, tile_index = 0;
+    for (int cg0 = 0; cg0 < num_cg; cg0 += batch)
+    {
+        int const nb = min(batch, num_cg - cg0);
+        for (int cb = 0; cb < nb; ++cb)
+        {
+            int const cg = cg0 + cb;
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    acc[mb][c] = 0.f;
+
+            for (int panel = 0; panel < num_panels; ++panel)
+            {
+                if (num_panels > 1 && (cg > 0 || panel > 0))
+                    load_act(panel);
+
+                if (ok)
+                    ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
+                uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
+#pragma unroll
+                for (int j = 0; j < C::UPW; ++j)
+                    process_unit(j, cg, tile);
+                // The last warp to finish with this slot refills it with the tile num_slots ahead.
+                __syncwarp();
+                if (lane == 0)
+                {
+                    __threadfence_block();
+                    if (atomicAdd(&done[slot], 1) == kWarps - 1)
+                    {
+                        done[slot] = 0;
+                        int const next = tile_index + a.num_slots;
+                        if (next < num_tiles)
+                        {
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            issue_tile(next, slot);
+                        }
+                    }
+                }
+                ++tile_index;
+                if (++slot == a.num_slots)
+                {
+                    slot = 0;
+                    ++use;
+                }
+            }
+            if (t < MT)
+            {
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        red[(((cb * kWarps + warp) * MB + mb) * 4 + c) * (8 * MT) + g * MT + t] = acc[mb][c];
+            }
         }
 
-        // Combine the 16 warps' partial sums (fixed order) and write this column group.
-        float* buf = red + (cg & 1) * (C::RED_FLOATS / 2);
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                buf[((warp * MB + mb) * 4 + c) * 32 + lane] = acc[mb][c];
+        // Combine the 16 warps' partial sums in a fixed order and write this batch of columns.
         named_bar_sync(1, kConsumerThreads);
-        if (tid < 128 * MB)
+        constexpr int MPAD = 8 * MB;
+        for (int o = tid; o < nb * 16 * MPAD; o += kConsumerThreads)
         {
-            int const mb = tid >> 7, c = (tid >> 5) & 3, l = tid & 31;
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w)
-                sum += buf[((w * MB + mb) * 4 + c) * 32 + l];
-            int const lg = l >> 2, lt = l & 3;
-            int const col_in = (c < 2) ? (BITS == 4 ? 2 * lg : lg) : (BITS == 4 ? 2 * lg + 1 : 8 + lg);
-            int const row = mb * 8 + 2 * lt + (c & 1);
-            int const irow = r0 + cg * C::RPG + col_in / C::IL;
+            int const col_in = o & 15, row = (o >> 4) & (MPAD - 1), cb = o / (16 * MPAD);
+            int const lg = BITS == 4 ? col_in >> 1 : col_in & 7;
+            int const chalf = BITS == 4 ? col_in & 1 : col_in >> 3;
+            int const irow = r0 + (cg0 + cb) * C::RPG + col_in / C::IL;
             if (row < a.m && irow < r1)
             {
-                int const col = (r0 + cg * C::RPG) * C::IL + col_in;
+                int const mb = row >> 3, lt = (row & 7) >> 1, c = chalf * 2 + (row & 1);
+                float const* src = red + ((cb * kWarps * MB + mb) * 4 + c) * (8 * MT) + lg * MT + lt;
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w)
+                    sum += src[w * MB * 4 * 8 * MT];
+                int const col = (r0 + (cg0 + cb) * C::RPG) * C::IL + col_in;
                 float v = a.alpha * sum;
                 if (a.bias)
                     v += P::to_float(static_cast<uint16_t const*>(a.bias)[col]);
                 static_cast<uint16_t*>(a.out)[size_t(row) * a.n + col] = P::from_float(v);
             }
         }
+        if (cg0 + batch < num_cg)
+            named_bar_sync(1, kConsumerThreads);
     }
 }
 
@@ -381,18 +575,36 @@ namespace w4
 namespace gemv
 {
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE>
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD>
 static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     using C = Cfg<BITS, MB>;
-    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE>;
-    size_t const fixed = C::RED_FLOATS * sizeof(float) + 64;
-    int slots = int((size_t(dev.max_smem_optin) - fixed) / (C::TILE_BYTES + 16));
+    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE, FOLD>;
+    Args args = a;
+    args.groups_per_panel = a.group_shift >= 31 ? 1 : C::KP >> a.group_shift;
+    args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
+    args.slot_bytes = C::TILE_BYTES + 2 * args.box_stride;
+    size_t const fixed = kRedBytes + 64;
+    int slots = int((size_t(dev.max_smem_optin) - fixed) / (args.slot_bytes + 16));
     if (slots < 2)
         return W4_ERR_CUDA;
     if (slots > 12)
         slots = 12;
-    size_t const smem = size_t(slots) * C::TILE_BYTES + fixed + size_t(slots) * 16;
+    args.num_slots = slots;
+    size_t const smem = size_t(slots) * args.slot_bytes + fixed + size_t(slots) * 16;
+
+    // Scale / zero tensors as 2-D maps [groups, n]; every tile fetches a box of its panel's group
+    // rows x kScaleBoxCols columns.
+    CUtensorMap tm_scales, tm_zeros;
+    uint64_t const groups = uint64_t(a.num_groups);
+    if (!make_tensor_map_2d(&tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.scales, uint64_t(a.n), groups,
+            uint64_t(a.n) * 2, kScaleBoxCols, uint32_t(args.groups_per_panel), CU_TENSOR_MAP_SWIZZLE_NONE))
+        return W4_ERR_CUDA;
+    tm_zeros = tm_scales;
+    if (HAS_ZERO
+        && !make_tensor_map_2d(&tm_zeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.zeros, uint64_t(a.n), groups,
+            uint64_t(a.n) * 2, kScaleBoxCols, uint32_t(args.groups_per_panel), CU_TENSOR_MAP_SWIZZLE_NONE))
+        return W4_ERR_CUDA;
 
     // The opt-in shared-memory limit is a per-function, per-device attribute: set it once.
     static bool configured[64] = {};
@@ -404,32 +616,36 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
         if (dev.device >= 0 && dev.device < 64)
             configured[dev.device] = true;
     }
-    Args args = a;
-    args.num_slots = slots;
     int const grid = args.num_rows < dev.num_sms ? args.num_rows : dev.num_sms;
-    kernel<<<grid, kThreads, smem, stream>>>(args);
+    kernel<<<grid, kThreads, smem, stream>>>(args, tm_scales, tm_zeros);
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
-template <typename T, int BITS, int MB>
+template <typename T, int BITS, int MB, bool FOLD>
 static int dispatch_flags(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     bool const z = a.zeros != nullptr, s = a.act_scale != nullptr;
     if (z && s)
-        return launch_one<T, BITS, MB, true, true>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, true, FOLD>(a, dev, stream);
     if (z)
-        return launch_one<T, BITS, MB, true, false>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, false, FOLD>(a, dev, stream);
     if (s)
-        return launch_one<T, BITS, MB, false, true>(a, dev, stream);
-    return launch_one<T, BITS, MB, false, false>(a, dev, stream);
+        return launch_one<T, BITS, MB, false, true, FOLD>(a, dev, stream);
+    return launch_one<T, BITS, MB, false, false, FOLD>(a, dev, stream);
 }
 
 template <typename T>
 static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev, cudaStream_t stream)
 {
     if (bits == 4)
-        return mb == 1 ? dispatch_flags<T, 4, 1>(a, dev, stream) : dispatch_flags<T, 4, 2>(a, dev, stream);
-    return mb == 1 ? dispatch_flags<T, 8, 1>(a, dev, stream) : dispatch_flags<T, 8, 2>(a, dev, stream);
+    {
+        // A warp unit spans 128 k for int4: the folded arithmetic needs one scale group per unit.
+        bool const fold = a.group_shift >= 7;
+        if (fold)
+            return mb == 1 ? dispatch_flags<T, 4, 1, true>(a, dev, stream) : dispatch_flags<T, 4, 2, true>(a, dev, stream);
+        return mb == 1 ? dispatch_flags<T, 4, 1, false>(a, dev, stream) : dispatch_flags<T, 4, 2, false>(a, dev, stream);
+    }
+    return mb == 1 ? dispatch_flags<T, 8, 1, true>(a, dev, stream) : dispatch_flags<T, 8, 2, true>(a, dev, stream);
 }
 
 } // namespace gemv
@@ -455,7 +671,8 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
         a.m = rows;
         a.n = p.n;
         a.k = p.k;
-        a.group = p.group_size ? p.group_size : p.k;
+        a.group_shift = p.group_size == 64 ? 6 : (p.group_size == 128 ? 7 : 31);
+        a.num_groups = p.group_size ? p.k / p.group_size : 1;
         a.num_rows = p.n / (p.weight_bits == 4 ? 4 : 2);
         int const mb = rows <= 8 ? 1 : 2;
         int const rc = p.act_dtype == W4_DTYPE_FP16 ? gemv::dispatch_bits<__half>(a, p.weight_bits, mb, dev, stream)
