@@ -37,6 +37,8 @@
 //    max|ref| bound this path is held to.
 // In both, the pre-quant scale product is rounded to T (utility.h:116) and alpha * acc + bias is
 // formed in fp32 (utility.h:256-266).
+#include <cstdlib>
+
 #include "w4_common.cuh"
 #include "w4_internal.h"
 #include "w4_tma.h"
@@ -134,6 +136,7 @@ struct Args
     int slot_bytes;       // tile bytes + scale/zero boxes, multiple of 128
     int groups_per_panel; // scale rows delivered with every tile (1 for per-channel)
     int box_stride;       // bytes between the scale box and the zero box (multiple of 128)
+    int depth;            // tiles kept in flight ahead of the one being consumed
 };
 
 // Shared flag: once any wait in the CTA timed out, every later wait returns at once.
@@ -150,6 +153,19 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     atomicExch(&g_device_status, kDeviceTimeout);
     return false;
 }
+
+#ifdef W4_DBG_TRACE
+// Debug build only: per-warp time stamps of CTA 0 (never compiled into the product library).
+__device__ long long g_trace[16 * 64];
+#define W4_STAMP(slot_)                                                                                                \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        if (blockIdx.x == 0 && lane == 0 && (slot_) < 64)                                                               \
+            g_trace[warp * 64 + (slot_)] = clock64();                                                                  \
+    } while (0)
+#else
+#define W4_STAMP(slot_)
+#endif
 
 __device__ __forceinline__ void prefetch_l2(void const* p)
 {
@@ -169,7 +185,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + size_t(a.num_slots) * a.slot_bytes);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(a.num_slots) * a.slot_bytes + kRedBytes);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(full_bar + a.num_slots);
+    uint64_t* empty_bar = full_bar + a.num_slots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + a.num_slots);
 
     int const tid = threadIdx.x;
     int const warp = tid >> 5, lane = tid & 31;
@@ -180,14 +197,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const num_cg = (r1 - r0 + C::RPG - 1) / C::RPG;
     int const num_panels = (a.k + C::KP - 1) / C::KP;
     size_t const row_bytes = size_t(2) * a.k;
+    // With a single k panel the rows of a column group are adjacent in memory as well: keep them
+    // adjacent in the slot so that one bulk copy moves the whole tile.
+    int const row_stride = num_panels == 1 ? int(row_bytes) : C::ROW_STRIDE;
 
-    int* done = const_cast<int*>(abort_flag) + 1; // per slot: warps that finished reading it
+    int* next_tile = const_cast<int*>(abort_flag) + 1; // first tile whose copies have not been started
     int const num_tiles = num_cg * num_panels;
 
-    // Starts the bulk copies of tile i (column group i / num_panels, k panel i % num_panels) into
-    // its ring slot. Called by one thread: thread 0 for the first num_slots tiles, afterwards by
-    // whichever warp was the last to finish reading the slot's previous tile, so nobody ever waits
-    // for a slot to drain and no warp is set aside as a producer.
+    // Starts the copies of tile i (column group i / num_panels, k panel i % num_panels) into its
+    // ring slot; called by one thread at a time (see try_issue).
     auto issue_tile = [&](int i, int slot)
     {
         int const cg = i / num_panels, panel = i - cg * num_panels;
@@ -199,8 +217,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_expect_tx(&full_bar[slot], bytes * rows + box_bytes * (HAS_ZERO ? 2 : 1));
         uint8_t* dst = ring + size_t(slot) * a.slot_bytes;
         uint8_t const* src = a.weight + size_t(row_first) * row_bytes + size_t(panel) * C::ROW_STRIDE;
-        for (int r = 0; r < rows; ++r)
-            bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
+        if (num_panels == 1)
+            bulk_g2s(dst, src, bytes * rows, &full_bar[slot]);
+        else
+            for (int r = 0; r < rows; ++r)
+                bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
         // The scale / zero rows of this panel for the group's columns travel with the tile, from
         // the 8-column boundary at or below the group's first column.
         int const col_aligned = (row_first * C::IL) & ~7;
@@ -210,19 +231,63 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(dst + C::TILE_BYTES + a.box_stride, &tm_zeros, col_aligned, grow, &full_bar[slot]);
     };
 
+    // Tile j may start once (a) tile j - depth has fully arrived, so that only `depth` tiles share
+    // the memory pipe and they land in order, early enough to overlap with the arithmetic (the
+    // copy engine serves all outstanding copies side by side: started together they would also all
+    // finish together, at the very end), and (b) every warp has released the tile that used the
+    // slot before. There is no producer warp: lane 0 of every warp calls this at each tile
+    // boundary and while it polls for data; the compare-and-swap picks one issuer per tile.
+    auto try_issue = [&]()
+    {
+        for (;;)
+        {
+            int const j = *const_cast<volatile int*>(next_tile);
+            if (j >= num_tiles)
+                return;
+            int const slot = j % a.num_slots, use = j / a.num_slots;
+            if (use > 0 && !mbar_test_wait(&empty_bar[slot], (use - 1) & 1))
+                return;
+            if (j >= a.depth)
+            {
+                int const jd = j - a.depth;
+                if (!mbar_test_wait(&full_bar[jd % a.num_slots], (jd / a.num_slots) & 1))
+                    return;
+            }
+            if (atomicCAS(next_tile, j, j + 1) == j)
+            {
+                if (use > 0)
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_tile(j, slot);
+            }
+        }
+    };
+
     if (tid == 0)
     {
         for (int s = 0; s < a.num_slots; ++s)
         {
             mbar_init(&full_bar[s], 1);
-            done[s] = 0;
+            mbar_init(&empty_bar[s], kWarps);
         }
         *abort_flag = 0;
+        *next_tile = 0;
         mbar_fence_init();
-        for (int i = 0; i < min(a.num_slots, num_tiles); ++i)
-            issue_tile(i, i);
     }
+    else if (tid == 32)
+    {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_scales) : "memory");
+        if (HAS_ZERO)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_zeros) : "memory");
+    }
+    W4_STAMP(0);
     __syncthreads();
+    W4_STAMP(1);
+    // Programmatic dependent launch: let the next kernel in the stream begin its own prologue as
+    // SMs free up. Everything up to the activation load touches only weights, scales and zeros,
+    // which no earlier kernel writes, so it may run ahead of the kernel before this one.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (tid == 0)
+        try_issue();
 
     // ---------------------------------------------------------------------- consumers
     int const g = lane >> 2, t = lane & 3;
@@ -232,8 +297,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // whole 128-byte line.
     int const colA = BITS == 4 ? 2 * g : g;
     int const colB = BITS == 4 ? 2 * g + 1 : 8 + g;
-    int const segA = (colA / C::IL) * C::ROW_STRIDE + (colA % C::IL) * (128 / C::IL);
-    int const segB = (colB / C::IL) * C::ROW_STRIDE + (colB % C::IL) * (128 / C::IL);
+    int const segA = (colA / C::IL) * row_stride + (colA % C::IL) * (128 / C::IL);
+    int const segB = (colB / C::IL) * row_stride + (colB % C::IL) * (128 / C::IL);
 
     T const* act = static_cast<T const*>(a.act);
     T const* act_scale = static_cast<T const*>(a.act_scale);
@@ -474,8 +539,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const per_cg = kWarps * MB * 4 * 8 * MT;
     int const batch = max(1, (kRedBytes / 4) / per_cg);
 
+    W4_STAMP(2);
+    // Activations (and, later, the output) belong to the preceding kernels: wait for them here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (num_cg > 0)
         load_act(0);
+    W4_STAMP(3);
 
     bool ok = true;
     int slot = 0, use = 0, tile_index = 0;
@@ -497,27 +566,41 @@ __global__ void __launch_bounds__(kThreads, 1)
                     load_act(panel);
 
                 if (ok)
-                    ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
-                uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
-#pragma unroll
-                for (int j = 0; j < C::UPW; ++j)
-                    process_unit(j, cg, tile);
-                // The last warp to finish with this slot refills it with the tile num_slots ahead.
-                __syncwarp();
-                if (lane == 0)
                 {
-                    __threadfence_block();
-                    if (atomicAdd(&done[slot], 1) == kWarps - 1)
+                    // poll for the tile; while it is not there, help start later tiles
+                    uint32_t polls = 0;
+                    while (!mbar_try_wait(&full_bar[slot], use & 1))
                     {
-                        done[slot] = 0;
-                        int const next = tile_index + a.num_slots;
-                        if (next < num_tiles)
+                        if (lane == 0)
+                            try_issue();
+                        if (++polls > kMaxWaitPolls || ((polls & 1023u) == 0 && *abort_flag))
                         {
-                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                            issue_tile(next, slot);
+                            ok = false;
+                            *abort_flag = 1;
+                            atomicExch(&g_device_status, kDeviceTimeout);
+                            break;
                         }
                     }
                 }
+                if (lane == 0)
+                    try_issue(); // this tile has arrived: the one `depth` ahead may start
+                uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
+                W4_STAMP(4 + 3 * tile_index);
+#ifndef W4_DBG_NOCOMPUTE
+#pragma unroll
+                for (int j = 0; j < C::UPW; ++j)
+                    process_unit(j, cg, tile);
+#endif
+                W4_STAMP(5 + 3 * tile_index);
+                __syncwarp();
+                W4_STAMP(43 + tile_index);
+                if (lane == 0)
+                {
+                    mbar_arrive(&empty_bar[slot]);
+                    W4_STAMP(50 + tile_index);
+                    try_issue();
+                }
+                W4_STAMP(6 + 3 * tile_index);
                 ++tile_index;
                 if (++slot == a.num_slots)
                 {
@@ -536,7 +619,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
 
         // Combine the 16 warps' partial sums in a fixed order and write this batch of columns.
+        W4_STAMP(40);
         named_bar_sync(1, kConsumerThreads);
+        W4_STAMP(41);
         constexpr int MPAD = 8 * MB;
         for (int o = tid; o < nb * 16 * MPAD; o += kConsumerThreads)
         {
@@ -561,6 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (cg0 + batch < num_cg)
             named_bar_sync(1, kConsumerThreads);
+        W4_STAMP(42);
     }
 }
 
@@ -591,6 +677,15 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     if (slots > 12)
         slots = 12;
     args.num_slots = slots;
+    // Tiles in flight ahead of the consumers: about 72 KB per SM covers the HBM latency-bandwidth
+    // product with margin. W4_GEMV_DEPTH overrides it (tuning aid).
+    static int const depth_override = []
+    {
+        char const* e = getenv("W4_GEMV_DEPTH");
+        return e ? atoi(e) : 0;
+    }();
+    int depth = depth_override > 0 ? depth_override : (72 * 1024 + args.slot_bytes / 2) / args.slot_bytes;
+    args.depth = depth < 1 ? 1 : (depth > slots - 1 ? slots - 1 : depth);
     size_t const smem = size_t(slots) * args.slot_bytes + fixed + size_t(slots) * 16;
 
     // Scale / zero tensors as 2-D maps [groups, n]; every tile fetches a box of its panel's group
@@ -617,7 +712,25 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
             configured[dev.device] = true;
     }
     int const grid = args.num_rows < dev.num_sms ? args.num_rows : dev.num_sms;
-    kernel<<<grid, kThreads, smem, stream>>>(args, tm_scales, tm_zeros);
+    // Launched as a programmatic dependent of whatever precedes it in the stream (the kernel
+    // orders itself with griddepcontrol.wait). W4_GEMV_PDL=0 turns the attribute off.
+    static bool const use_pdl = []
+    {
+        char const* e = getenv("W4_GEMV_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, args, tm_scales, tm_zeros) != cudaSuccess)
+        return W4_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
@@ -649,6 +762,13 @@ static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev,
 }
 
 } // namespace gemv
+
+#ifdef W4_DBG_TRACE
+extern "C" int w4_dbg_read_trace(long long* out)
+{
+    return cudaMemcpyFromSymbol(out, gemv::g_trace, sizeof(long long) * 16 * 64) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
 {
