@@ -19,8 +19,8 @@ static __device__ int g_device_status = 0;
 constexpr int kDeviceTimeout = -10; // == W4_ERR_DEVICE_TIMEOUT
 
 // Upper bound on polls of one mbarrier wait. One try_wait already blocks for a hardware-defined
-// interval, so this is seconds of wall time, far beyond any legitimate wait.
-constexpr uint32_t kMaxWaitPolls = 1u << 24;
+// interval, so this is on the order of a second, far beyond any legitimate wait.
+constexpr uint32_t kMaxWaitPolls = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(void const* p)
 {

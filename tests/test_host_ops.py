@@ -1,0 +1,143 @@
+"""CPU: the product's host-side code (C ABI of libw4gemm.so + the Python mirror of the reference's
+ops) against the oracle and the golden vectors; no kernel is launched here."""
+import ctypes
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tensorrt_llm_b200 as pkg
+from oracle import woq_oracle as o
+from tensorrt_llm_b200 import quantize
+from tensorrt_llm_b200._lib import W4GemmParams
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "quant_*.npz")))
+_DT = {"torch.float32": torch.float32, "torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16}
+_QT = {8: torch.int8, 4: torch.quint4x2}
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = open(os.path.join(os.path.dirname(__file__), "..", "include", "w4_gemm.h")).read()
+    import re
+    declared = set(re.findall(r"\b(w4_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/w4_gemm.h but not exported"
+    assert set(pkg._lib.EXPORTS) <= declared
+    assert lib.w4_gemm_version() >= 100
+    assert pkg._lib.status_string(0) == "ok" and "null" in pkg._lib.status_string(-1)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_host_ops_match_golden(path):
+    g = np.load(path)
+    w = torch.from_numpy(g["weight_f32"]).to(_DT[str(g["dtype"])])
+    for bits in (8, 4):
+        u, p, s = quantize._symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
+        assert np.array_equal(u.numpy(), g[f"unprocessed_int{bits}"])
+        assert np.array_equal(p.numpy(), g[f"processed_int{bits}"])
+        assert s.dtype == w.dtype and np.array_equal(s.to(torch.float32).numpy(), g[f"scales_int{bits}_f32"])
+        raw = torch.from_numpy(g[f"raw_int{bits}"])
+        got = quantize.preprocess_weights_for_mixed_gemm(raw, _QT[bits], torch.float16)
+        assert np.array_equal(got.numpy(), g[f"raw_processed_int{bits}"])
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("K,N", [(64, 64), (128, 448), (1024, 1024)])
+def test_host_ops_match_oracle(bits, K, N):
+    w = torch.randn(K, N, generator=torch.Generator().manual_seed(K + N)) * 0.02
+    got = quantize._symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
+    exp = o.symmetric_quantize(w, bits)
+    for a, b in zip(got, exp):
+        assert torch.equal(a, b)
+    p2, s2 = quantize.symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
+    assert torch.equal(p2, exp[1]) and torch.equal(s2, exp[2])
+
+
+def test_batched_weights():
+    w = torch.randn(3, 64, 64, generator=torch.Generator().manual_seed(0))
+    p, s = quantize.symmetric_quantize_last_axis_of_batched_matrix(w, torch.int8)
+    assert p.shape == (3, 64, 64) and s.shape == (3, 64)
+    for e in range(3):
+        assert torch.equal(p[e], o.symmetric_quantize(w[e], 8)[1])
+
+
+def test_torch_ops_registered():
+    import tensorrt_llm_b200.torch_ops  # noqa: F401
+    w = torch.randn(64, 64)
+    a = torch.ops.trtllm.symmetric_quantize_last_axis_of_batched_matrix(w, torch.quint4x2)
+    b = quantize.symmetric_quantize_last_axis_of_batched_matrix(w, torch.quint4x2)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    x = torch.randint(-8, 8, (4, 16), dtype=torch.int8)
+    packed = torch.ops.trtllm.pack_int8_tensor_to_packed_int4(x)
+    assert torch.equal(torch.ops.trtllm.unpack_int4_packed_tensor_to_int8(packed), x)
+    assert hasattr(torch.ops.trtllm, "weight_only_groupwise_quant_gemm")
+
+
+def test_error_behaviour_of_host_ops():
+    with pytest.raises(RuntimeError):
+        quantize.symmetric_quantize_last_axis_of_batched_matrix(torch.zeros(0, 64), torch.int8)
+    with pytest.raises(RuntimeError):
+        quantize.symmetric_quantize_last_axis_of_batched_matrix(torch.zeros(64, 64, dtype=torch.float64), torch.int8)
+    with pytest.raises(RuntimeError):
+        quantize.symmetric_quantize_last_axis_of_batched_matrix(torch.zeros(64, 64), torch.int32)
+    with pytest.raises(RuntimeError):
+        quantize.preprocess_weights_for_mixed_gemm(torch.zeros(64, 64), torch.int8)
+    with pytest.raises(RuntimeError):
+        quantize.pack_int8_tensor_to_packed_int4(torch.full((2, 2), 9, dtype=torch.int8))
+    with pytest.raises(pkg.W4Error):
+        quantize.preprocess_weights_for_mixed_gemm(torch.zeros(48, 64, dtype=torch.int8), torch.int8)
+
+
+def _params(**kw):
+    base = dict(act=16, weight=16, scales=16, out=16, alpha=1.0, m=1, n=128, k=128, group_size=128, weight_bits=4,
+                act_dtype=1, regime=1)
+    base.update(kw)
+    return W4GemmParams(**base)
+
+
+def test_launch_argument_validation(lib):
+    """w4_gemm_validate runs the launcher's checks without touching a device."""
+    v = lambda **kw: lib.w4_gemm_validate(ctypes.byref(_params(**kw)))
+    assert v() == 0
+    assert lib.w4_gemm_validate(None) == -1
+    assert v(act=0) == -1 and v(out=0) == -1
+    assert v(k=100) == -2 and v(n=100) == -2 and v(n=96, weight_bits=8) == 0 and v(n=96) == -2
+    assert v(group_size=32) == -3 and v(k=192, group_size=128) == -3 and v(k=192, group_size=64) == 0
+    assert v(act_dtype=5) == -4 and v(weight_bits=2) == -4
+    assert v(act=8) == -5 and v(zeros=4) == -5
+    assert v(regime=7) == -9
+    assert v(m=0, act=0, out=0) == 0  # empty batch: nothing to do, as the plugins return early
+    # tensor-core regime with a pre-quant scale needs the caller's workspace
+    need = lib.w4_gemm_workspace_bytes(512, 128, 128, 128, 4, 1, 1, 2)
+    assert need == 512 * 128 * 2
+    assert v(m=512, regime=2, act_scale=16) == -7
+    assert v(m=512, regime=2, act_scale=16, workspace=16, workspace_bytes=need) == 0
+    assert lib.w4_gemm_workspace_bytes(8, 128, 128, 128, 4, 1, 1, 1) == 0
+
+
+def test_regime_heuristic(lib):
+    for m in (1, 2, 4, 8, 16):
+        assert lib.w4_gemm_select_regime(m, 14336, 4096, 128, 4) == pkg.W4_REGIME_GEMV
+    for m in (256, 4096, 8192):
+        assert lib.w4_gemm_select_regime(m, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMM
+
+
+def test_plugin_mirror_fields_and_serialisation():
+    g = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_BF16, pkg.ZERO | pkg.PRE_QUANT_SCALE | pkg.BIAS, 128, 1.0)
+    assert (g.pre_quant_scale_idx, g.weight_idx, g.scales_idx, g.zeros_idx, g.bias_idx, g.nb_inputs) == (1, 2, 3, 4, 5, 6)
+    g2 = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.INT8_WEIGHT, 64)
+    assert (g2.weight_idx, g2.scales_idx, g2.zeros_idx, g2.bias_idx, g2.bits) == (1, 2, 2, 2, 8)
+    g.configure_plugin(1, 4096, 4096, 14336)
+    r = pkg.WeightOnlyGroupwiseQuantMatmulPlugin.deserialize(g.serialize())
+    assert (r.type_id, r.quant_algo, r.group_size, r.alpha, r.dims) == (g.type_id, g.quant_algo, 128, 1.0, g.dims)
+    assert g.get_workspace_size() == 4096 * 14336 * 2  # smoothed activations, as the reference sizes it
+    p = pkg.WeightOnlyQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.ops.WEIGHT_TYPE_INT4)
+    assert p.get_output_dimensions((2, 3, 64), (64, 32)) == (2, 3, 64)
+    assert p.supports_format_combination(1, [torch.float16, torch.int8, torch.float16, torch.float16])
+    with pytest.raises(RuntimeError):
+        pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.FP8_ALPHA, 128)
+    with pytest.raises(RuntimeError):
+        pkg.WeightOnlyQuantMatmulPlugin(0, 1)
