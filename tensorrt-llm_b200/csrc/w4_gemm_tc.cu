@@ -290,11 +290,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint16_t const* bias = static_cast<uint16_t const*>(a.bias);
         uint16_t* out = static_cast<uint16_t*>(a.out);
         int const gsh = a.group_shift >= 31 ? 30 : a.group_shift - 6; // log2(k steps per scale group)
-        // Column segment of this thread inside a stage's weight lines. int4: two 16-byte chunks;
-        // odd groups of four lanes read them in the opposite order so that a quarter-warp touches
-        // every bank once.
+        // Column segment of this thread inside a stage's weight lines (two or four 16-byte chunks).
         int const w_off = (n_local / IL) * 128 + (n_local % IL) * SEG;
-        int const swap = BITS == 4 ? ((lane >> 2) & 1) : 0;
 
         int s = 0, t = 0;
         uint32_t ph = 0, aph = 0, dph = 0;
@@ -333,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 uint4 raw[CHUNKS];
 #pragma unroll
                 for (int c = 0; c < CHUNKS; ++c)
-                    raw[c] = *reinterpret_cast<uint4 const*>(wsm + ((c ^ swap) * 16));
+                    raw[c] = *reinterpret_cast<uint4 const*>(wsm + c * 16);
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&bars->empty[s]);
@@ -362,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                             for (int p = 0; p < 4; ++p) // pair p of register j holds k = 2j + 8p (+1)
                                 v[j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
                         }
-                        tc_st16(a_addr + 16 * (c ^ swap), v);
+                        tc_st16(a_addr + 16 * c, v); // the TMEM address is warp-uniform
                     }
                 }
                 else

@@ -1,0 +1,145 @@
+"""Tensor-parallel weight-only linear layers, sharded the way the reference does it.
+
+* Column-parallel (QKV, gate/up): the output features N are split into ``tp_size`` contiguous
+  chunks (tensorrt_llm/layers/linear.py:340-343, tensorrt_llm/models/convert_utils.py:37-43 of
+  TensorRT-LLM); scales and zeros are split on N; activations are replicated; no communication
+  when the output is not gathered (tensorrt_llm/quantization/layers.py:1056-1058).
+* Row-parallel (o_proj, down): the input features K are split (layers/linear.py:466-468); scale
+  and zero *rows* are split with K; every rank produces a full [M, N] partial result and one
+  all-reduce (sum) over the TP group finishes it (quantization/layers.py:1185-1186,
+  cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407). The bias of a row-parallel layer
+  is added once, after the reduction.
+* Shards are cut BEFORE quantisation / the layout transform (convert_utils.py:70-88,
+  quantization/functional.py:881-889): per-channel scales of a K shard come from that shard's own
+  maximum and the interleaved layout is built per shard.
+
+One process per GPU; the collective is ``torch.distributed.all_reduce`` (NCCL over NVLink on GPUs,
+gloo in the CPU tests) on the tensor the GEMM wrote. ``matmul`` can be replaced (the CPU tests pass
+the oracle) so that the sharding logic is testable without a GPU.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Optional
+
+import torch
+
+from . import _lib, ops, quantize
+from .mapping import Mapping
+
+
+def split(v: torch.Tensor, tp_size: int, idx: int, dim: int = 0) -> torch.Tensor:
+    """Contiguous chunk ``idx`` of ``tp_size`` along ``dim`` (convert_utils.py:37-43)."""
+    if tp_size == 1:
+        return v
+    if v.shape[dim] % tp_size:
+        raise ValueError(f"dimension {dim} of size {v.shape[dim]} is not divisible by tp_size {tp_size}")
+    return torch.chunk(v, tp_size, dim=dim)[idx].contiguous()
+
+
+def _check_shard(k: int, n: int, bits: int, group_size: int):
+    if k % 64 or (n * bits // 8) % 32:
+        raise ValueError(f"shard [{k}, {n}] violates the layout's divisibility rules (k % 64, n*bits/8 % 32)")
+    if group_size and k % group_size:
+        raise ValueError(f"shard k={k} is not a multiple of the group size {group_size}")
+
+
+class _ShardedLinear:
+    """State shared by the two layer kinds: one rank's preprocessed weight, scales, zeros."""
+
+    def __init__(self, mapping: Mapping, bits: int, group_size: int, dtype: torch.dtype, device):
+        self.mapping, self.bits, self.group_size, self.dtype, self.device = mapping, bits, group_size, dtype, device
+        self.weight = self.scales = self.zeros = self.bias = self.pre_quant_scale = None
+        self.matmul: Optional[Callable] = None  # test hook; None = the CUDA op
+
+    def _load(self, q_shard, scales, zeros, bias, pre_quant_scale):
+        """q_shard: signed int8 [k_local, n_local] integers of this rank."""
+        k, n = q_shard.shape
+        _check_shard(k, n, self.bits, self.group_size)
+        packed = quantize.pack_int8_tensor_to_packed_int4(q_shard.contiguous()) if self.bits == 4 else q_shard
+        qt = torch.quint4x2 if self.bits == 4 else torch.int8
+        self.q = q_shard  # kept for the test hook only
+        self.weight = quantize.preprocess_weights_for_mixed_gemm(packed.contiguous(), qt, torch.float16).to(self.device)
+        mv = lambda t: None if t is None else t.to(self.dtype).contiguous().to(self.device)
+        self.scales, self.zeros, self.bias, self.pre_quant_scale = mv(scales), mv(zeros), mv(bias), mv(pre_quant_scale)
+        self.k_local, self.n_local = k, n
+
+    def _gemm(self, x: torch.Tensor, with_bias: bool) -> torch.Tensor:
+        bias = self.bias if with_bias else None
+        if self.matmul is not None:
+            return self.matmul(self, x, bias)
+        if self.group_size == 0:
+            return ops.weight_only_quant_matmul(x, self.weight, self.scales, 1 if self.bits == 8 else 2)
+        algo = (_lib.INT8_WEIGHT if self.bits == 8 else 0) | (_lib.ZERO if self.zeros is not None else 0) \
+            | (_lib.BIAS if bias is not None else 0) | (_lib.PRE_QUANT_SCALE if self.pre_quant_scale is not None else 0)
+        return ops.weight_only_groupwise_quant_matmul(x, self.pre_quant_scale, self.weight, self.scales, self.zeros,
+                                                      bias, 1.0, algo, self.group_size)
+
+
+class WeightOnlyColumnLinear(_ShardedLinear):
+    """y_local[.., N/tp] = x[.., K] @ W[:, chunk]; no communication (gather_output = False)."""
+
+    @classmethod
+    def from_quantized(cls, mapping, q, scales, zeros=None, bias=None, pre_quant_scale=None, *, bits=4,
+                       group_size=128, dtype=torch.bfloat16, device="cpu"):
+        """q: signed int8 [K, N]; scales/zeros: [K/G, N] (or [N] for group_size 0); bias [N]."""
+        self = cls(mapping, bits, group_size, dtype, device)
+        tp, r = mapping.tp_size, mapping.tp_rank
+        last = lambda t: None if t is None else split(t, tp, r, dim=t.dim() - 1)
+        self._load(split(q, tp, r, dim=1), last(scales), last(zeros), last(bias), pre_quant_scale)
+        return self
+
+    @classmethod
+    def from_float(cls, mapping, weight, *, bits=8, dtype=torch.float16, device="cpu"):
+        """Per-channel: weight fp [K, N]; the N chunk is cut first, then quantised with its own scales."""
+        self = cls(mapping, bits, 0, dtype, device)
+        shard = split(weight, mapping.tp_size, mapping.tp_rank, dim=1)
+        qt = torch.quint4x2 if bits == 4 else torch.int8
+        u, _, s = quantize._symmetric_quantize_last_axis_of_batched_matrix(shard.contiguous(), qt)
+        self._load(quantize.unpack_int4_packed_tensor_to_int8(u) if bits == 4 else u, s, None, None, None)
+        return self
+
+    def forward(self, x):
+        return self._gemm(x, with_bias=True)
+
+    __call__ = forward
+
+
+class WeightOnlyRowLinear(_ShardedLinear):
+    """y[.., N] = all_reduce_sum_over_tp( x_local[.., K/tp] @ W[chunk, :] ) (+ bias once)."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.group = None  # torch.distributed process group of mapping.tp_group
+
+    @classmethod
+    def from_quantized(cls, mapping, q, scales, zeros=None, bias=None, pre_quant_scale=None, *, bits=4,
+                       group_size=128, dtype=torch.bfloat16, device="cpu", group=None):
+        self = cls(mapping, bits, group_size, dtype, device)
+        tp, r = mapping.tp_size, mapping.tp_rank
+        rows = lambda t: None if t is None else (t if group_size == 0 else split(t, tp, r, dim=0))
+        ps = None if pre_quant_scale is None else split(pre_quant_scale.reshape(-1), tp, r, dim=0)
+        self._load(split(q, tp, r, dim=0), rows(scales), rows(zeros), bias, ps)
+        self.group = group
+        return self
+
+    @classmethod
+    def from_float(cls, mapping, weight, *, bits=8, dtype=torch.float16, device="cpu", group=None):
+        self = cls(mapping, bits, 0, dtype, device)
+        shard = split(weight, mapping.tp_size, mapping.tp_rank, dim=0)
+        qt = torch.quint4x2 if bits == 4 else torch.int8
+        u, _, s = quantize._symmetric_quantize_last_axis_of_batched_matrix(shard.contiguous(), qt)
+        self._load(quantize.unpack_int4_packed_tensor_to_int8(u) if bits == 4 else u, s, None, None, None)
+        self.group = group
+        return self
+
+    def forward(self, x_local, all_reduce: bool = True):
+        y = self._gemm(x_local, with_bias=False)
+        if all_reduce and self.mapping.tp_size > 1:
+            import torch.distributed as dist
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
+
+    __call__ = forward

@@ -1,0 +1,113 @@
+"""CPU: tensor-parallel sharding logic. Rank math against the reference's expectations
+(tests/test_mapping.py:22-50 of TensorRT-LLM) and the column/row-parallel layers run as two gloo
+ranks, with the CPU oracle standing in for the GPU kernel."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import woq_oracle as oracle
+from tensorrt_llm_b200 import tp
+from tensorrt_llm_b200.mapping import Mapping
+
+
+def test_mapping_groups_tp2_pp2_cp2():
+    m = Mapping(world_size=8, rank=0, tp_size=2, pp_size=2, cp_size=2)
+    assert m.tp_groups == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert m.pp_groups == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert m.cp_groups == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    m = Mapping(world_size=8, rank=6, tp_size=2, pp_size=2, cp_size=2)
+    assert (m.tp_rank, m.cp_rank, m.pp_rank) == (0, 1, 1)
+    assert m.tp_group == [6, 7] and m.pp_group == [2, 6] and m.cp_group == [4, 6]
+
+
+def test_mapping_tp8_and_errors():
+    for r in range(8):
+        m = Mapping(world_size=8, rank=r, tp_size=8)
+        assert m.tp_rank == r and m.tp_group == list(range(8)) and m.pp_group == [r]
+    m = Mapping(world_size=8, rank=5, tp_size=4, pp_size=2)
+    assert m.tp_group == [4, 5, 6, 7] and m.pp_group == [1, 5] and m.pp_rank == 1 and m.is_last_pp_rank()
+    with pytest.raises(ValueError):
+        Mapping(world_size=8, rank=0, tp_size=3)
+    with pytest.raises(ValueError):
+        Mapping(world_size=4, rank=4, tp_size=4)
+
+
+def test_split_and_shard_rules():
+    x = torch.arange(24).reshape(4, 6)
+    assert torch.equal(tp.split(x, 2, 1, dim=0), x[2:]) and torch.equal(tp.split(x, 3, 0, dim=1), x[:, :2])
+    with pytest.raises(ValueError):
+        tp.split(x, 4, 0, dim=1)
+    q = torch.zeros(192, 128, dtype=torch.int8)
+    with pytest.raises(ValueError):  # 96-row K shard is not a multiple of the 64-wide k tile
+        tp.WeightOnlyRowLinear.from_quantized(Mapping(2, 0, tp_size=2), q, torch.ones(3, 128), bits=4, group_size=64)
+
+
+def _oracle_matmul(layer, x, bias):
+    return oracle.kernel_rounding_ref(x, layer.q, layer.scales.cpu(), zeros=None if layer.zeros is None else
+                                      layer.zeros.cpu(), bias=bias, pre_quant_scale=layer.pre_quant_scale,
+                                      group_size=layer.group_size)
+
+
+def _worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mapping = Mapping(world_size=world, rank=rank, tp_size=world)
+        g = torch.Generator().manual_seed(0)  # same full problem on every rank
+        K, N, M, G = 256, 256, 3, 64
+        q = torch.randint(-8, 8, (K, N), dtype=torch.int8, generator=g)
+        scales = (torch.rand(K // G, N, generator=g) * 0.02 + 0.001).to(torch.bfloat16)
+        zeros = (torch.rand(K // G, N, generator=g) * 0.2 - 0.1).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g).to(torch.bfloat16)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        full = oracle.kernel_rounding_ref(x, q, scales, zeros=zeros, bias=bias, group_size=G)
+
+        col = tp.WeightOnlyColumnLinear.from_quantized(mapping, q, scales, zeros, bias, bits=4, group_size=G)
+        col.matmul = _oracle_matmul
+        y_col = col(x)
+        assert y_col.shape == (M, N // world)
+        exp_col = full[:, rank * (N // world):(rank + 1) * (N // world)]
+        assert torch.equal(y_col, exp_col), "column-parallel shard differs from the matching slice"
+
+        row = tp.WeightOnlyRowLinear.from_quantized(mapping, q, scales, zeros, bias, bits=4, group_size=G)
+        row.matmul = _oracle_matmul
+        x_local = tp.split(x, world, rank, dim=1)
+        y_row = row(x_local)
+        err = float((y_row.float() - full.float()).abs().max())
+        assert err <= oracle.tolerance(full), f"row-parallel result off by {err}"
+        # every rank holds the same reduced tensor
+        gathered = [torch.empty_like(y_row) for _ in range(world)]
+        dist.all_gather(gathered, y_row)
+        assert all(torch.equal(gathered[0], t) for t in gathered)
+
+        # per-channel: a K shard is quantised with its own scales
+        w = torch.randn(K, N, generator=g) * 0.02
+        rowf = tp.WeightOnlyRowLinear.from_float(mapping, w, bits=8, dtype=torch.float16)
+        u_ref, _, s_ref = oracle.symmetric_quantize(tp.split(w, world, rank, dim=0).contiguous(), 8)
+        assert torch.equal(rowf.q, u_ref) and torch.equal(rowf.scales, s_ref.to(torch.float16))
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_and_row_parallel_two_ranks():
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29500 + (os.getpid() % 500)
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_rank_that_never_joins_times_out():
+    """Failure on the host side: a rendezvous that a rank never joins ends with an error after the
+    timeout instead of hanging."""
+    from datetime import timedelta
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(29400 + (os.getpid() % 90))
+    with pytest.raises(Exception):
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=timedelta(seconds=2))
+    if dist.is_initialized():
+        dist.destroy_process_group()
