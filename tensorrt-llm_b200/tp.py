@@ -143,3 +143,77 @@ class WeightOnlyRowLinear(_ShardedLinear):
         return y
 
     __call__ = forward
+
+
+# ------------------------------------------------------------------------------------------------
+# Measurement helper: the Llama-3-70B linear set under tensor parallelism
+# ------------------------------------------------------------------------------------------------
+LLAMA70B_LAYERS = (  # name, K, N, parallel kind
+    ("qkv", 8192, 10240, "column"),
+    ("gate_up", 8192, 57344, "column"),
+    ("o_proj", 8192, 8192, "row"),
+    ("down", 28672, 8192, "row"),
+)
+
+
+def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2048), reps=20,
+                             group_size=128):
+    """Times every linear of one Llama-3-70B layer at tp = world size: W4A16 group-128 with zeros,
+    bf16, seeded random shard contents (random bytes are what the layout of random int4 weights
+    is). Column-parallel layers: the local GEMM only. Row-parallel layers: local GEMM, then the
+    NCCL all-reduce of the [M, 8192] partial sums, each timed with CUDA events (max over ranks).
+    Between repetitions a buffer larger than the L2 is written so that weights stream from HBM."""
+    import torch.distributed as dist
+
+    g = torch.Generator(device=device).manual_seed(3 + rank)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    out = {}
+    for name, K, N, kind in LLAMA70B_LAYERS:
+        k_loc, n_loc = (K, N // world) if kind == "column" else (K // world, N)
+        _check_shard(k_loc, n_loc, 4, group_size)
+        w = torch.randint(0, 256, (k_loc, n_loc // 2), dtype=torch.uint8, device=device, generator=g).view(torch.int8)
+        s = (torch.rand((k_loc // group_size, n_loc), device=device, generator=g) * 0.019 + 0.001).to(torch.bfloat16)
+        z = (torch.rand((k_loc // group_size, n_loc), device=device, generator=g) * 0.2 - 0.1).to(torch.bfloat16)
+        for m in ms:
+            x = torch.randn((m, k_loc), device=device, generator=g).to(torch.bfloat16)
+            y = torch.empty((m, n_loc), dtype=torch.bfloat16, device=device)
+            ws_bytes = ops.workspace_bytes(m, n_loc, k_loc, group_size, 4, torch.bfloat16, False)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device) if ws_bytes else None
+
+            def gemm():
+                ops.gemm_raw(x, w, s, y, n=n_loc, k=k_loc, weight_bits=4, group_size=group_size, zeros=z,
+                             workspace=ws)
+
+            try:
+                gemm()
+            except _lib.W4Error as e:
+                out[f"{name}_m{m}"] = {"unavailable": str(e)}
+                continue
+            t_gemm, t_ar = [], []
+            for _ in range(reps):
+                flush.zero_()
+                barrier()
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record()
+                gemm()
+                e1.record()
+                if kind == "row" and world > 1:
+                    dist.all_reduce(y, op=dist.ReduceOp.SUM)
+                e2.record()
+                torch.cuda.synchronize()
+                t_gemm.append(e0.elapsed_time(e1))
+                t_ar.append(e1.elapsed_time(e2))
+            t_gemm.sort()
+            t_ar.sort()
+            gemm_us = max_over_ranks(t_gemm[len(t_gemm) // 2] * 1e3)
+            ar_us = max_over_ranks(t_ar[len(t_ar) // 2] * 1e3) if kind == "row" and world > 1 else 0.0
+            nbytes = k_loc * n_loc // 2 + 2 * (k_loc // group_size) * n_loc * 2 + m * k_loc * 2 + m * n_loc * 2
+            flops = 2.0 * m * n_loc * k_loc
+            out[f"{name}_m{m}"] = {
+                "kind": kind, "k_local": k_loc, "n_local": n_loc, "gemm_us": gemm_us, "allreduce_us": ar_us,
+                "allreduce_bytes": m * n_loc * 2 if kind == "row" and world > 1 else 0,
+                "per_gpu_GB/s": nbytes / gemm_us / 1e3, "per_gpu_TFLOP/s": flops / gemm_us / 1e6,
+                "regime": "gemv" if ops.select_regime(m, n_loc, k_loc, group_size, 4) == _lib.W4_REGIME_GEMV else "gemm",
+            }
+    del flush
+    return out
