@@ -53,7 +53,8 @@ extern "C"
         W4_ERR_WORKSPACE = -7,      /* workspace missing or smaller than w4_gemm_workspace_bytes() */
         W4_ERR_CUDA = -8,           /* a CUDA runtime call failed; see cudaGetLastError() */
         W4_ERR_BAD_REGIME = -9,     /* regime not valid for this shape */
-        W4_ERR_DEVICE_TIMEOUT = -10 /* a bounded device-side wait expired (reported by w4_gemm_device_status) */
+        W4_ERR_DEVICE_TIMEOUT = -10, /* a bounded device-side wait expired (reported by w4_gemm_device_status) */
+        W4_ERR_STATIC_SCRATCH = -11  /* problem too large for w4_gemm_launch_static_scratch's built-in scratch */
     } W4Status;
 
     /* Activation / scale / output element type (one type for all of them, as in the plugins). */
@@ -136,6 +137,31 @@ extern "C"
     /* Reads and clears the device-side status word of the current device (synchronises the
      * device). 0, or W4_ERR_DEVICE_TIMEOUT when a kernel gave up a bounded wait. */
     int w4_gemm_device_status(void);
+
+/* Size of the scratch array built into the library for w4_gemm_launch_static_scratch. */
+#define W4_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+
+    /*
+     * Same contract as w4_gemm_launch, for callers that can neither allocate device memory nor
+     * pass a workspace (allocation-free regions of a serving loop, plugin hosts that granted no
+     * workspace, processes in which another component owns the allocator). It always runs the
+     * tensor-core kernel and keeps that kernel's only scratch - the activations multiplied by the
+     * AWQ pre-quant scale, m * k * 2 bytes - in a W4_STATIC_SCRATCH_BYTES (8 MiB) array that is
+     * part of the library image. This entry point has no counterpart in the reference.
+     *   - p->workspace / p->workspace_bytes are ignored; nothing is allocated or freed, here or
+     *     in any library it calls.
+     *   - m * k * 2 > W4_STATIC_SCRATCH_BYTES with act_scale set returns W4_ERR_STATIC_SCRATCH
+     *     (for example m = 512, k = 8192 still fits; m = 4096, k = 4096 does not).
+     *   - The first call on each device resolves the array's device address; make that call
+     *     before starting any stream capture on that device.
+     *   - All calls on a device share the one array, which still holds the previous call's data;
+     *     the kernel overwrites everything it reads, so nothing needs clearing, but two calls
+     *     whose execution overlaps on the GPU (different streams) would race on it: serialise
+     *     them.
+     *   - Every GPU that loads the library gives up 8 MiB for the array until the process exits.
+     */
+    int w4_gemm_launch_static_scratch(const W4GemmParams* p, void* stream);
+    size_t w4_gemm_static_scratch_bytes(void);
 
     /* ---- host-side (CPU) weight preparation, bit-exact with the reference ---- */
 

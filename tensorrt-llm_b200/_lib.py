@@ -20,7 +20,7 @@ BIAS, ZERO, PRE_QUANT_SCALE, FP8_ALPHA, INT8_WEIGHT = 1, 2, 4, 8, 16
 EXPORTS = (
     "w4_gemm_version", "w4_status_string", "w4_gemm_validate", "w4_gemm_launch", "w4_gemm_workspace_bytes",
     "w4_gemm_select_regime", "w4_gemm_device_status", "w4_symmetric_quantize", "w4_preprocess_weights",
-    "w4_pack_int4", "w4_unpack_int4",
+    "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
 )
 
 
@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
         l.w4_status_string.argtypes = [ctypes.c_int]
         l.w4_gemm_validate.argtypes = [ctypes.POINTER(W4GemmParams)]
         l.w4_gemm_launch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
+        l.w4_gemm_launch_static_scratch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
+        l.w4_gemm_static_scratch_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 8
         l.w4_gemm_select_regime.argtypes = [ctypes.c_int] * 5

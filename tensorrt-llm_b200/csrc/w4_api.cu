@@ -118,6 +118,7 @@ extern "C"
         case W4_ERR_CUDA: return "CUDA runtime error";
         case W4_ERR_BAD_REGIME: return "regime not valid for this problem";
         case W4_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        case W4_ERR_STATIC_SCRATCH: return "m * k * 2 bytes exceed the built-in scratch of w4_gemm_launch_static_scratch";
         default: return "unknown status";
         }
     }

@@ -3,3 +3,4 @@
 #include "w4_gemv.cu"
 #include "w4_gemm_tc.cu"
 #include "w4_api.cu"
+#include "w4_static_scratch.cu"
