@@ -15,12 +15,13 @@
 // of W times up to 256 rows of the activation matrix, so each weight is converted once per 256
 // activation rows.
 //
-// Warp roles (192 threads, one CTA per SM, persistent over tiles):
+// Warp roles (320 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer: activation tile [BM x 64] + packed weight tile per k step
 //   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits to mbarriers
-//   warps 2..5  conversion: shared memory -> registers -> exact int->T conversion, scale/zero ->
-//               tcgen05.st into the TMEM ring of A stages; after the last k step the same warps
-//               run the epilogue (tcgen05.ld, alpha/bias, convert, store).
+//   warps 2..9  conversion, two warps per TMEM lane quadrant taking alternate k steps: shared memory
+//               -> registers -> exact int->T conversion, scale/zero -> tcgen05.st into the TMEM ring
+//               of A stages; after the last k step the same warps run the epilogue (tcgen05.ld,
+//               alpha/bias, convert, store), each on its share of the accumulator columns.
 // All waits are bounded; a timeout sets the device status word and the CTA drains and exits.
 #include <type_traits>
 
@@ -38,7 +39,8 @@ constexpr int BK = 64;        // k per pipeline step (one 128-byte swizzle span 
 constexpr int kAStages = 4;   // TMEM ring of converted-weight stages (32 columns each)
 constexpr int kACol0 = 256;   // first TMEM column of that ring; the accumulator uses [0, 256)
 constexpr int kTmemCols = 512;
-constexpr int kThreads = 192;
+constexpr int kConvGroups = 2;   // groups of 4 conversion warps; group g converts k steps with ks % 2 == g
+constexpr int kThreads = 64 + 128 * kConvGroups;
 constexpr int kMaxStages = 8;
 
 struct Args
@@ -65,6 +67,28 @@ struct __align__(8) Barriers
     uint32_t tmem_base;
     int abort_flag;
 };
+
+#ifdef W4_DBG_TRACE
+// Debug build only: cycles CTA 0 spent in each kind of wait, per role.
+__device__ long long g_tc_trace[64];
+#define W4_TC_TIMED(slot_, expr_)                                                                                     \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        long long t0_ = clock64();                                                                                     \
+        expr_;                                                                                                         \
+        dbg_acc[(slot_) & 3] += clock64() - t0_;                                                                       \
+    } while (0)
+#define W4_TC_FLUSH(base_)                                                                                             \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        if (blockIdx.x == 0 && lane == 0)                                                                              \
+            for (int i_ = 0; i_ < 4; ++i_)                                                                             \
+                g_tc_trace[(base_) + i_] = dbg_acc[i_];                                                                \
+    } while (0)
+#else
+#define W4_TC_TIMED(slot_, expr_) expr_
+#define W4_TC_FLUSH(base_)
+#endif
 
 __device__ __forceinline__ bool wait_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
@@ -169,6 +193,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile int* abort_flag = &bars->abort_flag;
 
     int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef W4_DBG_TRACE
+    long long dbg_acc[4] = {0, 0, 0, 0};
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+    {
+        for (int i = 0; i < 32; ++i)
+            g_tc_trace[i] = 0;
+        g_tc_trace[33] = clock64();
+    }
+    __syncthreads();
+#endif
     int const num_tiles = a.tiles_n * a.tiles_m;
     int const ksteps = a.k / BK;
 
@@ -185,7 +219,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&bars->a_empty[s], 1);
         }
         mbar_init(&bars->d_full, 1);
-        mbar_init(&bars->d_empty, 4);
+        mbar_init(&bars->d_empty, 4 * kConvGroups);
         bars->abort_flag = 0;
         mbar_fence_init();
     }
@@ -212,17 +246,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+#ifdef W4_DBG_MMA_ONLY
+            ok = false; // timing experiment: nothing is loaded
+#endif
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
             {
                 int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
                 for (int ks = 0; ks < ksteps; ++ks)
                 {
-                    if (!(ok = wait_flag(&bars->empty[s], ph ^ 1, abort_flag)))
+                    W4_TC_TIMED(0, ok = wait_flag(&bars->empty[s], ph ^ 1, abort_flag));
+                    if (!ok)
                         break;
                     uint8_t* stage = smem + size_t(s) * STAGE_BYTES;
-                    mbar_expect_tx(&bars->full[s], STAGE_BYTES);
-                    tma_load_2d(stage, &tm_act, ks * BK, tm * BM, &bars->full[s]);
-                    tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), &bars->full[s]);
+#ifdef W4_DBG_HALF_ACT
+                    // timing experiment only (wrong results): fetch the activation tile on even steps only
+                    if (ks & 1)
+                    {
+                        mbar_expect_tx(&bars->full[s], W_BYTES);
+                        tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), &bars->full[s]);
+                    }
+                    else
+#endif
+                    {
+                        mbar_expect_tx(&bars->full[s], STAGE_BYTES);
+                        tma_load_2d(stage, &tm_act, ks * BK, tm * BM, &bars->full[s]);
+                        tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), &bars->full[s]);
+                    }
                     if (++s == a.num_stages)
                     {
                         s = 0;
@@ -244,17 +293,22 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 if (it > 0)
                 {
-                    if (!(ok = wait_flag(&bars->d_empty, dph, abort_flag)))
+                    W4_TC_TIMED(3, ok = wait_flag(&bars->d_empty, dph, abort_flag));
+                    if (!ok)
                         break;
                     dph ^= 1;
                     tc_fence_after();
                 }
                 for (int ks = 0; ks < ksteps; ++ks)
                 {
-                    if (!(ok = wait_flag(&bars->full[s], ph, abort_flag)))
+#ifndef W4_DBG_MMA_ONLY
+                    W4_TC_TIMED(1, ok = wait_flag(&bars->full[s], ph, abort_flag));
+                    if (!ok)
                         break;
-                    if (!(ok = wait_flag(&bars->a_full[t], aph, abort_flag)))
+                    W4_TC_TIMED(2, ok = wait_flag(&bars->a_full[t], aph, abort_flag));
+                    if (!ok)
                         break;
+#endif
                     tc_fence_after();
                     uint32_t const b_addr = smem_u32(smem + size_t(s) * STAGE_BYTES);
 #pragma unroll
@@ -283,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
         // ------------------------------------------------------------------ conversion + epilogue
         int const quad = warp & 3;             // TMEM lane quadrant this warp may touch
+        int const cgroup = (warp - 2) >> 2;    // which k steps this warp converts
         int const n_local = quad * 32 + lane;  // weight column inside the tile = TMEM lane
         uint32_t const lane_addr = tmem + (uint32_t(quad * 32) << 16);
         uint16_t const* scales = static_cast<uint16_t const*>(a.scales);
@@ -308,7 +363,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (HAS_ZERO)
                     z2_next = zeros[n];
             }
+#ifdef W4_DBG_MMA_ONLY
+            for (int ks = 0; ks < 0; ++ks)
+#else
             for (int ks = 0; ks < ksteps; ++ks)
+#endif
             {
                 if ((ks & ((1 << gsh) - 1)) == 0)
                 {
@@ -323,74 +382,79 @@ __global__ void __launch_bounds__(kThreads, 1)
                             z2_next = zeros[size_t(gnext) * a.n + n];
                     }
                 }
-                if (!(ok = wait_flag(&bars->full[s], ph, abort_flag)))
-                    break;
-                uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
-                constexpr int CHUNKS = SEG / 16; // 2 (int4) or 4 (int8)
-                uint4 raw[CHUNKS];
-#pragma unroll
-                for (int c = 0; c < CHUNKS; ++c)
-                    raw[c] = *reinterpret_cast<uint4 const*>(wsm + c * 16);
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&bars->empty[s]);
+                if ((ks % kConvGroups) == cgroup)
+                {
+                    W4_TC_TIMED(4 + 4 * quad, ok = wait_flag(&bars->full[s], ph, abort_flag));
+                    if (!ok)
+                        break;
+                    uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
+                    constexpr int CHUNKS = SEG / 16; // 2 (int4) or 4 (int8)
+                    uint4 raw[CHUNKS];
+    #pragma unroll
+                    for (int c = 0; c < CHUNKS; ++c)
+                        raw[c] = *reinterpret_cast<uint4 const*>(wsm + c * 16);
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&bars->empty[s]);
+                    W4_TC_TIMED(5 + 4 * quad, ok = wait_flag(&bars->a_empty[t], aph ^ 1, abort_flag));
+                    if (!ok)
+                        break;
+                    tc_fence_after();
+                    uint32_t const a_addr = lane_addr + kACol0 + t * 32;
+                    if (BITS == 4)
+                    {
+    #pragma unroll
+                        for (int c = 0; c < 2; ++c)
+                        {
+                            uint32_t const r[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+                            uint32_t v[16];
+    #pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                            {
+                                uint32_t q[4];
+                                cvt_int4x8<T>(r[j], q);
+    #pragma unroll
+                                for (int p = 0; p < 4; ++p) // pair p of register j holds k = 2j + 8p (+1)
+                                    v[j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+                            }
+                            tc_st16(a_addr + 16 * c, v); // the TMEM address is warp-uniform
+                        }
+                    }
+                    else
+                    {
+    #pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                        {
+                            uint32_t v[16];
+    #pragma unroll
+                            for (int cc = 0; cc < 2; ++cc)
+                            {
+                                uint4 const x = raw[2 * h + cc];
+                                uint32_t const r[4] = {x.x, x.y, x.z, x.w};
+    #pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                {
+                                    uint32_t q[2];
+                                    cvt_int8x4<T>(r[j], q);
+    #pragma unroll
+                                    for (int p = 0; p < 2; ++p) // pair p of register j holds k = 2j + 8p (+1)
+                                        v[8 * cc + j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+                                }
+                            }
+                            tc_st16(a_addr + 16 * h, v);
+                        }
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&bars->a_full[t]);
+                }
                 if (++s == a.num_stages)
                 {
                     s = 0;
                     ph ^= 1;
                 }
-                if (!(ok = wait_flag(&bars->a_empty[t], aph ^ 1, abort_flag)))
-                    break;
-                tc_fence_after();
-                uint32_t const a_addr = lane_addr + kACol0 + t * 32;
-                if (BITS == 4)
-                {
-#pragma unroll
-                    for (int c = 0; c < 2; ++c)
-                    {
-                        uint32_t const r[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-                        uint32_t v[16];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                        {
-                            uint32_t q[4];
-                            cvt_int4x8<T>(r[j], q);
-#pragma unroll
-                            for (int p = 0; p < 4; ++p) // pair p of register j holds k = 2j + 8p (+1)
-                                v[j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
-                        }
-                        tc_st16(a_addr + 16 * c, v); // the TMEM address is warp-uniform
-                    }
-                }
-                else
-                {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                    {
-                        uint32_t v[16];
-#pragma unroll
-                        for (int cc = 0; cc < 2; ++cc)
-                        {
-                            uint4 const x = raw[2 * h + cc];
-                            uint32_t const r[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                            {
-                                uint32_t q[2];
-                                cvt_int8x4<T>(r[j], q);
-#pragma unroll
-                                for (int p = 0; p < 2; ++p) // pair p of register j holds k = 2j + 8p (+1)
-                                    v[8 * cc + j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
-                            }
-                        }
-                        tc_st16(a_addr + 16 * h, v);
-                    }
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&bars->a_full[t]);
                 if (++t == kAStages)
                 {
                     t = 0;
@@ -401,14 +465,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
 
             // ---- epilogue: this thread owns output column n for all BM rows of the tile
-            if (!(ok = wait_flag(&bars->d_full, dph, abort_flag)))
+            W4_TC_TIMED(6 + 4 * quad, ok = wait_flag(&bars->d_full, dph, abort_flag));
+            if (!ok)
                 break;
             dph ^= 1;
             tc_fence_after();
             float const bias_f = (bias && n_ok) ? P::to_float(bias[n]) : 0.f;
             int const m0 = tm * BM;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BM; c0 += 32)
+            for (int c0 = cgroup * 32; c0 < BM; c0 += 32 * kConvGroups)
             {
                 if (m0 + c0 >= a.m)
                     break; // warp-uniform
@@ -432,6 +497,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     }
 
+#ifdef W4_DBG_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        g_tc_trace[32] = clock64();
+#endif
+    if (warp == 0)
+        W4_TC_FLUSH(40);
+    else if (warp == 1)
+        W4_TC_FLUSH(0);
+    else if (warp < 6)
+        W4_TC_FLUSH(4 + 4 * (warp & 3));
     // Teardown: everyone meets here (also after a timeout), then the allocating warp frees TMEM.
     tc_fence_before();
     __syncthreads();
@@ -519,6 +594,13 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 }
 
 } // namespace tc
+
+#ifdef W4_DBG_TRACE
+extern "C" int w4_dbg_read_tc_trace(long long* out)
+{
+    return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale)
 {
