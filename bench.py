@@ -175,11 +175,14 @@ def decode_runner(pkg, p, sets, m, device):
     act = p["act"][:m].contiguous().to(device)
     ps = p["ps"].to(device)
     out = torch.empty((m, C2["n"]), dtype=torch.bfloat16, device=device)
+    # the regime is chosen by the library; the tensor-core kernel wants scratch for the pre-quant scale
+    ws_bytes = ops.workspace_bytes(m, C2["n"], C2["k"], 128, 4, torch.bfloat16, True)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device) if ws_bytes else None
 
     def fn(i):
         w, s, z = sets[i % len(sets)]
         ops.gemm_raw(act, w, s, out, n=C2["n"], k=C2["k"], weight_bits=4, group_size=128, zeros=z, act_scale=ps,
-                     regime=pkg.W4_REGIME_AUTO)
+                     regime=pkg.W4_REGIME_AUTO, workspace=ws)
 
     return fn, out, act, ps
 

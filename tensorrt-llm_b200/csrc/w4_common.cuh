@@ -21,6 +21,8 @@ constexpr int kDeviceTimeout = -10; // == W4_ERR_DEVICE_TIMEOUT
 // Upper bound on polls of one mbarrier wait. One try_wait already blocks for a hardware-defined
 // interval, so this is on the order of a second, far beyond any legitimate wait.
 constexpr uint32_t kMaxWaitPolls = 1u << 20;
+// Same bound for loops that spin on the non-blocking mbarrier test (tens of cycles per poll).
+constexpr uint32_t kMaxSpinPolls = 1u << 26;
 
 __device__ __forceinline__ uint32_t smem_u32(void const* p)
 {

@@ -23,6 +23,7 @@
 //               of A stages; after the last k step the same warps run the epilogue (tcgen05.ld,
 //               alpha/bias, convert, store), each on its share of the accumulator columns.
 // All waits are bounded; a timeout sets the device status word and the CTA drains and exits.
+#include <cstdlib>
 #include <type_traits>
 
 #include "w4_common.cuh"
@@ -36,12 +37,13 @@ namespace tc
 
 constexpr int BN = 128;       // weight columns per tile (MMA M, TMEM lanes)
 constexpr int BK = 64;        // k per pipeline step (one 128-byte swizzle span of T)
-constexpr int kAStages = 4;   // TMEM ring of converted-weight stages (32 columns each)
+constexpr int kMaxAStages = 8; // TMEM ring of converted-weight stages (32 columns each): columns 256..511
 constexpr int kACol0 = 256;   // first TMEM column of that ring; the accumulator uses [0, 256)
 constexpr int kTmemCols = 512;
 constexpr int kConvGroups = 2;   // groups of 4 conversion warps; group g converts k steps with ks % 2 == g
 constexpr int kThreads = 64 + 128 * kConvGroups;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = kMaxAStages; // one ring index for the shared-memory stage and its TMEM stage
+constexpr int kScaleLookahead = 6; // scale groups fetched ahead of use by the conversion warps
 
 struct Args
 {
@@ -56,27 +58,46 @@ struct Args
     int num_stages;
 };
 
-struct __align__(8) Barriers
+struct __align__(16) Barriers
 {
-    uint64_t full[kMaxStages];    // TMA landed (tx bytes)
-    uint64_t empty[kMaxStages];   // MMA finished with the activations + 4 conversion warps read the weights
-    uint64_t a_full[kAStages];    // 4 conversion warps stored the stage into TMEM
-    uint64_t a_empty[kAStages];   // MMA finished reading the stage
+    uint64_t full[kMaxStages];    // TMA landed (tx bytes); watched by the conversion warps only
+    uint64_t done[kMaxStages];    // the MMAs of the step completed: smem stage and TMEM stage are free
     uint64_t d_full;              // accumulator complete
     uint64_t d_empty;             // 4 epilogue warps drained the accumulator
+    // Steps each conversion warp has finished storing into TMEM, [group][quadrant]. The MMA warp
+    // polls these with plain acquire loads: an mbarrier test issued by the MMA warp right after its
+    // tcgen05.commit is held back until the committed MMAs finish, which costs a full step.
+    alignas(16) uint32_t ready[kConvGroups][4];
     uint32_t tmem_base;
     int abort_flag;
+#ifdef W4_DBG_TRACE
+    long long issue_time[kMaxStages];
+    long long tl[8][16]; // [event][step - 100] time line of tile 0, steps 100..115
+#endif
 };
 
 #ifdef W4_DBG_TRACE
 // Debug build only: cycles CTA 0 spent in each kind of wait, per role.
-__device__ long long g_tc_trace[64];
+__device__ long long g_tc_trace[192];
 #define W4_TC_TIMED(slot_, expr_)                                                                                     \
     do                                                                                                                 \
     {                                                                                                                  \
         long long t0_ = clock64();                                                                                     \
         expr_;                                                                                                         \
         dbg_acc[(slot_) & 3] += clock64() - t0_;                                                                       \
+    } while (0)
+#define W4_TC_TL(ev_, ks_, first_)                                                                                     \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        if (blockIdx.x == 0 && (first_) && (ks_) >= 100 && (ks_) < 116)                                                \
+            bars->tl[ev_][(ks_) -100] = clock64();                                                                     \
+    } while (0)
+#define W4_TC_PHASE(i_)                                                                                                \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        long long now_ = clock64();                                                                                    \
+        dbg_ph[i_] += now_ - dbg_last;                                                                                 \
+        dbg_last = now_;                                                                                               \
     } while (0)
 #define W4_TC_FLUSH(base_)                                                                                             \
     do                                                                                                                 \
@@ -88,20 +109,33 @@ __device__ long long g_tc_trace[64];
 #else
 #define W4_TC_TIMED(slot_, expr_) expr_
 #define W4_TC_FLUSH(base_)
+#define W4_TC_PHASE(i_)
+#define W4_TC_TL(ev_, ks_, first_)
 #endif
 
 __device__ __forceinline__ bool wait_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
-    for (uint32_t i = 0; i < kMaxWaitPolls; ++i)
+    // Spin on the non-blocking test: the blocking try_wait form parks the thread for a
+    // hardware-defined interval, which costs about a microsecond per hand-off in this pipeline.
+    for (uint32_t i = 0; i < kMaxSpinPolls; ++i)
     {
-        if (mbar_try_wait(bar, parity))
+        if (mbar_test_wait(bar, parity))
             return true;
-        if ((i & 255u) == 255u && *abort_flag)
+        if ((i & 1023u) == 1023u && *abort_flag)
             return false;
     }
     *abort_flag = 1;
     atomicExch(&g_device_status, kDeviceTimeout);
     return false;
+}
+
+// Warp-wide wait: one lane polls, the result is broadcast (keeps 31 lanes off the barrier word).
+__device__ __forceinline__ bool wait_flag_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane)
+{
+    int ok = 1;
+    if (lane == 0)
+        ok = wait_flag(bar, parity, abort_flag) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 __device__ __forceinline__ void tc_fence_before()
@@ -114,24 +148,112 @@ __device__ __forceinline__ void tc_fence_after()
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-__device__ __forceinline__ void tc_commit(uint64_t* bar)
+__device__ __forceinline__ bool mbar_test_wait_addr(uint32_t bar_addr, uint32_t parity)
 {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem descriptor]; A is 128 lanes x 16 k of T (8 columns).
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate)
-{
-    uint32_t const acc = accumulate ? 1u : 0u;
+    uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+
+// The following are executed by a whole (converged) warp; one elected lane performs the operation.
+// Keeping the surrounding control flow warp-uniform lets the compiler hold addresses and
+// descriptors in uniform registers, which is what the tensor-core and TMA instructions consume;
+// issued from inside a divergent `if (lane == 0)` every operand has to be moved across first and
+// one tcgen05.mma costs ~70 cycles to issue.
+__device__ __forceinline__ void tc_mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p, pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
         : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_elect(uint32_t bar_addr)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(bar_addr)
+        : "memory");
+}
+
+__device__ __forceinline__ void expect_tx_elect(uint32_t bar_addr, uint32_t bytes)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
+        "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+        "}\n" ::"r"(bar_addr),
+        "r"(bytes)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, void const* tensor_map, int c0, int c1, uint32_t bar_addr)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
+        "@pe cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        "}\n" ::"r"(dst),
+        "l"(tensor_map), "r"(c0), "r"(c1), "r"(bar_addr)
+        : "memory");
+}
+
+// Warp-uniform bounded spin on an mbarrier phase (every lane polls the same word).
+__device__ __forceinline__ bool spin_wait(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag)
+{
+    uint32_t polls = 0;
+    while (!mbar_test_wait_addr(bar_addr, parity))
+    {
+        if ((++polls & 0xffffu) == 0 && (*abort_flag || polls >= kMaxSpinPolls))
+        {
+            *abort_flag = 1;
+            atomicExch(&g_device_status, kDeviceTimeout);
+            return false;
+        }
+    }
+    return true;
+}
+
+// Spins until all four conversion warps of a group have published at least `needed` steps.
+__device__ __forceinline__ bool spin_ready(uint32_t addr, uint32_t needed, volatile int* abort_flag)
+{
+    uint32_t polls = 0;
+    for (;;)
+    {
+        uint32_t a, b, c, d;
+        asm volatile("ld.acquire.cta.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                     : "r"(addr)
+                     : "memory");
+        // counters only grow and stay within a few steps of each other: compare as signed distance
+        if (int(a - needed) >= 0 && int(b - needed) >= 0 && int(c - needed) >= 0 && int(d - needed) >= 0)
+            return true;
+        if ((++polls & 0xffffu) == 0 && (*abort_flag || polls >= kMaxSpinPolls))
+        {
+            *abort_flag = 1;
+            atomicExch(&g_device_status, kDeviceTimeout);
+            return false;
+        }
+    }
 }
 
 __device__ __forceinline__ void tc_st16(uint32_t taddr, uint32_t const (&v)[16])
@@ -195,6 +317,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef W4_DBG_TRACE
     long long dbg_acc[4] = {0, 0, 0, 0};
+    long long dbg_ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long dbg_last = clock64();
     if (blockIdx.x == 0 && threadIdx.x == 0)
     {
         for (int i = 0; i < 32; ++i)
@@ -211,16 +335,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int s = 0; s < a.num_stages; ++s)
         {
             mbar_init(&bars->full[s], 1);
-            mbar_init(&bars->empty[s], 5);
-        }
-        for (int s = 0; s < kAStages; ++s)
-        {
-            mbar_init(&bars->a_full[s], 4);
-            mbar_init(&bars->a_empty[s], 1);
+            mbar_init(&bars->done[s], 1);
         }
         mbar_init(&bars->d_full, 1);
         mbar_init(&bars->d_empty, 4 * kConvGroups);
         bars->abort_flag = 0;
+        for (int i = 0; i < kConvGroups * 4; ++i)
+            (&bars->ready[0][0])[i] = 0;
         mbar_fence_init();
     }
     if (warp == 1)
@@ -239,39 +360,38 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 0)
     {
         // ------------------------------------------------------------------ TMA producer
+        // (whole warp, warp-uniform; an elected lane issues the copies)
         if (lane == 0)
         {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_act) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        }
+        __syncwarp();
+        {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-#ifdef W4_DBG_MMA_ONLY
-            ok = false; // timing experiment: nothing is loaded
-#endif
+            uint32_t const smem_base = smem_u32(smem);
+            uint32_t const full0 = smem_u32(&bars->full[0]), done0 = smem_u32(&bars->done[0]);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
             {
                 int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
                 for (int ks = 0; ks < ksteps; ++ks)
                 {
-                    W4_TC_TIMED(0, ok = wait_flag(&bars->empty[s], ph ^ 1, abort_flag));
+                    W4_TC_TIMED(0, ok = spin_wait(done0 + 8 * s, ph ^ 1, abort_flag));
                     if (!ok)
                         break;
-                    uint8_t* stage = smem + size_t(s) * STAGE_BYTES;
-#ifdef W4_DBG_HALF_ACT
-                    // timing experiment only (wrong results): fetch the activation tile on even steps only
-                    if (ks & 1)
-                    {
-                        mbar_expect_tx(&bars->full[s], W_BYTES);
-                        tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), &bars->full[s]);
-                    }
-                    else
+                    W4_TC_TL(0, ks, tile == 0 && lane == 0);
+                    uint32_t const stage = smem_base + uint32_t(s) * STAGE_BYTES;
+                    uint32_t const full = full0 + 8 * s;
+#ifdef W4_DBG_TRACE
+                    if (lane == 0)
+                        bars->issue_time[s] = clock64();
 #endif
-                    {
-                        mbar_expect_tx(&bars->full[s], STAGE_BYTES);
-                        tma_load_2d(stage, &tm_act, ks * BK, tm * BM, &bars->full[s]);
-                        tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), &bars->full[s]);
-                    }
+                    expect_tx_elect(full, STAGE_BYTES);
+                    tma_load_2d_elect(stage, &tm_act, ks * BK, tm * BM, full);
+                    tma_load_2d_elect(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), full);
+                    W4_TC_TL(1, ks, tile == 0 && lane == 0);
                     if (++s == a.num_stages)
                     {
                         s = 0;
@@ -284,52 +404,70 @@ __global__ void __launch_bounds__(kThreads, 1)
     else if (warp == 1)
     {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0)
+        // One thread feeds the tensor core; its queue is only about one instruction deep, so this
+        // loop has to come back with the next MMA within ~100 cycles: descriptors and addresses are
+        // advanced incrementally, there is one wait and one commit per k step, and the wait spins
+        // on the non-blocking test.
         {
-            int s = 0, t = 0;
-            uint32_t ph = 0, aph = 0, dph = 0;
+            uint64_t const desc0 = smem_desc_sw128(smem_u32(smem));
+            constexpr uint64_t kDescStage = uint64_t(STAGE_BYTES >> 4); // address field is in 16-byte units
+            uint32_t const done0 = smem_u32(&bars->done[0]);
+            uint32_t const d_empty = smem_u32(&bars->d_empty), d_full = smem_u32(&bars->d_full);
+            uint64_t desc = desc0;
+            uint32_t a_col = tmem + kACol0;
+            uint32_t done = done0;
+            uint32_t const ready0 = smem_u32(&bars->ready[0][0]);
+            uint32_t issued[kConvGroups] = {}; // k steps issued so far per conversion group, over all tiles
+            int s = 0;
+            uint32_t ph = 0, dph = 0;
             bool ok = true;
             for (int tile = blockIdx.x, it = 0; tile < num_tiles && ok; tile += gridDim.x, ++it)
             {
                 if (it > 0)
                 {
-                    W4_TC_TIMED(3, ok = wait_flag(&bars->d_empty, dph, abort_flag));
+                    W4_TC_TIMED(3, ok = spin_wait(d_empty, dph, abort_flag));
                     if (!ok)
                         break;
                     dph ^= 1;
                     tc_fence_after();
                 }
+                uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ++ks)
                 {
-#ifndef W4_DBG_MMA_ONLY
-                    W4_TC_TIMED(1, ok = wait_flag(&bars->full[s], ph, abort_flag));
+                    // The conversion warps publish a step only after they have seen the stage's TMA
+                    // barrier, so it covers the activations as well.
+                    uint32_t const grp = uint32_t(ks) % kConvGroups; // the group that converts this step
+                    uint32_t const needed = ++issued[grp];
+                    W4_TC_TIMED(2, ok = spin_ready(ready0 + 16 * grp, needed, abort_flag));
                     if (!ok)
                         break;
-                    W4_TC_TIMED(2, ok = wait_flag(&bars->a_full[t], aph, abort_flag));
-                    if (!ok)
-                        break;
-#endif
+                    W4_TC_TL(3, ks, tile == 0 && lane == 0);
+                    W4_TC_PHASE(0);
                     tc_fence_after();
-                    uint32_t const b_addr = smem_u32(smem + size_t(s) * STAGE_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)
-                        tc_mma_ts(tmem, tmem + kACol0 + t * 32 + kk * 8, smem_desc_sw128(b_addr + kk * 32), kIdesc,
-                            (ks | kk) != 0);
-                    tc_commit(&bars->empty[s]);
-                    tc_commit(&bars->a_empty[t]);
+                    W4_TC_PHASE(1);
+                    tc_mma_ts_elect(tmem, a_col, desc, kIdesc, accumulate);
+                    tc_mma_ts_elect(tmem, a_col + 8, desc + 2, kIdesc, 1u);
+                    tc_mma_ts_elect(tmem, a_col + 16, desc + 4, kIdesc, 1u);
+                    tc_mma_ts_elect(tmem, a_col + 24, desc + 6, kIdesc, 1u);
+                    accumulate = 1u;
+                    W4_TC_PHASE(2);
+                    tc_commit_elect(done); // frees the shared-memory stage and the TMEM stage
+                    W4_TC_PHASE(3);
+                    W4_TC_TL(4, ks, tile == 0 && lane == 0);
+                    desc += kDescStage;
+                    a_col += 32;
+                    done += 8;
                     if (++s == a.num_stages)
                     {
                         s = 0;
                         ph ^= 1;
-                    }
-                    if (++t == kAStages)
-                    {
-                        t = 0;
-                        aph ^= 1;
+                        desc = desc0;
+                        a_col = tmem + kACol0;
+                        done = done0;
                     }
                 }
                 if (ok)
-                    tc_commit(&bars->d_full);
+                    tc_commit_elect(d_full);
             }
         }
     }
@@ -348,124 +486,143 @@ __global__ void __launch_bounds__(kThreads, 1)
         // Column segment of this thread inside a stage's weight lines (two or four 16-byte chunks).
         int const w_off = (n_local / IL) * 128 + (n_local % IL) * SEG;
 
-        int s = 0, t = 0;
-        uint32_t ph = 0, aph = 0, dph = 0;
+        int s = 0;
+        uint32_t ph = 0, dph = 0;
+        uint32_t my_steps = 0; // steps this warp has stored into TMEM (published by lane 0)
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
         {
             int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
             int const n = tn * BN + n_local;
             bool const n_ok = n < a.n;
-            uint32_t s2 = 0, z2 = 0, s2_next = 0, z2_next = 0;
-            if (n_ok)
+            // Scale / zero of this thread's column, one pair per scale group. The loads come from
+            // global memory (L2 at best, ~1 us under load) while a k step lasts a quarter of that,
+            // so they are issued kScaleLookahead groups ahead into a small shift register.
+            uint32_t s2 = 0, z2 = 0;
+            uint32_t sq[kScaleLookahead], zq[kScaleLookahead];
+            int const num_groups = a.group_shift >= 31 ? 1 : (a.k >> a.group_shift);
+#pragma unroll
+            for (int i = 0; i < kScaleLookahead; ++i)
             {
-                s2_next = scales[n];
-                if (HAS_ZERO)
-                    z2_next = zeros[n];
+                sq[i] = 0;
+                zq[i] = 0;
+                if (n_ok && i < num_groups)
+                {
+                    sq[i] = scales[size_t(i) * a.n + n];
+                    if (HAS_ZERO)
+                        zq[i] = zeros[size_t(i) * a.n + n];
+                }
             }
-#ifdef W4_DBG_MMA_ONLY
-            for (int ks = 0; ks < 0; ++ks)
-#else
             for (int ks = 0; ks < ksteps; ++ks)
-#endif
             {
                 if ((ks & ((1 << gsh) - 1)) == 0)
                 {
-                    // new scale group: take the prefetched pair, start fetching the next one
-                    s2 = s2_next | (s2_next << 16);
-                    z2 = z2_next | (z2_next << 16);
-                    int const gnext = (ks >> gsh) + 1;
-                    if (n_ok && (gnext << gsh) < ksteps)
+                    // new scale group: take the oldest prefetched pair, fetch the one furthest ahead
+                    s2 = sq[0] | (sq[0] << 16);
+                    z2 = zq[0] | (zq[0] << 16);
+#pragma unroll
+                    for (int i = 0; i + 1 < kScaleLookahead; ++i)
                     {
-                        s2_next = scales[size_t(gnext) * a.n + n];
+                        sq[i] = sq[i + 1];
+                        zq[i] = zq[i + 1];
+                    }
+                    int const gnext = (ks >> gsh) + kScaleLookahead;
+                    if (n_ok && gnext < num_groups)
+                    {
+                        sq[kScaleLookahead - 1] = scales[size_t(gnext) * a.n + n];
                         if (HAS_ZERO)
-                            z2_next = zeros[size_t(gnext) * a.n + n];
+                            zq[kScaleLookahead - 1] = zeros[size_t(gnext) * a.n + n];
                     }
                 }
                 if ((ks % kConvGroups) == cgroup)
                 {
-                    W4_TC_TIMED(4 + 4 * quad, ok = wait_flag(&bars->full[s], ph, abort_flag));
+                    W4_TC_PHASE(0); // idle / skipped steps
+                    W4_TC_TIMED(4 + 4 * quad, ok = wait_flag_warp(&bars->full[s], ph, abort_flag, lane));
                     if (!ok)
                         break;
+                    W4_TC_PHASE(1); // waited for TMA
+#ifdef W4_DBG_TRACE
+                    dbg_ph[6] += clock64() - bars->issue_time[s];
+#endif
                     uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
                     constexpr int CHUNKS = SEG / 16; // 2 (int4) or 4 (int8)
                     uint4 raw[CHUNKS];
     #pragma unroll
                     for (int c = 0; c < CHUNKS; ++c)
                         raw[c] = *reinterpret_cast<uint4 const*>(wsm + c * 16);
-                    __syncwarp();
-                    if (lane == 0)
-                        mbar_arrive(&bars->empty[s]);
-                    W4_TC_TIMED(5 + 4 * quad, ok = wait_flag(&bars->a_empty[t], aph ^ 1, abort_flag));
-                    if (!ok)
-                        break;
-                    tc_fence_after();
-                    uint32_t const a_addr = lane_addr + kACol0 + t * 32;
+                    W4_TC_PHASE(2); // shared loads + release
+                    // Convert into registers first; only the stores have to wait for the TMEM stage.
+                    uint32_t v[2][16];
                     if (BITS == 4)
                     {
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 2; ++c)
                         {
                             uint32_t const r[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-                            uint32_t v[16];
-    #pragma unroll
+#pragma unroll
                             for (int j = 0; j < 4; ++j)
                             {
                                 uint32_t q[4];
                                 cvt_int4x8<T>(r[j], q);
-    #pragma unroll
-                                for (int p = 0; p < 4; ++p) // pair p of register j holds k = 2j + 8p (+1)
-                                    v[j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+#pragma unroll
+                                for (int p = 0; p < 4; ++p) // pair p of register j holds k = 32c + 2j + 8p (+1)
+                                    v[c][j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
                             }
-                            tc_st16(a_addr + 16 * c, v); // the TMEM address is warp-uniform
                         }
                     }
                     else
                     {
-    #pragma unroll
+#pragma unroll
                         for (int h = 0; h < 2; ++h)
-                        {
-                            uint32_t v[16];
-    #pragma unroll
+#pragma unroll
                             for (int cc = 0; cc < 2; ++cc)
                             {
-                                uint4 const x = raw[2 * h + cc];
+                                uint4 const x = raw[(2 * h + cc) % CHUNKS];
                                 uint32_t const r[4] = {x.x, x.y, x.z, x.w};
-    #pragma unroll
+#pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                 {
                                     uint32_t q[2];
                                     cvt_int8x4<T>(r[j], q);
-    #pragma unroll
-                                    for (int p = 0; p < 2; ++p) // pair p of register j holds k = 2j + 8p (+1)
-                                        v[8 * cc + j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+#pragma unroll
+                                    for (int p = 0; p < 2; ++p) // pair p of register j holds k = 16(2h+cc) + 2j + 8p (+1)
+                                        v[h][8 * cc + j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
                                 }
                             }
-                            tc_st16(a_addr + 16 * h, v);
-                        }
                     }
+                    W4_TC_PHASE(3); // conversion
+                    W4_TC_TIMED(5 + 4 * quad, ok = wait_flag_warp(&bars->done[s], ph ^ 1, abort_flag, lane));
+                    if (!ok)
+                        break;
+                    tc_fence_after();
+                    W4_TC_PHASE(4); // waited for the TMEM stage
+                    uint32_t const a_addr = lane_addr + kACol0 + s * 32; // warp-uniform column address
+                    tc_st16(a_addr, v[0]);
+                    tc_st16(a_addr + 16, v[1]);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0)
-                        mbar_arrive(&bars->a_full[t]);
+                    {
+                        ++my_steps;
+                        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(&bars->ready[cgroup][quad])),
+                                     "r"(my_steps)
+                                     : "memory");
+                    }
+                    W4_TC_PHASE(5); // tcgen05.st + wait + signal
+                    W4_TC_TL((quad == 0 ? 2 : 4 + quad), ks, tile == 0 && lane == 0);
                 }
                 if (++s == a.num_stages)
                 {
                     s = 0;
                     ph ^= 1;
                 }
-                if (++t == kAStages)
-                {
-                    t = 0;
-                    aph ^= 1;
-                }
             }
             if (!ok)
                 break;
 
             // ---- epilogue: this thread owns output column n for all BM rows of the tile
-            W4_TC_TIMED(6 + 4 * quad, ok = wait_flag(&bars->d_full, dph, abort_flag));
+            W4_TC_TIMED(6 + 4 * quad, ok = wait_flag_warp(&bars->d_full, dph, abort_flag, lane));
             if (!ok)
                 break;
             dph ^= 1;
@@ -501,6 +658,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (blockIdx.x == 0 && threadIdx.x == 0)
         g_tc_trace[32] = clock64();
 #endif
+#ifdef W4_DBG_TRACE
+    if (warp == 2 && blockIdx.x == 0 && lane == 0)
+        for (int i = 0; i < 8; ++i)
+            g_tc_trace[48 + i] = dbg_ph[i];
+    if (warp == 1 && blockIdx.x == 0 && lane == 0)
+        for (int i = 0; i < 4; ++i)
+            g_tc_trace[56 + i] = dbg_ph[i];
+#endif
     if (warp == 0)
         W4_TC_FLUSH(40);
     else if (warp == 1)
@@ -510,6 +675,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // Teardown: everyone meets here (also after a timeout), then the allocating warp frees TMEM.
     tc_fence_before();
     __syncthreads();
+#ifdef W4_DBG_TRACE
+    if (blockIdx.x == 0 && threadIdx.x < 128)
+        g_tc_trace[64 + threadIdx.x] = bars->tl[threadIdx.x >> 4][threadIdx.x & 15];
+#endif
     if (warp == 1)
     {
         tc_fence_after();
@@ -545,6 +714,13 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
     if (stages < 2)
         return W4_ERR_CUDA;
     a.num_stages = stages > kMaxStages ? kMaxStages : stages;
+    static int const st_override = []
+    {
+        char const* e = getenv("W4_TC_STAGES"); // tuning aid: fewer pipeline stages
+        return e ? atoi(e) : 0;
+    }();
+    if (st_override > 1 && st_override < a.num_stages)
+        a.num_stages = st_override;
     size_t const smem = size_t(a.num_stages) * STAGE_BYTES + fixed;
 
     // Activations [m, k] of T, boxes of 64 k x BM rows, 128-byte swizzle (rows past m read as 0).
@@ -577,9 +753,15 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
 template <typename T, int BITS, bool HAS_ZERO>
 static int dispatch_bm(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
 {
-    if (p.m <= 64)
+    static int const bm_override = []
+    {
+        char const* e = getenv("W4_TC_BM"); // tuning aid: force the activation-row tile
+        return e ? atoi(e) : 0;
+    }();
+    int const bm = bm_override ? bm_override : (p.m <= 64 ? 64 : (p.m <= 128 ? 128 : 256));
+    if (bm == 64)
         return launch_one<T, BITS, 64, HAS_ZERO>(p, act, dev, stream);
-    if (p.m <= 128)
+    if (bm == 128)
         return launch_one<T, BITS, 128, HAS_ZERO>(p, act, dev, stream);
     return launch_one<T, BITS, 256, HAS_ZERO>(p, act, dev, stream);
 }
@@ -598,7 +780,7 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 #ifdef W4_DBG_TRACE
 extern "C" int w4_dbg_read_tc_trace(long long* out)
 {
-    return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 64) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 192) == cudaSuccess ? 0 : -1;
 }
 #endif
 
