@@ -115,6 +115,31 @@ __device__ __forceinline__ void tma_load_2d(void* dst, void const* tensor_map, i
         : "memory");
 }
 
+// Variants for a converged warp: one elected lane performs the operation, operands are warp-uniform.
+__device__ __forceinline__ void elect_expect_tx(uint32_t bar_addr, uint32_t bytes)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
+        "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+        "}\n" ::"r"(bar_addr),
+        "r"(bytes)
+        : "memory");
+}
+
+__device__ __forceinline__ void elect_tma_load_2d(uint32_t dst, void const* tensor_map, int c0, int c1, uint32_t bar_addr)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "elect.sync _|pe, 0xffffffff;\n"
+        "@pe cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        "}\n" ::"r"(dst),
+        "l"(tensor_map), "r"(c0), "r"(c1), "r"(bar_addr)
+        : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

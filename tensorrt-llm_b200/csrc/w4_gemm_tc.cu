@@ -193,30 +193,6 @@ __device__ __forceinline__ void tc_commit_elect(uint32_t bar_addr)
         : "memory");
 }
 
-__device__ __forceinline__ void expect_tx_elect(uint32_t bar_addr, uint32_t bytes)
-{
-    asm volatile(
-        "{\n"
-        ".reg .pred pe;\n"
-        "elect.sync _|pe, 0xffffffff;\n"
-        "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
-        "}\n" ::"r"(bar_addr),
-        "r"(bytes)
-        : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, void const* tensor_map, int c0, int c1, uint32_t bar_addr)
-{
-    asm volatile(
-        "{\n"
-        ".reg .pred pe;\n"
-        "elect.sync _|pe, 0xffffffff;\n"
-        "@pe cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-        "}\n" ::"r"(dst),
-        "l"(tensor_map), "r"(c0), "r"(c1), "r"(bar_addr)
-        : "memory");
-}
-
 // Warp-uniform bounded spin on an mbarrier phase (every lane polls the same word).
 __device__ __forceinline__ bool spin_wait(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag)
 {
@@ -388,9 +364,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (lane == 0)
                         bars->issue_time[s] = clock64();
 #endif
-                    expect_tx_elect(full, STAGE_BYTES);
-                    tma_load_2d_elect(stage, &tm_act, ks * BK, tm * BM, full);
-                    tma_load_2d_elect(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), full);
+                    elect_expect_tx(full, STAGE_BYTES);
+                    elect_tma_load_2d(stage, &tm_act, ks * BK, tm * BM, full);
+                    elect_tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), full);
                     W4_TC_TL(1, ks, tile == 0 && lane == 0);
                     if (++s == a.num_stages)
                     {

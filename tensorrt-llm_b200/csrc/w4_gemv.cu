@@ -172,7 +172,7 @@ __device__ __forceinline__ void prefetch_l2(void const* p)
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD>
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros)
 {
@@ -204,11 +204,26 @@ __global__ void __launch_bounds__(kThreads, 1)
     int* next_tile = const_cast<int*>(abort_flag) + 1; // first tile whose copies have not been started
     int const num_tiles = num_cg * num_panels;
 
-    // Starts the copies of tile i (column group i / num_panels, k panel i % num_panels) into its
-    // ring slot; called by one thread at a time (see try_issue).
+    // Partial sums in shared memory: [cg in batch][warp][mb][c][g * MT + t], only the lanes whose
+    // rows exist (t < MT) are stored.
+    int const MT = MB == 2 ? 4 : (a.m + 1) >> 1;
+    int const per_cg = kWarps * MB * 4 * 8 * MT;
+    int const red_cap = max(1, (kRedBytes / 4) / per_cg); // column groups the reduction buffer holds
+    // Column groups that share one activation load (only matters with several k panels); the
+    // reduction batch is a whole number of such sub-batches.
+    int const cbe = min(CB, red_cap);
+    int const batch = (red_cap / cbe) * cbe;
+
+
+    // Starts the copies of tile i into its ring slot; called by one thread at a time (see try_issue).
     auto issue_tile = [&](int i, int slot)
     {
-        int const cg = i / num_panels, panel = i - cg * num_panels;
+        // Tile order: column groups in sub-batches of `cbe`; inside a sub-batch the k panels are
+        // the outer loop, so one activation load serves all its column groups.
+        int const per_sb = cbe * num_panels;
+        int const sb = i / per_sb, r = i - sb * per_sb;
+        int const ncb = min(cbe, num_cg - sb * cbe);
+        int const panel = r / ncb, cg = sb * cbe + (r - panel * ncb);
         int const row_first = r0 + cg * C::RPG;
         int const rows = min(C::RPG, r1 - row_first);
         int const kp_len = min(C::KP, a.k - panel * C::KP);
@@ -239,23 +254,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     // boundary and while it polls for data; the compare-and-swap picks one issuer per tile.
     auto try_issue = [&]()
     {
+        // *next_tile packs the next tile to start, its ring slot and how often that slot has been
+        // used (mod 256): j | slot << 16 | use << 20, so the common "nothing to do" path needs no
+        // division.
         for (;;)
         {
-            int const j = *const_cast<volatile int*>(next_tile);
+            uint32_t const st = *const_cast<volatile uint32_t*>(reinterpret_cast<uint32_t*>(next_tile));
+            int const j = int(st & 0xffffu), slot = int((st >> 16) & 0xfu), use = int(st >> 20);
             if (j >= num_tiles)
                 return;
-            int const slot = j % a.num_slots, use = j / a.num_slots;
-            if (use > 0 && !mbar_test_wait(&empty_bar[slot], (use - 1) & 1))
+            if (j >= a.num_slots && !mbar_test_wait(&empty_bar[slot], (use - 1) & 1))
                 return;
             if (j >= a.depth)
             {
-                int const jd = j - a.depth;
-                if (!mbar_test_wait(&full_bar[jd % a.num_slots], (jd / a.num_slots) & 1))
+                // tile j - depth: `depth` slots back in the ring
+                int const sd = slot >= a.depth ? slot - a.depth : slot - a.depth + a.num_slots;
+                int const ud = slot >= a.depth ? use : use - 1;
+                if (!mbar_test_wait(&full_bar[sd], ud & 1))
                     return;
             }
-            if (atomicCAS(next_tile, j, j + 1) == j)
+            bool const wrap = slot + 1 == a.num_slots;
+            uint32_t const nxt = uint32_t(j + 1) | (uint32_t(wrap ? 0 : slot + 1) << 16)
+                | (uint32_t((use + (wrap ? 1 : 0)) & 0xff) << 20);
+            if (atomicCAS(reinterpret_cast<uint32_t*>(next_tile), st, nxt) == st)
             {
-                if (use > 0)
+                if (j >= a.num_slots)
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 issue_tile(j, slot);
             }
@@ -392,10 +415,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     };
 
-    float acc[MB][4]; // running sums of the current column group
+    float acc[CB][MB][4]; // running sums of the column groups of the current sub-batch
 
     // One warp unit (16 columns x UK k) out of the tile in shared memory.
-    auto process_unit = [&](int j, int cg, uint8_t const* tile)
+    auto process_unit = [&](int j, int cg, uint8_t const* tile, float(&acc)[MB][4])
     {
         uint32_t s_word, z_word;
         read_scales(j, cg, tile, s_word, z_word);
@@ -533,12 +556,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     };
 
-    // Partial sums in shared memory: [cg in batch][warp][mb][c][g * MT + t], only the lanes whose
-    // rows exist (t < MT) are stored.
-    int const MT = MB == 2 ? 4 : (a.m + 1) >> 1;
-    int const per_cg = kWarps * MB * 4 * 8 * MT;
-    int const batch = max(1, (kRedBytes / 4) / per_cg);
-
     W4_STAMP(2);
     // Activations (and, later, the output) belong to the preceding kernels: wait for them here.
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -548,73 +565,90 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     bool ok = true;
     int slot = 0, use = 0, tile_index = 0;
+    bool first_act = true; // the first activation fragments were loaded above
     for (int cg0 = 0; cg0 < num_cg; cg0 += batch)
     {
         int const nb = min(batch, num_cg - cg0);
-        for (int cb = 0; cb < nb; ++cb)
+        for (int c0 = 0; c0 < nb; c0 += cbe)
         {
-            int const cg = cg0 + cb;
+            int const ncb = min(cbe, nb - c0);
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb)
+            for (int ci = 0; ci < CB; ++ci)
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    acc[mb][c] = 0.f;
+                for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        acc[ci][mb][c] = 0.f;
 
             for (int panel = 0; panel < num_panels; ++panel)
             {
-                if (num_panels > 1 && (cg > 0 || panel > 0))
+                if (num_panels > 1 && !first_act)
                     load_act(panel);
-
-                if (ok)
+                first_act = false;
+#pragma unroll
+                for (int ci = 0; ci < CB; ++ci)
                 {
-                    // poll for the tile; while it is not there, help start later tiles
-                    uint32_t polls = 0;
-                    while (!mbar_try_wait(&full_bar[slot], use & 1))
+                    if (ci >= ncb)
+                        break;
+                    int const cg = cg0 + c0 + ci;
+                    if (ok)
                     {
-                        if (lane == 0)
-                            try_issue();
-                        if (++polls > kMaxWaitPolls || ((polls & 1023u) == 0 && *abort_flag))
+                        // poll for the tile; while it is not there, help start later tiles
+                        uint32_t polls = 0;
+                        while (!mbar_try_wait(&full_bar[slot], use & 1))
                         {
-                            ok = false;
-                            *abort_flag = 1;
-                            atomicExch(&g_device_status, kDeviceTimeout);
-                            break;
+                            if (lane == 0)
+                                try_issue();
+                            if (++polls > kMaxWaitPolls || ((polls & 1023u) == 0 && *abort_flag))
+                            {
+                                ok = false;
+                                *abort_flag = 1;
+                                atomicExch(&g_device_status, kDeviceTimeout);
+                                break;
+                            }
                         }
                     }
-                }
-                if (lane == 0)
-                    try_issue(); // this tile has arrived: the one `depth` ahead may start
-                uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
-                W4_STAMP(4 + 3 * tile_index);
+                    if (lane == 0)
+                        try_issue(); // this tile has arrived: the one `depth` ahead may start
+                    uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
+                    W4_STAMP(4 + 3 * tile_index);
 #ifndef W4_DBG_NOCOMPUTE
 #pragma unroll
-                for (int j = 0; j < C::UPW; ++j)
-                    process_unit(j, cg, tile);
+                    for (int j = 0; j < C::UPW; ++j)
+                        process_unit(j, cg, tile, acc[ci]);
 #endif
-                W4_STAMP(5 + 3 * tile_index);
-                __syncwarp();
-                W4_STAMP(43 + tile_index);
-                if (lane == 0)
-                {
-                    mbar_arrive(&empty_bar[slot]);
-                    W4_STAMP(50 + tile_index);
-                    try_issue();
-                }
-                W4_STAMP(6 + 3 * tile_index);
-                ++tile_index;
-                if (++slot == a.num_slots)
-                {
-                    slot = 0;
-                    ++use;
+                    W4_STAMP(5 + 3 * tile_index);
+                    __syncwarp();
+                    W4_STAMP(43 + tile_index);
+                    if (lane == 0)
+                    {
+                        mbar_arrive(&empty_bar[slot]);
+                        W4_STAMP(50 + tile_index);
+                        try_issue();
+                    }
+                    W4_STAMP(6 + 3 * tile_index);
+                    ++tile_index;
+                    if (++slot == a.num_slots)
+                    {
+                        slot = 0;
+                        ++use;
+                    }
                 }
             }
             if (t < MT)
             {
 #pragma unroll
-                for (int mb = 0; mb < MB; ++mb)
+                for (int ci = 0; ci < CB; ++ci)
+                {
+                    if (ci >= ncb)
+                        break;
+                    int const cb = c0 + ci;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        red[(((cb * kWarps + warp) * MB + mb) * 4 + c) * (8 * MT) + g * MT + t] = acc[mb][c];
+                    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            red[(((cb * kWarps + warp) * MB + mb) * 4 + c) * (8 * MT) + g * MT + t] = acc[ci][mb][c];
+                }
             }
         }
 
@@ -661,11 +695,11 @@ namespace w4
 namespace gemv
 {
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD>
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
 static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     using C = Cfg<BITS, MB>;
-    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE, FOLD>;
+    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE, FOLD, CB>;
     Args args = a;
     args.groups_per_panel = a.group_shift >= 31 ? 1 : C::KP >> a.group_shift;
     args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
@@ -712,6 +746,13 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
             configured[dev.device] = true;
     }
     int const grid = args.num_rows < dev.num_sms ? args.num_rows : dev.num_sms;
+    {
+        // the kernel's tile counter is 16 bits wide
+        long const rows_per_cta = (args.num_rows + grid - 1) / grid;
+        long const tiles_per_cta = ((rows_per_cta + C::RPG - 1) / C::RPG + 1) * ((a.k + C::KP - 1) / C::KP);
+        if (tiles_per_cta > 60000)
+            return W4_ERR_BAD_SHAPE;
+    }
     // Launched as a programmatic dependent of whatever precedes it in the stream (the kernel
     // orders itself with griddepcontrol.wait). W4_GEMV_PDL=0 turns the attribute off.
     static bool const use_pdl = []
@@ -734,17 +775,27 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
-template <typename T, int BITS, int MB, bool FOLD>
+template <typename T, int BITS, int MB, bool FOLD, int CB>
 static int dispatch_flags(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     bool const z = a.zeros != nullptr, s = a.act_scale != nullptr;
     if (z && s)
-        return launch_one<T, BITS, MB, true, true, FOLD>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, true, FOLD, CB>(a, dev, stream);
     if (z)
-        return launch_one<T, BITS, MB, true, false, FOLD>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, false, FOLD, CB>(a, dev, stream);
     if (s)
-        return launch_one<T, BITS, MB, false, true, FOLD>(a, dev, stream);
-    return launch_one<T, BITS, MB, false, false, FOLD>(a, dev, stream);
+        return launch_one<T, BITS, MB, false, true, FOLD, CB>(a, dev, stream);
+    return launch_one<T, BITS, MB, false, false, FOLD, CB>(a, dev, stream);
+}
+
+// With more than one k panel the column groups are walked in sub-batches that share each
+// activation load (4 groups for m <= 8, 2 for m <= 16); with a single panel there is nothing to share.
+template <typename T, int BITS, int MB, bool FOLD>
+static int dispatch_panels(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
+{
+    if (a.k > Cfg<BITS, MB>::KP)
+        return dispatch_flags<T, BITS, MB, FOLD, (MB == 1 ? 4 : 2)>(a, dev, stream);
+    return dispatch_flags<T, BITS, MB, FOLD, 1>(a, dev, stream);
 }
 
 template <typename T>
@@ -755,10 +806,10 @@ static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev,
         // A warp unit spans 128 k for int4: the folded arithmetic needs one scale group per unit.
         bool const fold = a.group_shift >= 7;
         if (fold)
-            return mb == 1 ? dispatch_flags<T, 4, 1, true>(a, dev, stream) : dispatch_flags<T, 4, 2, true>(a, dev, stream);
-        return mb == 1 ? dispatch_flags<T, 4, 1, false>(a, dev, stream) : dispatch_flags<T, 4, 2, false>(a, dev, stream);
+            return mb == 1 ? dispatch_panels<T, 4, 1, true>(a, dev, stream) : dispatch_panels<T, 4, 2, true>(a, dev, stream);
+        return mb == 1 ? dispatch_panels<T, 4, 1, false>(a, dev, stream) : dispatch_panels<T, 4, 2, false>(a, dev, stream);
     }
-    return mb == 1 ? dispatch_flags<T, 8, 1, true>(a, dev, stream) : dispatch_flags<T, 8, 2, true>(a, dev, stream);
+    return mb == 1 ? dispatch_panels<T, 8, 1, true>(a, dev, stream) : dispatch_panels<T, 8, 2, true>(a, dev, stream);
 }
 
 } // namespace gemv

@@ -59,6 +59,16 @@ def test_reference_test_shapes(m, n, k, group, bits):
     _check(p)
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m,n,k,group", [(3, 1024, 8192, 128), (8, 2048, 12288, 128), (12, 512, 6144, 64),
+                                         (1, 14336, 8192, 128), (16, 4096, 14336, 128)])
+def test_several_k_panels(m, n, k, group, bits):
+    """K larger than one shared-memory panel: column groups are walked in sub-batches that share
+    the activation fragments."""
+    p = make_problem(m, n, k, bits, group, torch.bfloat16, zero=True, bias=True, prequant=True, seed=k // 64 + m)
+    _check(p)
+
+
 def test_alpha_scaling():
     p = make_problem(2, 256, 256, 4, 128, torch.bfloat16, zero=True, seed=5)
     _check(p, alpha=0.5)
