@@ -162,16 +162,12 @@ extern "C"
         (void) group_size;
         if (m <= 8)
             return W4_REGIME_GEMV; // one pass over the weights
-        // Cost model fitted to measurements on B200 (microseconds):
-        //  decode kernel: one pass over the packed weights per 8 rows at ~1.7 TB/s plus ~4 us;
-        //  tensor-core kernel: ~0.465 us per 64-wide k step per wave of 128-column tiles (its
-        //  per-step pipeline floor, independent of the row tile for m <= 256) plus ~7 us.
+        // Cost model fitted to measurements on B200 (microseconds): the decode kernel makes one
+        // pass over the packed weights per 8 rows at ~1.7 TB/s plus ~4 us; the tensor-core kernel's
+        // estimate comes from its own per-step costs (148 SMs assumed: no device is queried here).
         double const weight_mb = double(n) * double(k) * weight_bits / 8.0 / 1.0e6;
         double const gemv_us = double((m + 7) / 8) * (weight_mb / 1.7 + 4.0);
-        int const bm = m <= 64 ? 64 : (m <= 128 ? 128 : 256);
-        long const tiles = long((n + 127) / 128) * long((m + bm - 1) / bm);
-        double const waves = double((tiles + 147) / 148);
-        double const gemm_us = 7.0 + 0.465 * double(k / 64) * waves * (bm == 256 ? 1.15 : 1.0);
+        double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, 148);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;
     }
 

@@ -12,16 +12,25 @@
 // output column n, 128 per tile), written there straight from registers by the conversion warps,
 // so they never travel through shared memory; the activations are the "B" operand, brought by TMA
 // into 128-byte-swizzled shared memory and consumed by the MMA unmodified. One tile is 128 columns
-// of W times up to 256 rows of the activation matrix, so each weight is converted once per 256
-// activation rows.
+// of W times 64..256 rows of the activation matrix; a pipeline step covers 128 k (two 64-wide
+// swizzled halves, eight tcgen05.mma of K = 16).
 //
-// Warp roles (320 threads, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer: activation tile [BM x 64] + packed weight tile per k step
-//   warp 1      allocates TMEM, issues tcgen05.mma (one elected lane), commits to mbarriers
+// Warp roles (320 threads, one CTA per SM, persistent over tiles, n-fastest tile order):
+//   warp 0      TMA producer: two activation half-tiles [BM x 64] + the packed weight lines per step
+//   warp 1      allocates TMEM, issues tcgen05.mma and tcgen05.commit (whole warp, warp-uniform
+//               operands, one elected lane per instruction)
 //   warps 2..9  conversion, two warps per TMEM lane quadrant taking alternate k steps: shared memory
 //               -> registers -> exact int->T conversion, scale/zero -> tcgen05.st into the TMEM ring
 //               of A stages; after the last k step the same warps run the epilogue (tcgen05.ld,
 //               alpha/bias, convert, store), each on its share of the accumulator columns.
+// Hand-offs: `full` (TMA -> conversion), per-warp step counters polled with acquire loads
+// (conversion -> MMA), `done` (tcgen05.commit -> producer and conversion: the shared-memory stage
+// and the TMEM stage of a step are released together), `d_full` / `d_empty` (accumulator).
+// What was measured while tuning (B200): the pipeline has a cost per k step of roughly 900-1100
+// cycles that does not depend on the row tile, so the step is made as fat as shared memory allows
+// (128 k); issuing tcgen05.mma from a divergent single lane costs ~70 cycles per instruction
+// against ~40 from a converged warp; scale/zero loads need several groups of lookahead because a
+// step is shorter than an L2 round trip.
 // All waits are bounded; a timeout sets the device status word and the CTA drains and exits.
 #include <cstdlib>
 #include <type_traits>
@@ -36,8 +45,9 @@ namespace tc
 {
 
 constexpr int BN = 128;       // weight columns per tile (MMA M, TMEM lanes)
-constexpr int BK = 64;        // k per pipeline step (one 128-byte swizzle span of T)
-constexpr int kMaxAStages = 8; // TMEM ring of converted-weight stages (32 columns each): columns 256..511
+constexpr int BK = 128;       // k per pipeline step: two 64-wide halves (one 128-byte swizzle span of T each)
+constexpr int kHalves = BK / 64;
+constexpr int kMaxAStages = 4; // TMEM ring of converted-weight stages (64 columns each): columns 256..511
 constexpr int kACol0 = 256;   // first TMEM column of that ring; the accumulator uses [0, 256)
 constexpr int kTmemCols = 512;
 constexpr int kConvGroups = 2;   // groups of 4 conversion warps; group g converts k steps with ks % 2 == g
@@ -274,8 +284,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 {
     using P = Pair<T>;
     constexpr int IL = BITS == 4 ? 4 : 2;
-    constexpr int ACT_BYTES = BM * 128;          // BM rows x 64 k of T
-    constexpr int W_BYTES = (BN / IL) * 128;     // interleaved rows x one 128-byte line each
+    constexpr int ACT_HALF = BM * 128;                      // BM rows x 64 k of T (one swizzled tile)
+    constexpr int ACT_BYTES = kHalves * ACT_HALF;
+    constexpr int W_BYTES = (BN / IL) * 128 * kHalves;      // interleaved rows x two adjacent 128-byte lines
     constexpr int STAGE_BYTES = ACT_BYTES + W_BYTES;
     constexpr int SEG = 128 / IL;                // bytes of one column inside a line
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = fp16, 1 = bf16
@@ -304,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
 #endif
     int const num_tiles = a.tiles_n * a.tiles_m;
-    int const ksteps = a.k / BK;
+    int const ksteps = (a.k + BK - 1) / BK; // a trailing 64-wide half reads as zeros (TMA fill)
 
     if (threadIdx.x == 0)
     {
@@ -366,7 +377,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
                     elect_expect_tx(full, STAGE_BYTES);
                     elect_tma_load_2d(stage, &tm_act, ks * BK, tm * BM, full);
-                    elect_tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128, tn * (BN / IL), full);
+                    elect_tma_load_2d(stage + ACT_HALF, &tm_act, ks * BK + 64, tm * BM, full);
+                    elect_tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128 * kHalves, tn * (BN / IL), full);
                     W4_TC_TL(1, ks, tile == 0 && lane == 0);
                     if (++s == a.num_stages)
                     {
@@ -425,13 +437,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tc_mma_ts_elect(tmem, a_col + 8, desc + 2, kIdesc, 1u);
                     tc_mma_ts_elect(tmem, a_col + 16, desc + 4, kIdesc, 1u);
                     tc_mma_ts_elect(tmem, a_col + 24, desc + 6, kIdesc, 1u);
+                    constexpr uint64_t kDescHalf = uint64_t(ACT_HALF >> 4); // second 64-wide half of the step
+                    tc_mma_ts_elect(tmem, a_col + 32, desc + kDescHalf, kIdesc, 1u);
+                    tc_mma_ts_elect(tmem, a_col + 40, desc + kDescHalf + 2, kIdesc, 1u);
+                    tc_mma_ts_elect(tmem, a_col + 48, desc + kDescHalf + 4, kIdesc, 1u);
+                    tc_mma_ts_elect(tmem, a_col + 56, desc + kDescHalf + 6, kIdesc, 1u);
                     accumulate = 1u;
                     W4_TC_PHASE(2);
                     tc_commit_elect(done); // frees the shared-memory stage and the TMEM stage
                     W4_TC_PHASE(3);
                     W4_TC_TL(4, ks, tile == 0 && lane == 0);
                     desc += kDescStage;
-                    a_col += 32;
+                    a_col += 32 * kHalves;
                     done += 8;
                     if (++s == a.num_stages)
                     {
@@ -458,9 +475,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint16_t const* zeros = static_cast<uint16_t const*>(a.zeros);
         uint16_t const* bias = static_cast<uint16_t const*>(a.bias);
         uint16_t* out = static_cast<uint16_t*>(a.out);
-        int const gsh = a.group_shift >= 31 ? 30 : a.group_shift - 6; // log2(k steps per scale group)
-        // Column segment of this thread inside a stage's weight lines (two or four 16-byte chunks).
-        int const w_off = (n_local / IL) * 128 + (n_local % IL) * SEG;
+        int const gsh = a.group_shift >= 31 ? 30 : a.group_shift - 6; // log2(64-wide halves per scale group)
+        // Column segment of this thread inside the first of a stage's two weight lines.
+        int const w_off = (n_local / IL) * (128 * kHalves) + (n_local % IL) * SEG;
 
         int s = 0;
         uint32_t ph = 0, dph = 0;
@@ -491,24 +508,35 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             for (int ks = 0; ks < ksteps; ++ks)
             {
-                if ((ks & ((1 << gsh) - 1)) == 0)
-                {
-                    // new scale group: take the oldest prefetched pair, fetch the one furthest ahead
-                    s2 = sq[0] | (sq[0] << 16);
-                    z2 = zq[0] | (zq[0] << 16);
+                // (scale, zero) pairs of the step's two halves; a new scale group starts every
+                // 2^gsh halves: take the oldest prefetched pair, fetch the one furthest ahead.
+                uint32_t s2h[kHalves], z2h[kHalves];
 #pragma unroll
-                    for (int i = 0; i + 1 < kScaleLookahead; ++i)
+                for (int h = 0; h < kHalves; ++h)
+                {
+                    int const u = ks * kHalves + h;
+                    if ((u & ((1 << gsh) - 1)) == 0)
                     {
-                        sq[i] = sq[i + 1];
-                        zq[i] = zq[i + 1];
+                        s2 = sq[0] | (sq[0] << 16);
+                        z2 = zq[0] | (zq[0] << 16);
+#pragma unroll
+                        for (int i = 0; i + 1 < kScaleLookahead; ++i)
+                        {
+                            sq[i] = sq[i + 1];
+                            zq[i] = zq[i + 1];
+                        }
+                        int const gnext = (u >> gsh) + kScaleLookahead;
+                        sq[kScaleLookahead - 1] = 0;
+                        zq[kScaleLookahead - 1] = 0;
+                        if (n_ok && gnext < num_groups)
+                        {
+                            sq[kScaleLookahead - 1] = scales[size_t(gnext) * a.n + n];
+                            if (HAS_ZERO)
+                                zq[kScaleLookahead - 1] = zeros[size_t(gnext) * a.n + n];
+                        }
                     }
-                    int const gnext = (ks >> gsh) + kScaleLookahead;
-                    if (n_ok && gnext < num_groups)
-                    {
-                        sq[kScaleLookahead - 1] = scales[size_t(gnext) * a.n + n];
-                        if (HAS_ZERO)
-                            zq[kScaleLookahead - 1] = zeros[size_t(gnext) * a.n + n];
-                    }
+                    s2h[h] = s2;
+                    z2h[h] = z2;
                 }
                 if ((ks % kConvGroups) == cgroup)
                 {
@@ -521,50 +549,59 @@ __global__ void __launch_bounds__(kThreads, 1)
                     dbg_ph[6] += clock64() - bars->issue_time[s];
 #endif
                     uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
-                    constexpr int CHUNKS = SEG / 16; // 2 (int4) or 4 (int8)
-                    uint4 raw[CHUNKS];
-    #pragma unroll
-                    for (int c = 0; c < CHUNKS; ++c)
-                        raw[c] = *reinterpret_cast<uint4 const*>(wsm + c * 16);
+                    constexpr int CHUNKS = SEG / 16; // 16-byte chunks per half: 2 (int4) or 4 (int8)
+                    uint4 raw[kHalves][CHUNKS];
+#pragma unroll
+                    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+                        for (int c = 0; c < CHUNKS; ++c)
+                            raw[h][c] = *reinterpret_cast<uint4 const*>(wsm + h * 128 + c * 16);
                     W4_TC_PHASE(2); // shared loads + release
                     // Convert into registers first; only the stores have to wait for the TMEM stage.
-                    uint32_t v[2][16];
-                    if (BITS == 4)
-                    {
+                    // v[2h + x] holds TMEM columns 32h + 16x .. +15 (k = 64h + 32x .. +31).
+                    uint32_t v[2 * kHalves][16];
 #pragma unroll
-                        for (int c = 0; c < 2; ++c)
+                    for (int h = 0; h < kHalves; ++h)
+                    {
+                        uint32_t const s2 = s2h[h], z2 = z2h[h];
+                        if (BITS == 4)
                         {
-                            uint32_t const r[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
+                            for (int c = 0; c < 2; ++c)
                             {
-                                uint32_t q[4];
-                                cvt_int4x8<T>(r[j], q);
-#pragma unroll
-                                for (int p = 0; p < 4; ++p) // pair p of register j holds k = 32c + 2j + 8p (+1)
-                                    v[c][j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
-                            }
-                        }
-                    }
-                    else
-                    {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-#pragma unroll
-                            for (int cc = 0; cc < 2; ++cc)
-                            {
-                                uint4 const x = raw[(2 * h + cc) % CHUNKS];
-                                uint32_t const r[4] = {x.x, x.y, x.z, x.w};
+                                uint32_t const r[4] = {raw[h][c].x, raw[h][c].y, raw[h][c].z, raw[h][c].w};
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                 {
-                                    uint32_t q[2];
-                                    cvt_int8x4<T>(r[j], q);
+                                    uint32_t q[4];
+                                    cvt_int4x8<T>(r[j], q);
 #pragma unroll
-                                    for (int p = 0; p < 2; ++p) // pair p of register j holds k = 16(2h+cc) + 2j + 8p (+1)
-                                        v[h][8 * cc + j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+                                    for (int p = 0; p < 4; ++p) // pair p of register j holds k = 32c + 2j + 8p (+1)
+                                        v[2 * h + c][j + 4 * p] = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
                                 }
                             }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int x = 0; x < 2; ++x)
+#pragma unroll
+                                for (int cc = 0; cc < 2; ++cc)
+                                {
+                                    uint4 const w = raw[h][(2 * x + cc) % CHUNKS];
+                                    uint32_t const r[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                    {
+                                        uint32_t q[2];
+                                        cvt_int8x4<T>(r[j], q);
+#pragma unroll
+                                        for (int p = 0; p < 2; ++p) // pair p of register j holds k = 16(2x+cc) + 2j + 8p (+1)
+                                            v[2 * h + x][8 * cc + j + 4 * p]
+                                                = HAS_ZERO ? P::fma(q[p], s2, z2) : P::mul(q[p], s2);
+                                    }
+                                }
+                        }
                     }
                     W4_TC_PHASE(3); // conversion
                     W4_TC_TIMED(5 + 4 * quad, ok = wait_flag_warp(&bars->done[s], ph ^ 1, abort_flag, lane));
@@ -572,9 +609,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                         break;
                     tc_fence_after();
                     W4_TC_PHASE(4); // waited for the TMEM stage
-                    uint32_t const a_addr = lane_addr + kACol0 + s * 32; // warp-uniform column address
-                    tc_st16(a_addr, v[0]);
-                    tc_st16(a_addr + 16, v[1]);
+                    uint32_t const a_addr = lane_addr + kACol0 + s * (32 * kHalves); // warp-uniform column address
+#pragma unroll
+                    for (int x = 0; x < 2 * kHalves; ++x)
+                        tc_st16(a_addr + 16 * x, v[x]);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     tc_fence_before();
                     __syncwarp();
@@ -670,7 +708,7 @@ template <typename T, int BITS, int BM, bool HAS_ZERO>
 static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
 {
     constexpr int IL = BITS == 4 ? 4 : 2;
-    constexpr int STAGE_BYTES = BM * 128 + (BN / IL) * 128;
+    constexpr int STAGE_BYTES = kHalves * (BM * 128 + (BN / IL) * 128);
     auto kernel = gemm_kernel<T, BITS, BM, HAS_ZERO>;
 
     Args a{};
@@ -704,11 +742,11 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
     CUtensorMap tm_act, tm_w;
     CUtensorMapDataType const dt
         = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (!make_tensor_map_2d(&tm_act, dt, act, uint64_t(p.k), uint64_t(p.m), uint64_t(p.k) * 2, BK, BM,
+    if (!make_tensor_map_2d(&tm_act, dt, act, uint64_t(p.k), uint64_t(p.m), uint64_t(p.k) * 2, 64, BM,
             CU_TENSOR_MAP_SWIZZLE_128B))
         return W4_ERR_CUDA;
     if (!make_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.weight, uint64_t(p.k) * 2, uint64_t(p.n / IL),
-            uint64_t(p.k) * 2, 128, BN / IL, CU_TENSOR_MAP_SWIZZLE_NONE))
+            uint64_t(p.k) * 2, 128 * kHalves, BN / IL, CU_TENSOR_MAP_SWIZZLE_NONE))
         return W4_ERR_CUDA;
 
     static bool configured[64] = {};
@@ -734,11 +772,13 @@ static int dispatch_bm(W4GemmParams const& p, void const* act, DeviceInfo const&
         char const* e = getenv("W4_TC_BM"); // tuning aid: force the activation-row tile
         return e ? atoi(e) : 0;
     }();
-    int const bm = bm_override ? bm_override : (p.m <= 64 ? 64 : (p.m <= 128 ? 128 : 256));
+    int const bm = bm_override ? bm_override : gemm_tc_row_tile(p.m, p.n, dev.num_sms);
     if (bm == 64)
         return launch_one<T, BITS, 64, HAS_ZERO>(p, act, dev, stream);
     if (bm == 128)
         return launch_one<T, BITS, 128, HAS_ZERO>(p, act, dev, stream);
+    if (bm == 192)
+        return launch_one<T, BITS, 192, HAS_ZERO>(p, act, dev, stream);
     return launch_one<T, BITS, 256, HAS_ZERO>(p, act, dev, stream);
 }
 
@@ -759,6 +799,49 @@ extern "C" int w4_dbg_read_tc_trace(long long* out)
     return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 192) == cudaSuccess ? 0 : -1;
 }
 #endif
+
+// Microseconds one CTA spends per 128-wide k step, by row tile (measured on B200, bf16 x int4,
+// group 128): up to 192 rows the step is bound by the conversion / hand-off pipeline, not by its
+// tensor work; 256 rows leave shared memory for three stages only and the step turns latency-bound.
+static double step_us(int bm)
+{
+    return bm <= 128 ? 0.645 : (bm == 192 ? 0.70 : 1.06);
+}
+
+static double waves(int m, int n, int bm, int num_sms)
+{
+    long const tiles = long((n + tc::BN - 1) / tc::BN) * long((m + bm - 1) / bm);
+    return double((tiles + num_sms - 1) / num_sms);
+}
+
+int gemm_tc_row_tile(int m, int n, int num_sms)
+{
+    if (m <= 64)
+        return 64;
+    if (m <= 128)
+        return 128;
+    if (m <= 192)
+        return 192;
+    int const cand[3] = {128, 192, 256};
+    int bm = 0;
+    double best = 0;
+    for (int i = 0; i < 3; ++i)
+    {
+        double const cost = waves(m, n, cand[i], num_sms) * step_us(cand[i]);
+        if (!bm || cost < best)
+        {
+            bm = cand[i];
+            best = cost;
+        }
+    }
+    return bm;
+}
+
+double gemm_tc_estimate_us(int m, int n, int k, int num_sms)
+{
+    int const bm = gemm_tc_row_tile(m, n, num_sms);
+    return 7.0 + waves(m, n, bm, num_sms) * step_us(bm) * double((k + tc::BK - 1) / tc::BK);
+}
 
 size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale)
 {

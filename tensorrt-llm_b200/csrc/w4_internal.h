@@ -26,6 +26,10 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
 // tcgen05 tensor-core kernel. Returns a W4Status.
 int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream);
 size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale);
+// Activation-row tile the tensor-core kernel uses for this problem, and its estimated duration
+// (microseconds, measured per-step costs); shared by the launcher and the regime heuristic.
+int gemm_tc_row_tile(int m, int n, int num_sms);
+double gemm_tc_estimate_us(int m, int n, int k, int num_sms);
 
 // out[m, k] = act[m, k] * scale[k], rounded to the element type (the reference's
 // apply_per_channel_scale, cpp/tensorrt_llm/kernels/preQuantScaleKernel.cu:43-95).
