@@ -197,12 +197,25 @@ struct Pair<__half>
     {
         return __half_as_ushort(__float2half_rn(f));
     }
+    // Both halves of a packed pair as floats (low half first).
+    static __device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi)
+    {
+        float2 const f = __half22float2(as(v));
+        lo = f.x;
+        hi = f.y;
+    }
     static __device__ __forceinline__ void mma(float (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1)
     {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    // d = a * b (no accumulator input: starts a chain without zeroing registers first)
+    static __device__ __forceinline__ void mma0(float (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     }
 };
 
@@ -238,13 +251,26 @@ struct Pair<__nv_bfloat16>
     {
         return __bfloat16_as_ushort(__float2bfloat16_rn(f));
     }
+    // Both halves of a packed pair as floats (low half first): two integer ops.
+    static __device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi)
+    {
+        lo = __uint_as_float(v << 16);
+        hi = __uint_as_float(v & 0xffff0000u);
+    }
     static __device__ __forceinline__ void mma(float (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1)
     {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
             "{%0,%1,%2,%3};"
             : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    // d = a * b (no accumulator input: starts a chain without zeroing registers first)
+    static __device__ __forceinline__ void mma0(float (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     }
 };
 

@@ -48,10 +48,17 @@ namespace w4
 namespace gemv
 {
 
-constexpr int kWarps = 16;                      // consumer warps
-constexpr int kConsumerThreads = kWarps * 32;   // 512
-constexpr int kThreads = kConsumerThreads;      // no dedicated producer: see issue_tile()
-constexpr int kRedBytes = 16 * 1024;            // shared memory for cross-warp partial sums
+#ifndef W4_GEMV_WARPS
+#define W4_GEMV_WARPS 16
+#endif
+constexpr int kWarps = W4_GEMV_WARPS;           // consumer warps
+constexpr int kConsumerThreads = kWarps * 32;
+constexpr int kThreads = kConsumerThreads + 128; // + one producer warp group (one lane of it works)
+// Registers: a fifth warp per scheduler would cap every thread at 96 registers; the producer group
+// gives its share back (setmaxnreg) and the consumer groups take it.
+constexpr int kProducerRegs = 24, kConsumerRegs = 112; // 128 * 24 + 512 * 112 <= 640 * 96 (the launch-time pool)
+constexpr int kRedBytes = kWarps * 1024;        // shared memory for cross-warp partial sums
+constexpr int kCtasPerSm = kWarps <= 8 ? 2 : 1; // 8 warps: half an SM, so two launches can overlap
 constexpr int kScaleBoxCols = 24;               // columns per scale/zero box: 16 + slack to start on a 16-byte boundary
 
 template <int BITS, int MB>
@@ -160,7 +167,7 @@ __device__ long long g_trace[16 * 64];
 #define W4_STAMP(slot_)                                                                                                \
     do                                                                                                                 \
     {                                                                                                                  \
-        if (blockIdx.x == 0 && lane == 0 && (slot_) < 64)                                                               \
+        if (blockIdx.x == 0 && lane == 0 && (slot_) < 60 + 4 * ((slot_) >= 60))                                                               \
             g_trace[warp * 64 + (slot_)] = clock64();                                                                  \
     } while (0)
 #else
@@ -173,7 +180,7 @@ __device__ __forceinline__ void prefetch_l2(void const* p)
 }
 
 template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
     gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros)
 {
     using C = Cfg<BITS, MB>;
@@ -201,7 +208,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     // adjacent in the slot so that one bulk copy moves the whole tile.
     int const row_stride = num_panels == 1 ? int(row_bytes) : C::ROW_STRIDE;
 
-    int* next_tile = const_cast<int*>(abort_flag) + 1; // first tile whose copies have not been started
     int const num_tiles = num_cg * num_panels;
 
     // Partial sums in shared memory: [cg in batch][warp][mb][c][g * MT + t], only the lanes whose
@@ -215,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const batch = (red_cap / cbe) * cbe;
 
 
-    // Starts the copies of tile i into its ring slot; called by one thread at a time (see try_issue).
+    // Starts the copies of tile i into its ring slot; called by the producer lane only.
     auto issue_tile = [&](int i, int slot)
     {
         // Tile order: column groups in sub-batches of `cbe`; inside a sub-batch the k panels are
@@ -246,45 +252,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_load_2d(dst + C::TILE_BYTES + a.box_stride, &tm_zeros, col_aligned, grow, &full_bar[slot]);
     };
 
-    // Tile j may start once (a) tile j - depth has fully arrived, so that only `depth` tiles share
-    // the memory pipe and they land in order, early enough to overlap with the arithmetic (the
-    // copy engine serves all outstanding copies side by side: started together they would also all
-    // finish together, at the very end), and (b) every warp has released the tile that used the
-    // slot before. There is no producer warp: lane 0 of every warp calls this at each tile
-    // boundary and while it polls for data; the compare-and-swap picks one issuer per tile.
-    auto try_issue = [&]()
-    {
-        // *next_tile packs the next tile to start, its ring slot and how often that slot has been
-        // used (mod 256): j | slot << 16 | use << 20, so the common "nothing to do" path needs no
-        // division.
-        for (;;)
-        {
-            uint32_t const st = *const_cast<volatile uint32_t*>(reinterpret_cast<uint32_t*>(next_tile));
-            int const j = int(st & 0xffffu), slot = int((st >> 16) & 0xfu), use = int(st >> 20);
-            if (j >= num_tiles)
-                return;
-            if (j >= a.num_slots && !mbar_test_wait(&empty_bar[slot], (use - 1) & 1))
-                return;
-            if (j >= a.depth)
-            {
-                // tile j - depth: `depth` slots back in the ring
-                int const sd = slot >= a.depth ? slot - a.depth : slot - a.depth + a.num_slots;
-                int const ud = slot >= a.depth ? use : use - 1;
-                if (!mbar_test_wait(&full_bar[sd], ud & 1))
-                    return;
-            }
-            bool const wrap = slot + 1 == a.num_slots;
-            uint32_t const nxt = uint32_t(j + 1) | (uint32_t(wrap ? 0 : slot + 1) << 16)
-                | (uint32_t((use + (wrap ? 1 : 0)) & 0xff) << 20);
-            if (atomicCAS(reinterpret_cast<uint32_t*>(next_tile), st, nxt) == st)
-            {
-                if (j >= a.num_slots)
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue_tile(j, slot);
-            }
-        }
-    };
-
     if (tid == 0)
     {
         for (int s = 0; s < a.num_slots; ++s)
@@ -293,7 +260,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&empty_bar[s], kWarps);
         }
         *abort_flag = 0;
-        *next_tile = 0;
         mbar_fence_init();
     }
     else if (tid == 32)
@@ -309,8 +275,46 @@ __global__ void __launch_bounds__(kThreads, 1)
     // SMs free up. Everything up to the activation load touches only weights, scales and zeros,
     // which no earlier kernel writes, so it may run ahead of the kernel before this one.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (tid == 0)
-        try_issue();
+
+    // ---------------------------------------------------------------------- producer
+    // Tile j starts once (a) every consumer warp has released the tile that used its slot before
+    // and (b) tile j - depth has fully arrived: only `depth` tiles share the memory pipe, so they
+    // land in order and early enough to overlap with the arithmetic (the copy engine serves all
+    // outstanding copies side by side: started together they would also all finish together).
+    // The producer touches only weights, scales and zeros, so it does not wait for the preceding
+    // kernel.
+    if (warp >= kWarps)
+    {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProducerRegs));
+        if (warp == kWarps && lane == 0)
+        {
+            int slot = 0, use = 0;
+            for (int j = 0; j < num_tiles; ++j)
+            {
+                if (j >= a.num_slots)
+                {
+                    if (!wait_or_abort(&empty_bar[slot], (use - 1) & 1, abort_flag))
+                        break;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                if (j >= a.depth)
+                {
+                    int const sd = slot >= a.depth ? slot - a.depth : slot - a.depth + a.num_slots;
+                    int const ud = slot >= a.depth ? use : use - 1;
+                    if (!wait_or_abort(&full_bar[sd], ud & 1, abort_flag))
+                        break;
+                }
+                issue_tile(j, slot);
+                if (++slot == a.num_slots)
+                {
+                    slot = 0;
+                    ++use;
+                }
+            }
+        }
+        return;
+    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
 
     // ---------------------------------------------------------------------- consumers
     int const g = lane >> 2, t = lane & 3;
@@ -394,16 +398,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     constexpr uint32_t one = Consts<T>::ONE2;
                     uint32_t const ones[4] = {one, one, one, one};
-                    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                    float sum[2][4]; // two independent chains
 #pragma unroll
                     for (int i = 0; i < C::AREGS / 2; ++i)
                     {
                         // same (b0, b1) pairing as the main loop; any pairing covers all of k once
                         int const lo = BITS == 4 ? (i >> 1) + 8 * (i & 1) : i;
-                        P::mma(sum, ones, afrag[j][mb][lo], afrag[j][mb][lo + 4]);
+                        if (i < 2)
+                            P::mma0(sum[i & 1], ones, afrag[j][mb][lo], afrag[j][mb][lo + 4]);
+                        else
+                            P::mma(sum[i & 1], ones, afrag[j][mb][lo], afrag[j][mb][lo + 4]);
                     }
-                    asum[j][mb][0] = sum[0];
-                    asum[j][mb][1] = sum[1];
+                    asum[j][mb][0] = sum[0][0] + sum[1][0];
+                    asum[j][mb][1] = sum[0][1] + sum[1][1];
                     if (PLANES == 2)
                     {
 #pragma unroll
@@ -434,14 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (FOLD)
         {
             constexpr uint32_t kMagic = F::MAGIC2;
-            float S[2][MB][4]; // two independent accumulation chains
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-                for (int mb = 0; mb < MB; ++mb)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        S[ch][mb][c] = 0.f;
+            float S[2][MB][4]; // two independent accumulation chains, each started by an mma0
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj)
             {
@@ -460,7 +460,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                         uint32_t const frag[4] = {xa[2 * h], xb[2 * h], xa[2 * h + 1], xb[2 * h + 1]};
 #pragma unroll
                         for (int mb = 0; mb < MB; ++mb)
-                            P::mma(S[h][mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
+                        {
+                            if (jj == 0)
+                                P::mma0(S[h][mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
+                            else
+                                P::mma(S[h][mb], frag, afrag[j][mb][jj + 8 * h], afrag[j][mb][jj + 8 * h + 4]);
+                        }
                     }
                 }
                 else if (PLANES == 1)
@@ -469,7 +474,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                         prmt(ra[jj], kMagic, 0x4341u), prmt(rb[jj], kMagic, 0x4341u)};
 #pragma unroll
                     for (int mb = 0; mb < MB; ++mb)
-                        P::mma(S[jj & 1][mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                    {
+                        if (jj < 2)
+                            P::mma0(S[jj & 1][mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                        else
+                            P::mma(S[jj & 1][mb], frag, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                    }
                 }
                 else
                 {
@@ -485,19 +495,24 @@ __global__ void __launch_bounds__(kThreads, 1)
                     {
                         int const jl = PLANES == 2 ? j : 0, ml = PLANES == 2 ? mb : 0;
                         int const i0 = PLANES == 2 ? jj : 0, i1 = PLANES == 2 ? jj + 4 : 0;
-                        P::mma(S[0][mb], lo, afrag_lo[jl][ml][i0], afrag_lo[jl][ml][i1]);
-                        P::mma(S[1][mb], hi, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                        if (jj == 0)
+                        {
+                            P::mma0(S[0][mb], lo, afrag_lo[jl][ml][i0], afrag_lo[jl][ml][i1]);
+                            P::mma0(S[1][mb], hi, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                        }
+                        else
+                        {
+                            P::mma(S[0][mb], lo, afrag_lo[jl][ml][i0], afrag_lo[jl][ml][i1]);
+                            P::mma(S[1][mb], hi, afrag[j][mb][jj], afrag[j][mb][jj + 4]);
+                        }
                     }
                 }
             }
             // scale, zero and magic-constant correction on the fp32 group sums
-            float const sA = P::to_float(uint16_t(s_word & 0xffffu)) , sB = P::to_float(uint16_t(s_word >> 16));
-            float zA = 0.f, zB = 0.f;
+            float sA, sB, zA = 0.f, zB = 0.f;
+            P::unpack2(s_word, sA, sB);
             if (HAS_ZERO)
-            {
-                zA = P::to_float(uint16_t(z_word & 0xffffu));
-                zB = P::to_float(uint16_t(z_word >> 16));
-            }
+                P::unpack2(z_word, zA, zB);
             float const cA = fmaf(-F::CORR, sA, zA), cB = fmaf(-F::CORR, sB, zB);
             float const mA = sA * F::SCALE, mB = sB * F::SCALE;
 #pragma unroll
@@ -593,40 +608,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                     int const cg = cg0 + c0 + ci;
                     if (ok)
                     {
-                        // poll for the tile; while it is not there, help start later tiles
-                        uint32_t polls = 0;
-                        while (!mbar_try_wait(&full_bar[slot], use & 1))
-                        {
-                            if (lane == 0)
-                                try_issue();
-                            if (++polls > kMaxWaitPolls || ((polls & 1023u) == 0 && *abort_flag))
-                            {
-                                ok = false;
-                                *abort_flag = 1;
-                                atomicExch(&g_device_status, kDeviceTimeout);
-                                break;
-                            }
-                        }
+                        ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
                     }
-                    if (lane == 0)
-                        try_issue(); // this tile has arrived: the one `depth` ahead may start
                     uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
-                    W4_STAMP(4 + 3 * tile_index);
+                    W4_STAMP(4 + 2 * tile_index);
 #ifndef W4_DBG_NOCOMPUTE
 #pragma unroll
                     for (int j = 0; j < C::UPW; ++j)
                         process_unit(j, cg, tile, acc[ci]);
 #endif
-                    W4_STAMP(5 + 3 * tile_index);
+                    W4_STAMP(5 + 2 * tile_index);
                     __syncwarp();
-                    W4_STAMP(43 + tile_index);
                     if (lane == 0)
-                    {
                         mbar_arrive(&empty_bar[slot]);
-                        W4_STAMP(50 + tile_index);
-                        try_issue();
-                    }
-                    W4_STAMP(6 + 3 * tile_index);
                     ++tile_index;
                     if (++slot == a.num_slots)
                     {
@@ -653,9 +647,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
 
         // Combine the 16 warps' partial sums in a fixed order and write this batch of columns.
-        W4_STAMP(40);
+        W4_STAMP(60);
         named_bar_sync(1, kConsumerThreads);
-        W4_STAMP(41);
+        W4_STAMP(61);
         constexpr int MPAD = 8 * MB;
         for (int o = tid; o < nb * 16 * MPAD; o += kConsumerThreads)
         {
@@ -680,7 +674,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (cg0 + batch < num_cg)
             named_bar_sync(1, kConsumerThreads);
-        W4_STAMP(42);
+        W4_STAMP(62);
     }
 }
 
@@ -705,7 +699,10 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
     args.slot_bytes = C::TILE_BYTES + 2 * args.box_stride;
     size_t const fixed = kRedBytes + 64;
-    int slots = int((size_t(dev.max_smem_optin) - fixed) / (args.slot_bytes + 16));
+    // Shared memory per CTA: all a block may have, or half of the SM's 228 KB less the 1 KB the
+    // system reserves per block when two CTAs are to fit.
+    size_t const smem_budget = kCtasPerSm == 1 ? size_t(dev.max_smem_optin) : size_t(233472 / 2 - 1024);
+    int slots = int((smem_budget - fixed) / (args.slot_bytes + 16));
     if (slots < 2)
         return W4_ERR_CUDA;
     if (slots > 12)
