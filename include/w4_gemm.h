@@ -68,7 +68,7 @@ extern "C"
     enum
     {
         W4_REGIME_AUTO = 0,
-        W4_REGIME_GEMV = 1, /* streaming decode kernel, any m (re-streams the weights every 16 rows) */
+        W4_REGIME_GEMV = 1, /* streaming decode kernel, any m (re-streams the weights every 8 rows) */
         W4_REGIME_GEMM = 2  /* tcgen05 tensor-core kernel */
     };
 

@@ -163,10 +163,10 @@ extern "C"
         if (m <= 8)
             return W4_REGIME_GEMV; // one pass over the weights
         // Cost model fitted to measurements on B200 (microseconds): the decode kernel makes one
-        // pass over the packed weights per 8 rows at ~1.7 TB/s plus ~4 us; the tensor-core kernel's
+        // pass over the packed weights per 8 rows at ~2.45 TB/s plus ~4.5 us; the tensor-core kernel's
         // estimate comes from its own per-step costs (148 SMs assumed: no device is queried here).
         double const weight_mb = double(n) * double(k) * weight_bits / 8.0 / 1.0e6;
-        double const gemv_us = double((m + 7) / 8) * (weight_mb / 1.7 + 4.0);
+        double const gemv_us = double((m + 7) / 8) * (weight_mb / 2.45 + 4.5);
         double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, 148);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;
     }

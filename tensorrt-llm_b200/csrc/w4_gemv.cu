@@ -1,4 +1,4 @@
-// Decode-regime kernel (m = 1..16 per pass): streams the packed int4/int8 weights exactly once.
+// Decode-regime kernel (m = 1..8 per pass): streams the packed int4/int8 weights exactly once.
 //
 // Replaces weight_only::kernel of the reference project
 // (cpp/tensorrt_llm/kernels/weightOnlyBatchedGemv/kernel.h:31-120) and, for m >= 5 / m >= 16, the
@@ -798,15 +798,14 @@ static int dispatch_panels(Args const& a, DeviceInfo const& dev, cudaStream_t st
 template <typename T>
 static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev, cudaStream_t stream)
 {
+    (void) mb; // only the 8-row variant (MB = 1) is instantiated
     if (bits == 4)
     {
         // A warp unit spans 128 k for int4: the folded arithmetic needs one scale group per unit.
         bool const fold = a.group_shift >= 7;
-        if (fold)
-            return mb == 1 ? dispatch_panels<T, 4, 1, true>(a, dev, stream) : dispatch_panels<T, 4, 2, true>(a, dev, stream);
-        return mb == 1 ? dispatch_panels<T, 4, 1, false>(a, dev, stream) : dispatch_panels<T, 4, 2, false>(a, dev, stream);
+        return fold ? dispatch_panels<T, 4, 1, true>(a, dev, stream) : dispatch_panels<T, 4, 1, false>(a, dev, stream);
     }
-    return mb == 1 ? dispatch_panels<T, 8, 1, true>(a, dev, stream) : dispatch_panels<T, 8, 2, true>(a, dev, stream);
+    return dispatch_panels<T, 8, 1, true>(a, dev, stream);
 }
 
 } // namespace gemv
@@ -824,9 +823,11 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
     if (dev.num_sms <= 0)
         return W4_ERR_CUDA;
     size_t const elt = 2;
-    for (int m0 = 0; m0 < p.m; m0 += 16)
+    // Passes of at most 8 rows: the 16-row variant of the kernel (two B fragments per weight
+    // fragment) measured slower than two 8-row passes on every shape tried, so it is not used.
+    for (int m0 = 0; m0 < p.m; m0 += 8)
     {
-        int const rows = p.m - m0 < 16 ? p.m - m0 : 16;
+        int const rows = p.m - m0 < 8 ? p.m - m0 : 8;
         gemv::Args a{};
         a.weight = static_cast<uint8_t const*>(p.weight);
         a.act = static_cast<char const*>(p.act) + size_t(m0) * p.k * elt;
@@ -842,7 +843,7 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
         a.group_shift = p.group_size == 64 ? 6 : (p.group_size == 128 ? 7 : 31);
         a.num_groups = p.group_size ? p.k / p.group_size : 1;
         a.num_rows = p.n / (p.weight_bits == 4 ? 4 : 2);
-        int const mb = rows <= 8 ? 1 : 2;
+        int const mb = 1;
         int const rc = p.act_dtype == W4_DTYPE_FP16 ? gemv::dispatch_bits<__half>(a, p.weight_bits, mb, dev, stream)
                                                     : gemv::dispatch_bits<__nv_bfloat16>(a, p.weight_bits, mb, dev, stream);
         if (rc != W4_OK)

@@ -20,7 +20,7 @@ struct DeviceInfo
 // Cached per-device properties of the current device (thread-safe, no allocation).
 DeviceInfo const& current_device_info();
 
-// Streaming decode kernel: handles any m by passes of at most 16 rows. Returns a W4Status.
+// Streaming decode kernel: handles any m by passes of at most 8 rows. Returns a W4Status.
 int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
 
 // tcgen05 tensor-core kernel. Returns a W4Status.
