@@ -6,13 +6,16 @@
 //
 // Design (B200): one persistent CTA per SM owns a contiguous range of "interleaved rows" of the
 // preprocessed weight (one interleaved row = IL adjacent output columns x all of K = 2K bytes, see
-// below), so every CTA streams one contiguous slab of HBM. A producer warp moves that slab into a
-// shared-memory ring with bulk (TMA-engine) copies, ~190 KB in flight per SM from the first cycle
-// (its spare lanes prefetch the CTA's scale/zero lines into L2); 16 consumer warps split K, pull
-// 16-byte chunks out of the ring with 128-bit shared loads and feed mma.sync (weights as the 16-row
-// A operand, the m <= 8 activation rows as the 8-column B operand), accumulating in fp32. Partial
-// sums of the 16 warps are combined through shared memory in a fixed order (deterministic) once
-// per batch of column groups, then alpha/bias are applied and the result stored.
+// below), so every CTA streams one contiguous slab of HBM. One lane of a producer warp group moves
+// that slab into a shared-memory ring with bulk (TMA-engine) copies, one tile (16 columns x one k
+// panel, with its scale/zero boxes) at a time, a bounded number of tiles in flight so that they
+// land in order; 16 consumer warps split K, pull 16-byte chunks out of the ring with 128-bit shared
+// loads and feed mma.sync (weights as the 16-row A operand, the m <= 8 activation rows as the
+// 8-column B operand, held in registers), accumulating in fp32. The producer group hands most of
+// its registers to the consumers (setmaxnreg). Partial sums of the 16 warps are combined through
+// shared memory in a fixed order (deterministic) once per batch of column groups, then alpha/bias
+// are applied and the result stored. The kernel is launched as a programmatic dependent: weight
+// copies start before the preceding kernel has finished, activations are read after it.
 //
 // Weight layout consumed (preprocess_weights_for_mixed_gemm on sm_100,
 // cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:564-615): interleaved row R
