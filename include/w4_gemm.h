@@ -26,6 +26,10 @@
  *   w4_symmetric_quantize    - symmetric_quantize<ComputeType, WeightType>
  *                              (cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:652-762).
  *   w4_preprocess_weights    - preprocess_weights_for_mixed_gemm (cutlass_preprocessors.cpp:564-615).
+ *   w4_preprocess_weights_device / w4_symmetric_quantize_device
+ *                            - the same two functions as CUDA kernels on device buffers (the
+ *                              reference runs them on one CPU thread only,
+ *                              cutlass_preprocessors.cpp:685-758); byte-identical results.
  *   w4_pack_int4 / w4_unpack_int4
  *                            - pack_int8_tensor_to_packed_int4 / unpack_int4_packed_tensor_to_int8
  *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:284-353).
@@ -61,7 +65,8 @@ extern "C"
     enum
     {
         W4_DTYPE_FP16 = 0,
-        W4_DTYPE_BF16 = 1
+        W4_DTYPE_BF16 = 1,
+        W4_DTYPE_FP32 = 2 /* only as the source type of w4_symmetric_quantize_device */
     };
 
     /* Which kernel family runs. AUTO applies w4_gemm_select_regime(). */
@@ -176,6 +181,20 @@ extern "C"
 
     int w4_pack_int4(int8_t* packed, const int8_t* unpacked, size_t num_packed_bytes);
     void w4_unpack_int4(int8_t* unpacked, const int8_t* packed, size_t num_packed_bytes);
+
+    /* ---- the same weight preparation on the GPU (device pointers, stream-ordered, no allocation) ---- */
+
+    /* in / out: [k, n*bits/8] bytes on the device, 16-byte aligned, out != in. Same bytes as
+     * w4_preprocess_weights. */
+    int w4_preprocess_weights_device(void* out, const void* in, size_t k, size_t n, int bits, void* stream);
+
+    /* weight: [k, n] row-major on the device, weight_dtype = W4_DTYPE_FP32 / FP16 / BF16 (the
+     * reference's ComputeType). processed (mandatory) and unprocessed (optional) as in
+     * w4_symmetric_quantize; scales: fp32 [n] (mandatory, also used as scratch for the column
+     * maxima); scales_t: optional copy rounded to scales_dtype (fp16 / bf16), which is what the
+     * GEMM takes. Same bytes and scale values as the host function. */
+    int w4_symmetric_quantize_device(void* processed, void* unprocessed, float* scales, void* scales_t,
+        int scales_dtype, const void* weight, int weight_dtype, size_t k, size_t n, int bits, void* stream);
 
 #ifdef __cplusplus
 }

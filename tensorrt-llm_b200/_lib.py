@@ -12,6 +12,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libw4gemm.so")
 
 W4_OK = 0
+W4_ERR_NULL_POINTER, W4_ERR_BAD_SHAPE, W4_ERR_BAD_GROUP, W4_ERR_BAD_DTYPE, W4_ERR_MISALIGNED = -1, -2, -3, -4, -5
+W4_ERR_UNSUPPORTED, W4_ERR_WORKSPACE, W4_ERR_CUDA, W4_ERR_BAD_REGIME = -6, -7, -8, -9
 W4_DTYPE_FP16, W4_DTYPE_BF16 = 0, 1
 W4_REGIME_AUTO, W4_REGIME_GEMV, W4_REGIME_GEMM = 0, 1, 2
 # quant_algo bits of the groupwise plugin
@@ -21,6 +23,7 @@ EXPORTS = (
     "w4_gemm_version", "w4_status_string", "w4_gemm_validate", "w4_gemm_launch", "w4_gemm_workspace_bytes",
     "w4_gemm_select_regime", "w4_gemm_device_status", "w4_symmetric_quantize", "w4_preprocess_weights",
     "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
+    "w4_preprocess_weights_device", "w4_symmetric_quantize_device",
 )
 
 
@@ -65,6 +68,11 @@ def lib() -> ctypes.CDLL:
                                             ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]
         l.w4_preprocess_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,
                                             ctypes.c_int]
+        l.w4_preprocess_weights_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                                   ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        l.w4_symmetric_quantize_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                   ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                   ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         l.w4_pack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.restype = None

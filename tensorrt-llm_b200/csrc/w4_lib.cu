@@ -4,3 +4,4 @@
 #include "w4_gemm_tc.cu"
 #include "w4_api.cu"
 #include "w4_static_scratch.cu"
+#include "w4_prep_gpu.cu"

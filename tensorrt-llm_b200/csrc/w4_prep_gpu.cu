@@ -1,0 +1,266 @@
+// Device-side weight preparation: per-column symmetric quantisation and the layout transform the
+// GEMM kernels consume, as CUDA kernels. The reference project does both on one CPU thread
+// (cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:564-615 and 652-762); the
+// bytes produced here are identical to its output on compute capability 10.x (and to the host
+// functions w4_preprocess_weights / w4_symmetric_quantize of this library).
+//
+// HBM-bound byte work. One CTA turns a tile of 64 k rows x 256 input bytes (512 int4 or 256 int8
+// columns) into 128 output lines of 128 bytes: the rows are read with coalesced 16-byte loads into
+// shared memory, every thread then builds output registers from the closed form of the four
+// reference passes (row permutation inside 16/32-row blocks, sub-byte transpose, column
+// interleave in 64-k tiles, bias + in-register shuffle) and a warp writes one whole output line
+// per store instruction.
+#include "w4_common.cuh"
+#include "w4_internal.h"
+
+namespace w4
+{
+namespace prep
+{
+
+constexpr int kTileK = 64;        // rows per tile: one interleave tile
+constexpr int kTileBytes = 256;   // input bytes per row per tile
+constexpr int kThreads = 256;
+constexpr int kSmemPitch = kTileBytes + 16; // padded row pitch of the staged tile
+
+__constant__ uint8_t c_perm8[16] = {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15};
+__constant__ uint8_t c_perm4[32] = {0, 1, 8, 9, 16, 17, 24, 25, 2, 3, 10, 11, 18, 19, 26, 27, 4, 5, 12, 13, 20, 21,
+    28, 29, 6, 7, 14, 15, 22, 23, 30, 31};
+
+// Output stage shared by both kernels: `tile` holds 64 rows of two's-complement weights (int4: two
+// per byte, even column in the low nibble) for `cols` columns starting at column n0.
+template <int BITS>
+__device__ __forceinline__ void emit_tile(uint32_t* out, uint8_t const* tile, int k_tile, int n0, int cols, int K)
+{
+    constexpr int E = 32 / BITS;           // elements per 32-bit register
+    constexpr int VT = 64 / E;             // registers per 64-k tile of one column
+    constexpr int IL = BITS == 8 ? 2 : 4;  // interleaved columns
+    constexpr int GP = BITS == 8 ? 16 : 32;
+    int const irows = cols / IL;
+    size_t const regs_per_irow = size_t(K / E) * IL;
+    for (int r = threadIdx.x; r < irows * 32; r += kThreads)
+    {
+        int const line = r >> 5, within = r & 31; // one 128-byte line = 32 registers = VT * IL
+        int const nl = line * IL + within / VT;   // column inside the tile
+        int const vr = within % VT;               // register of that column inside the k tile
+        uint32_t word = 0;
+#pragma unroll
+        for (int d = 0; d < E; ++d)
+        {
+            int const s = BITS == 4 ? (d < 4 ? 2 * d : 2 * (d - 4) + 1) : (d == 1 ? 2 : (d == 2 ? 1 : d));
+            int const kp = vr * E + s;
+            int const kl = (kp / GP) * GP + (BITS == 8 ? c_perm8[kp % GP] : c_perm4[kp % GP]);
+            uint32_t u;
+            if (BITS == 8)
+                u = uint8_t(int(int8_t(tile[kl * kSmemPitch + nl])) + 128);
+            else
+            {
+                uint8_t const b = tile[kl * kSmemPitch + (nl >> 1)];
+                u = (((nl & 1) ? (b >> 4) : b) + 8u) & 0xFu; // sign-extended nibble + 8 == (nibble + 8) mod 16
+            }
+            word |= u << (BITS * d);
+        }
+        size_t const irow = size_t(n0 / IL + line);
+        out[irow * regs_per_irow + size_t(k_tile) * 32 + within] = word;
+    }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kThreads) preprocess_kernel(uint32_t* out, uint8_t const* in, int K, int N)
+{
+    __shared__ __align__(16) uint8_t tile[kTileK * kSmemPitch];
+    int const row_bytes = N * BITS / 8;
+    int const b0 = blockIdx.x * kTileBytes;
+    int const nbytes = min(kTileBytes, row_bytes - b0);
+    int const k_tile = blockIdx.y;
+    // 64 rows x nbytes, 16 bytes per thread and step (row_bytes is a multiple of 32)
+    for (int i = threadIdx.x; i < kTileK * (kTileBytes / 16); i += kThreads)
+    {
+        int const r = i / (kTileBytes / 16), c = (i % (kTileBytes / 16)) * 16;
+        if (c < nbytes)
+            *reinterpret_cast<uint4*>(tile + r * kSmemPitch + c)
+                = *reinterpret_cast<uint4 const*>(in + size_t(k_tile * kTileK + r) * row_bytes + b0 + c);
+    }
+    __syncthreads();
+    emit_tile<BITS>(out, tile, k_tile, b0 * 8 / BITS, nbytes * 8 / BITS, K);
+}
+
+template <typename W>
+__device__ __forceinline__ float to_f32(W v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v)
+{
+    return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v)
+{
+    return __bfloat162float(v);
+}
+
+// Per-column max |w| over a slab of rows; non-negative floats order like their bit patterns, so
+// the slabs are merged with an integer atomic max (the result does not depend on the order).
+template <typename W>
+__global__ void __launch_bounds__(256) column_amax_kernel(float* amax, W const* w, int K, int N, int rows_per_block)
+{
+    int const c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= N)
+        return;
+    int const r0 = blockIdx.y * rows_per_block, r1 = min(K, r0 + rows_per_block);
+    float m = 0.f;
+    for (int r = r0; r < r1; ++r)
+        m = fmaxf(m, fabsf(to_f32(w[size_t(r) * N + c])));
+    atomicMax(reinterpret_cast<int*>(amax) + c, __float_as_int(m));
+}
+
+// amax -> scale = amax * 2^-(bits-1), in place, plus the copy rounded to the activation type.
+__global__ void finish_scales_kernel(float* scales, void* scales_t, int scales_dtype, int N, float range)
+{
+    int const c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= N)
+        return;
+    float const s = scales[c] * range;
+    scales[c] = s;
+    if (scales_t)
+    {
+        if (scales_dtype == W4_DTYPE_FP16)
+            static_cast<__half*>(scales_t)[c] = __float2half_rn(s);
+        else
+            static_cast<__nv_bfloat16*>(scales_t)[c] = __float2bfloat16_rn(s);
+    }
+}
+
+// Quantises a tile (q = clamp(int(round(w / scale))), round half away from zero, zero column -> 0),
+// optionally stores it row-major (the reference's "unprocessed" output) and emits the kernel layout.
+template <typename W, int BITS>
+__global__ void __launch_bounds__(kThreads)
+    quantize_kernel(uint32_t* out, uint8_t* unprocessed, W const* w, float const* scales, int K, int N)
+{
+    __shared__ __align__(16) uint8_t tile[kTileK * kSmemPitch];
+    constexpr int kCols = kTileBytes * 8 / BITS; // columns per tile
+    constexpr int kPer = 8 / BITS;               // columns per stored byte
+    int const row_bytes = N * BITS / 8;
+    int const n0 = blockIdx.x * kCols;
+    int const cols = min(kCols, N - n0);
+    int const k_tile = blockIdx.y;
+    int const lo = BITS == 8 ? -128 : -8, hi = BITS == 8 ? 127 : 7;
+    for (int i = threadIdx.x; i < kTileK * kTileBytes; i += kThreads)
+    {
+        int const r = i / kTileBytes, b = i % kTileBytes; // consecutive threads: consecutive bytes of a row
+        if (b * kPer < cols)
+        {
+            uint32_t byte = 0;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e)
+            {
+                int const c = n0 + b * kPer + e;
+                float const s = scales[c];
+                float const x = to_f32(w[size_t(k_tile * kTileK + r) * N + c]);
+                float const v = s != 0.f ? roundf(__fdiv_rn(x, s)) : 0.f;
+                int const iv = max(lo, min(hi, int(v)));
+                byte |= (uint32_t(iv) & (BITS == 8 ? 0xFFu : 0xFu)) << (BITS * e);
+            }
+            tile[r * kSmemPitch + b] = uint8_t(byte);
+            if (unprocessed)
+                unprocessed[size_t(k_tile * kTileK + r) * row_bytes + n0 / kPer + b] = uint8_t(byte);
+        }
+    }
+    __syncthreads();
+    emit_tile<BITS>(out, tile, k_tile, n0, cols, K);
+}
+
+bool shape_ok(long k, long n, int bits)
+{
+    return k > 0 && n > 0 && k % 64 == 0 && (n * bits / 8) % 32 == 0 && (k * bits / 8) % 32 == 0
+        && k < (1l << 31) && n < (1l << 31);
+}
+
+template <typename W>
+int quantize_typed(void* processed, void* unprocessed, float* scales, void* scales_t, int scales_dtype, W const* w,
+    int k, int n, int bits, cudaStream_t stream)
+{
+    if (cudaMemsetAsync(scales, 0, size_t(n) * sizeof(float), stream) != cudaSuccess)
+        return W4_ERR_CUDA;
+    int const rows_per_block = 256;
+    dim3 const ga((n + 255) / 256, (k + rows_per_block - 1) / rows_per_block);
+    column_amax_kernel<W><<<ga, 256, 0, stream>>>(scales, w, k, n, rows_per_block);
+    finish_scales_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scales, scales_t, scales_dtype, n,
+        1.f / float(1 << (bits - 1)));
+    int const cols_per_tile = kTileBytes * 8 / bits;
+    dim3 const gq((n + cols_per_tile - 1) / cols_per_tile, k / kTileK);
+    if (bits == 4)
+        quantize_kernel<W, 4><<<gq, kThreads, 0, stream>>>(static_cast<uint32_t*>(processed),
+            static_cast<uint8_t*>(unprocessed), w, scales, k, n);
+    else
+        quantize_kernel<W, 8><<<gq, kThreads, 0, stream>>>(static_cast<uint32_t*>(processed),
+            static_cast<uint8_t*>(unprocessed), w, scales, k, n);
+    return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
+}
+
+} // namespace prep
+} // namespace w4
+
+extern "C"
+{
+
+    int w4_preprocess_weights_device(void* out, const void* in, size_t k, size_t n, int bits, void* stream)
+    {
+        using namespace w4::prep;
+        if (!out || !in)
+            return W4_ERR_NULL_POINTER;
+        if (bits != 4 && bits != 8)
+            return W4_ERR_BAD_DTYPE;
+        if (!shape_ok(long(k), long(n), bits))
+            return W4_ERR_BAD_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 15u)
+            return W4_ERR_MISALIGNED;
+        if (out == in)
+            return W4_ERR_UNSUPPORTED; // not an in-place transform
+        cudaStream_t const s = static_cast<cudaStream_t>(stream);
+        int const row_bytes = int(n) * bits / 8;
+        dim3 const grid((row_bytes + kTileBytes - 1) / kTileBytes, unsigned(k) / kTileK);
+        if (bits == 4)
+            preprocess_kernel<4><<<grid, kThreads, 0, s>>>(static_cast<uint32_t*>(out),
+                static_cast<uint8_t const*>(in), int(k), int(n));
+        else
+            preprocess_kernel<8><<<grid, kThreads, 0, s>>>(static_cast<uint32_t*>(out),
+                static_cast<uint8_t const*>(in), int(k), int(n));
+        return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
+    }
+
+    int w4_symmetric_quantize_device(void* processed, void* unprocessed, float* scales, void* scales_t,
+        int scales_dtype, const void* weight, int weight_dtype, size_t k, size_t n, int bits, void* stream)
+    {
+        using namespace w4::prep;
+        if (!processed || !scales || !weight)
+            return W4_ERR_NULL_POINTER;
+        if (bits != 4 && bits != 8)
+            return W4_ERR_BAD_DTYPE;
+        if (scales_t && scales_dtype != W4_DTYPE_FP16 && scales_dtype != W4_DTYPE_BF16)
+            return W4_ERR_BAD_DTYPE;
+        if (!shape_ok(long(k), long(n), bits))
+            return W4_ERR_BAD_SHAPE;
+        if (reinterpret_cast<uintptr_t>(processed) & 15u)
+            return W4_ERR_MISALIGNED;
+        cudaStream_t const s = static_cast<cudaStream_t>(stream);
+        switch (weight_dtype)
+        {
+        case W4_DTYPE_FP32:
+            return quantize_typed(processed, unprocessed, scales, scales_t, scales_dtype,
+                static_cast<float const*>(weight), int(k), int(n), bits, s);
+        case W4_DTYPE_FP16:
+            return quantize_typed(processed, unprocessed, scales, scales_t, scales_dtype,
+                static_cast<__half const*>(weight), int(k), int(n), bits, s);
+        case W4_DTYPE_BF16:
+            return quantize_typed(processed, unprocessed, scales, scales_t, scales_dtype,
+                static_cast<__nv_bfloat16 const*>(weight), int(k), int(n), bits, s);
+        default: return W4_ERR_BAD_DTYPE;
+        }
+    }
+
+} // extern "C"

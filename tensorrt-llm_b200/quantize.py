@@ -1,6 +1,8 @@
 """Host-side weight preparation ops with the reference's names, arguments and error behaviour
 (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:123-353 of TensorRT-LLM). They run on CPU tensors,
-as the reference's do, through the C ABI of libw4gemm.so.
+as the reference's do, through the C ABI of libw4gemm.so. The two ``*_cuda`` functions at the end
+are additions without a reference counterpart: the same preparation on CUDA tensors (CUDA kernels,
+byte-identical results), for loaders that already hold the checkpoint on the GPU.
 """
 from __future__ import annotations
 
@@ -115,3 +117,62 @@ def pack_int8_tensor_to_packed_int4(weight: torch.Tensor) -> torch.Tensor:
     if rc != _lib.W4_OK:
         raise RuntimeError("Value in unpacked tensor not in int4 range")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU-side preparation (no reference counterpart: the reference prepares weights on the CPU only)
+# ---------------------------------------------------------------------------------------------
+_W_DTYPES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _check_cuda_contiguous(t: torch.Tensor, name: str):
+    if t.device.type != "cuda":
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def preprocess_weights_for_mixed_gemm_cuda(row_major_quantized_weight: torch.Tensor, quant_type) -> torch.Tensor:
+    """preprocess_weights_for_mixed_gemm on a CUDA int8 tensor [K, N*bits/8] (2-D); same bytes."""
+    t = row_major_quantized_weight
+    _check_cuda_contiguous(t, "row_major_quantized_weight")
+    if t.dtype != torch.int8:
+        raise RuntimeError("Quantized tensor must be int8 dtype")
+    if t.dim() != 2:
+        raise RuntimeError("Invalid dim. The dim of weight should be 2")
+    bits = _bits(quant_type)
+    out = torch.empty_like(t)
+    with torch.cuda.device(t.device):
+        rc = _lib.lib().w4_preprocess_weights_device(_ptr(out), _ptr(t), t.shape[0], t.shape[1] * 8 // bits, bits,
+                                                     _stream(t))
+    _lib.check(rc, "preprocess_weights_for_mixed_gemm_cuda")
+    return out
+
+
+def symmetric_quantize_last_axis_of_batched_matrix_cuda(weight: torch.Tensor, quant_type,
+                                                         return_unprocessed: bool = False):
+    """symmetric_quantize on a CUDA tensor [K, N] (fp32 / fp16 / bf16):
+    -> [processed, scales] or [unprocessed, processed, scales], scales in weight.dtype."""
+    _check_cuda_contiguous(weight, "weight")
+    if weight.dim() != 2 or weight.numel() == 0:
+        raise RuntimeError("Invalid dim. The dim of weight should be 2")
+    if weight.dtype not in _W_DTYPES:
+        raise RuntimeError("Invalid datatype. Weight must be FP16 or BF16")
+    bits = _bits(quant_type)
+    k, n = weight.shape
+    processed = torch.empty((k, n * bits // 8), dtype=torch.int8, device=weight.device)
+    unprocessed = torch.empty_like(processed) if return_unprocessed else None
+    scales = torch.empty((n,), dtype=torch.float32, device=weight.device)
+    scales_t = None if weight.dtype == torch.float32 else torch.empty((n,), dtype=weight.dtype, device=weight.device)
+    with torch.cuda.device(weight.device):
+        rc = _lib.lib().w4_symmetric_quantize_device(
+            _ptr(processed), _ptr(unprocessed) if unprocessed is not None else None, _ptr(scales),
+            _ptr(scales_t) if scales_t is not None else None, _W_DTYPES.get(weight.dtype, 0) if scales_t is not None
+            else 0, _ptr(weight), _W_DTYPES[weight.dtype], k, n, bits, _stream(weight))
+    _lib.check(rc, "symmetric_quantize_last_axis_of_batched_matrix_cuda")
+    s = scales if scales_t is None else scales_t
+    return [unprocessed, processed, s] if return_unprocessed else [processed, s]

@@ -1,0 +1,86 @@
+"""GPU: device-side quantise / layout kernels (w4_preprocess_weights_device,
+w4_symmetric_quantize_device) through the C ABI, byte for byte against the oracle, the committed
+golden vectors made from the reference's own code, and the host functions of the library."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import woq_oracle as o
+import tensorrt_llm_b200 as pkg
+from tensorrt_llm_b200 import quantize as Q
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "quant_*.npz")))
+_DT = {"torch.float32": torch.float32, "torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16}
+_QT = {8: torch.int8, 4: torch.quint4x2}
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_golden_vectors(path):
+    g = np.load(path)
+    dt = _DT[str(g["dtype"])]
+    w = torch.from_numpy(g["weight_f32"]).to(dt).cuda()
+    for bits in (8, 4):
+        u, p, s = Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w, _QT[bits], return_unprocessed=True)
+        assert np.array_equal(u.cpu().numpy(), g[f"unprocessed_int{bits}"])
+        assert np.array_equal(p.cpu().numpy(), g[f"processed_int{bits}"])
+        assert s.dtype == dt
+        assert np.array_equal(s.float().cpu().numpy(), g[f"scales_int{bits}_f32"])
+        raw = torch.from_numpy(g[f"raw_int{bits}"]).cuda()
+        out = Q.preprocess_weights_for_mixed_gemm_cuda(raw, _QT[bits])
+        assert np.array_equal(out.cpu().numpy(), g[f"raw_processed_int{bits}"])
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("k,n", [(64, 64), (64, 576), (192, 1088), (4096, 14336), (8192, 4096)])
+def test_preprocess_matches_oracle(bits, k, n):
+    rng = np.random.default_rng(k + n + bits)
+    q = rng.integers(-128, 128, size=(k, n * bits // 8), dtype=np.int8)
+    out = Q.preprocess_weights_for_mixed_gemm_cuda(torch.from_numpy(q).cuda(), _QT[bits])
+    assert np.array_equal(out.cpu().numpy(), o.preprocess_weights(q, bits))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("k,n", [(64, 64), (320, 704), (4096, 4096)])
+def test_quantize_matches_oracle(bits, dtype, k, n):
+    torch.manual_seed(k * 7 + n + bits)
+    w = (torch.randn(k, n) * 0.02).to(dtype)
+    w[:, 3] = 0  # a zero column: scale 0, q = 0
+    w[5, 7] = w[:, 7].abs().max() * 2  # a clear column maximum
+    u_ref, p_ref, s_ref = o.symmetric_quantize(w, bits)
+    u, p, s = Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w.cuda(), _QT[bits], return_unprocessed=True)
+    assert torch.equal(u.cpu(), u_ref)
+    assert torch.equal(p.cpu(), p_ref)
+    assert torch.equal(s.cpu().float(), s_ref.float())
+    # and the library's own host path (what a CPU caller gets)
+    p_host, s_host = Q.symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
+    assert torch.equal(p.cpu(), p_host) and torch.equal(s.cpu(), s_host)
+
+
+def test_round_trip_through_gemm():
+    """Weights prepared on the GPU feed the GEMM and give the oracle's result."""
+    from _cases import max_err
+    torch.manual_seed(11)
+    k, n, m = 4096, 4096, 4
+    w = (torch.randn(k, n) * 0.02).to(torch.float16)
+    p, s = Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w.cuda(), torch.int8)
+    act = torch.randn(m, k, dtype=torch.float16, device="cuda")
+    out = pkg.ops.weight_only_quant_matmul(act, p, s, 1)
+    u_ref, _, s_ref = o.symmetric_quantize(w, 8)
+    ref = act.float().cpu() @ (u_ref.float() * s_ref.float()[None, :])
+    assert max_err(out.float().cpu(), ref) <= 1e-2 * ref.abs().max()
+
+
+def test_error_codes():
+    lib = pkg._lib.lib()
+    a = torch.zeros(64, 32, dtype=torch.int8, device="cuda")
+    b = torch.zeros_like(a)
+    assert lib.w4_preprocess_weights_device(None, a.data_ptr(), 64, 64, 4, None) == pkg._lib.W4_ERR_NULL_POINTER
+    assert lib.w4_preprocess_weights_device(b.data_ptr(), a.data_ptr(), 64, 64, 5, None) == pkg._lib.W4_ERR_BAD_DTYPE
+    assert lib.w4_preprocess_weights_device(b.data_ptr(), a.data_ptr(), 48, 64, 4, None) == pkg._lib.W4_ERR_BAD_SHAPE
+    assert lib.w4_preprocess_weights_device(a.data_ptr(), a.data_ptr(), 64, 64, 4, None) == pkg._lib.W4_ERR_UNSUPPORTED
