@@ -30,6 +30,10 @@
  *                            - the same two functions as CUDA kernels on device buffers (the
  *                              reference runs them on one CPU thread only,
  *                              cutlass_preprocessors.cpp:685-758); byte-identical results.
+ *   w4_allreduce_oneshot     - the ncclAllReduce that follows the plugin in a row-parallel layer
+ *                              (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407), for
+ *                              latency-bound message sizes, as a peer-memory kernel in the manner of
+ *                              oneShotAllReduceKernel (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307).
  *   w4_pack_int4 / w4_unpack_int4
  *                            - pack_int8_tensor_to_packed_int4 / unpack_int4_packed_tensor_to_int8
  *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:284-353).
@@ -195,6 +199,43 @@ extern "C"
      * GEMM takes. Same bytes and scale values as the host function. */
     int w4_symmetric_quantize_device(void* processed, void* unprocessed, float* scales, void* scales_t,
         int scales_dtype, const void* weight, int weight_dtype, size_t k, size_t n, int bits, void* stream);
+
+    /* ---- row-parallel reduce over peer memory (one process per GPU, one node) ---- */
+
+#define W4_MAX_RANKS 8
+#define W4_ONESHOT_MAX_BYTES (1u << 20) /* larger messages are bandwidth-bound: use the library collective */
+
+    /*
+     * out[i] = sum over ranks r = 0..world-1 (in that order, fp32) of partials[r][i]  (+ bias[i % n])
+     *
+     *   partials[r]  rank r's [count] partial sums (fp16 / bf16) as mapped into THIS process: the
+     *                local buffer for r == rank, a peer mapping (CUDA IPC / symmetric memory) else.
+     *                The local GEMM writes partials[rank] directly (pass it as W4GemmParams.out).
+     *   flags[r]     rank r's W4_MAX_RANKS 32-bit flag words, mapped the same way; zero before the
+     *                first call (and all ranks must have seen the zeroing before anyone calls).
+     *   epoch        call number: 1 for the first call, +1 for every call, the same on every rank.
+     *                Alternate between two partial buffers from call to call.
+     *   timeout_ms   bound on the wait for the peers (0 = 2000). When it expires the kernel leaves
+     *                `out` untouched and w4_gemm_device_status() returns W4_ERR_DEVICE_TIMEOUT.
+     * count % 8 == 0, n % 8 == 0, count % n == 0, count * 2 <= W4_ONESHOT_MAX_BYTES, all data
+     * pointers 16-byte aligned. Stream-ordered after the GEMM that produced partials[rank];
+     * allocates nothing.
+     */
+    typedef struct W4AllReduceParams
+    {
+        const void* partials[W4_MAX_RANKS];
+        uint32_t* flags[W4_MAX_RANKS];
+        const void* bias; /* optional, [n] */
+        void* out;        /* local, [count] */
+        size_t count;
+        int n;
+        int rank, world;
+        int act_dtype; /* W4_DTYPE_FP16 / W4_DTYPE_BF16 */
+        uint32_t epoch;
+        uint32_t timeout_ms;
+    } W4AllReduceParams;
+
+    int w4_allreduce_oneshot(const W4AllReduceParams* p, void* stream);
 
 #ifdef __cplusplus
 }

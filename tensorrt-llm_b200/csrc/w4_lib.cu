@@ -5,3 +5,4 @@
 #include "w4_api.cu"
 #include "w4_static_scratch.cu"
 #include "w4_prep_gpu.cu"
+#include "w4_allreduce.cu"

@@ -70,7 +70,7 @@ def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, grou
     _lib.check(rc, "w4_gemm_launch")
 
 
-def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime):
+def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime, out=None):
     for name, t in (("act", act), ("weight", weight), ("scales", scales)):
         _require_cuda(t, name)
     if act.dtype not in _DTYPES:
@@ -86,8 +86,11 @@ def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_
     if weight.dim() != 2 or weight.shape[0] != k:
         raise RuntimeError("weight must be 2-D with K rows")
     n = row_bytes * 8 // weight_bits
-    out = torch.empty(act.shape[:-1] + (n,), dtype=act.dtype, device=act.device)
     m = act.numel() // k
+    if out is None:
+        out = torch.empty(act.shape[:-1] + (n,), dtype=act.dtype, device=act.device)
+    elif out.dtype != act.dtype or out.numel() != m * n or not out.is_contiguous() or out.device != act.device:
+        raise RuntimeError("out must be a contiguous [.., N] tensor of the activation dtype on the same device")
     if m == 0:
         return out
     ws_bytes = workspace_bytes(m, n, k, group_size, weight_bits, act.dtype, act_scale is not None, regime)
@@ -109,7 +112,7 @@ def weight_only_quant_matmul(act: torch.Tensor, weight: torch.Tensor, scales: to
 
 def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zeros, bias, alpha: float,
                                        quant_algo: int, group_size: int,
-                                       regime: int = W4_REGIME_AUTO) -> torch.Tensor:
+                                       regime: int = W4_REGIME_AUTO, out=None) -> torch.Tensor:
     """Groupwise W4A16 / W8A16 (GPTQ / AWQ). quant_algo bits: 1 bias, 2 zero, 4 pre-quant scale,
     8 fp8 alpha (W4A8, not supported), 16 int8 weight. Optional tensors must be present exactly
     when their bit is set. The weight may be viewed as the activation dtype, as the plugin takes it."""
@@ -122,7 +125,7 @@ def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zer
         if bool(quant_algo & bit) != (t is not None):
             raise RuntimeError(f"{name} must be given exactly when its quant_algo bit is set")
     bits = 8 if quant_algo & INT8_WEIGHT else 4
-    return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime)
+    return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime, out)
 
 
 class _PluginBase:
@@ -279,3 +282,26 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
         self = cls(t, q, g, al)
         self.dims = (a, b, c, d)
         return self
+
+
+def allreduce_oneshot(partial_ptrs, flag_ptrs, out: torch.Tensor, n: int, rank: int, epoch: int, bias=None,
+                      timeout_ms: int = 0, stream=None) -> None:
+    """out = sum over ranks (rank order, fp32) of the [count] partials behind ``partial_ptrs`` (+ bias).
+    ``partial_ptrs[r]`` / ``flag_ptrs[r]``: device addresses of rank r's partial buffer and flag
+    words as mapped into this process (see ``tp.OneShotAllReduce``). Mirrors the custom all-reduce the
+    reference uses behind dense row-parallel layers (kernels/customAllReduceKernels.cu:1307)."""
+    world = len(partial_ptrs)
+    if world != len(flag_ptrs) or not 1 <= world <= _lib.W4_MAX_RANKS:
+        raise RuntimeError("allreduce_oneshot: need 1..8 ranks and as many flag pointers as partial pointers")
+    p = _lib.W4AllReduceParams()
+    for r in range(world):
+        p.partials[r] = int(partial_ptrs[r])
+        p.flags[r] = int(flag_ptrs[r])
+    p.bias = bias.data_ptr() if bias is not None else None
+    p.out = out.data_ptr()
+    p.count, p.n, p.rank, p.world = out.numel(), n, rank, world
+    p.act_dtype, p.epoch, p.timeout_ms = _DTYPES[out.dtype], epoch & 0xFFFFFFFF, timeout_ms
+    s = stream if stream is not None else torch.cuda.current_stream(out.device)
+    with torch.cuda.device(out.device):
+        rc = _lib.lib().w4_allreduce_oneshot(ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
+    _lib.check(rc, "allreduce_oneshot")

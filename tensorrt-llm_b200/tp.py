@@ -133,7 +133,20 @@ class WeightOnlyRowLinear(_ShardedLinear):
         self.group = group
         return self
 
-    def forward(self, x_local, all_reduce: bool = True):
+    def forward(self, x_local, all_reduce: bool = True, oneshot: "OneShotAllReduce | None" = None):
+        """``oneshot``: use the peer-memory all-reduce for this call when the message fits it (the
+        GEMM then writes straight into the shared partial buffer); otherwise NCCL."""
+        m = x_local.numel() // x_local.shape[-1]
+        nbytes = m * self.n_local * x_local.element_size()
+        if (oneshot is not None and all_reduce and self.mapping.tp_size > 1 and nbytes <= oneshot.max_bytes
+                and self.matmul is None and self.group_size != 0 and nbytes % 16 == 0):
+            part = oneshot.partial(m, self.n_local)
+            algo = (_lib.INT8_WEIGHT if self.bits == 8 else 0) | (_lib.ZERO if self.zeros is not None else 0) \
+                | (_lib.PRE_QUANT_SCALE if self.pre_quant_scale is not None else 0)
+            ops.weight_only_groupwise_quant_matmul(x_local, self.pre_quant_scale, self.weight, self.scales, self.zeros,
+                                                   None, 1.0, algo, self.group_size, out=part)
+            y = torch.empty(x_local.shape[:-1] + (self.n_local,), dtype=x_local.dtype, device=x_local.device)
+            return oneshot.reduce(y, bias=self.bias)
         y = self._gemm(x_local, with_bias=False)
         if all_reduce and self.mapping.tp_size > 1:
             import torch.distributed as dist
@@ -143,6 +156,54 @@ class WeightOnlyRowLinear(_ShardedLinear):
         return y
 
     __call__ = forward
+
+
+class OneShotAllReduce:
+    """Peer-memory all-reduce for the small [M, N] partial sums of row-parallel layers (decode).
+
+    Owns one symmetric-memory allocation per rank (``torch.distributed._symmetric_memory``: every
+    rank's block is mapped into every process of the group): 256 bytes of flag words, then two
+    partial buffers used alternately. ``partial(m, n)`` returns the local buffer the next GEMM must
+    write; ``reduce(out)`` launches the library's one-shot kernel behind it on the current stream.
+    All ranks must make the same sequence of calls, as with any collective. Plain peer loads and
+    stores only (no multicast). Messages above ``W4_ONESHOT_MAX_BYTES`` belong to NCCL."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, group, device, dtype=torch.bfloat16, max_bytes: int = _lib.W4_ONESHOT_MAX_BYTES):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > _lib.W4_MAX_RANKS:
+            raise RuntimeError(f"OneShotAllReduce supports at most {_lib.W4_MAX_RANKS} ranks")
+        self.dtype, self.max_bytes = dtype, int(max_bytes)
+        self.buf = symm_mem.empty(self.FLAG_BYTES + 2 * self.max_bytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        dist.barrier(self.group)  # every rank's flags are zero before anyone announces call 1
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.epoch = 0
+
+    def _offset(self, epoch: int) -> int:
+        return self.FLAG_BYTES + (epoch & 1) * self.max_bytes
+
+    def partial(self, m: int, n: int) -> torch.Tensor:
+        """Local buffer for the partial sums of the next call to ``reduce``."""
+        nbytes = m * n * self.buf.new_empty(0, dtype=self.dtype).element_size()
+        if nbytes > self.max_bytes:
+            raise RuntimeError("message too large for the one-shot all-reduce")
+        off = self._offset(self.epoch + 1)
+        return self.buf[off:off + nbytes].view(self.dtype).view(m, n)
+
+    def reduce(self, out: torch.Tensor, bias=None, timeout_ms: int = 0) -> torch.Tensor:
+        self.epoch += 1
+        off = self._offset(self.epoch)
+        ops.allreduce_oneshot([p + off for p in self.ptrs], self.ptrs, out, out.shape[-1], self.rank, self.epoch,
+                              bias=bias, timeout_ms=timeout_ms)
+        return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -168,6 +229,12 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
     g = torch.Generator(device=device).manual_seed(3 + rank)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
     out = {}
+    one, one_err = None, None
+    if world > 1:
+        try:
+            one = OneShotAllReduce(None, device, torch.bfloat16)
+        except Exception as e:  # symmetric memory not available on this box: NCCL only, and say so
+            one_err = f"{type(e).__name__}: {e}"[:200]
     for name, K, N, kind in LLAMA70B_LAYERS:
         k_loc, n_loc = (K, N // world) if kind == "column" else (K // world, N)
         _check_shard(k_loc, n_loc, 4, group_size)
@@ -203,6 +270,23 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                 torch.cuda.synchronize()
                 t_gemm.append(e0.elapsed_time(e1))
                 t_ar.append(e1.elapsed_time(e2))
+            t_one = []
+            use_one = kind == "row" and world > 1 and one is not None and m * n_loc * 2 <= one.max_bytes
+            if use_one:
+                y2 = torch.empty_like(y)
+                for _ in range(reps):
+                    flush.zero_()
+                    barrier()
+                    part = one.partial(m, n_loc)
+                    ops.gemm_raw(x, w, s, part, n=n_loc, k=k_loc, weight_bits=4, group_size=group_size, zeros=z,
+                                 workspace=ws)
+                    e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+                    e1.record()
+                    one.reduce(y2)
+                    e2.record()
+                    torch.cuda.synchronize()
+                    t_one.append(e1.elapsed_time(e2))
+                t_one.sort()
             t_gemm.sort()
             t_ar.sort()
             gemm_us = max_over_ranks(t_gemm[len(t_gemm) // 2] * 1e3)
@@ -215,5 +299,9 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                 "per_gpu_GB/s": nbytes / gemm_us / 1e3, "per_gpu_TFLOP/s": flops / gemm_us / 1e6,
                 "regime": "gemv" if ops.select_regime(m, n_loc, k_loc, group_size, 4) == _lib.W4_REGIME_GEMV else "gemm",
             }
+            if kind == "row" and world > 1:
+                out[f"{name}_m{m}"]["oneshot_allreduce_us"] = (
+                    max_over_ranks(t_one[len(t_one) // 2] * 1e3) if use_one else
+                    (one_err or "message above the one-shot limit: NCCL"))
     del flush
     return out
