@@ -104,7 +104,9 @@ extern "C"
      *   bias       [n]                                                    device, optional
      *   out        [m, n] row-major, same type as act                     device, mandatory
      *   n          the real number of output features (not the packed extent)
-     *   workspace  scratch of at least w4_gemm_workspace_bytes(); may be NULL when that is 0
+     *   workspace  scratch of w4_gemm_workspace_bytes(); may be NULL when that is 0. Mandatory only when
+     *              act_scale is set and the tensor-core kernel runs (m*k*2 bytes); the rest lets that
+     *              kernel split k over idle SMs and is optional (smaller: it runs unsplit)
      */
     typedef struct W4GemmParams
     {

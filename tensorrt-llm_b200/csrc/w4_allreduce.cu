@@ -12,7 +12,7 @@
 // applies to this path. No multicast objects and no cluster multicast: plain peer loads and stores.
 //
 // Synchronisation. Each rank owns kMaxRanks flag words; rank s announces call number `epoch` by
-// storing it (release, system scope) into word s of every peer's flags after a system-wide fence.
+// storing it (release, system scope) into word s of every peer's flags.
 // A CTA starts reducing once all words of its own rank's flags have reached `epoch`. Call numbers
 // only grow, so flags are never reset. Callers alternate between two partial buffers: a rank can
 // only reach call e + 2 after every peer has announced call e + 1, which a peer does after its call
@@ -83,12 +83,10 @@ __global__ void __launch_bounds__(kThreads) oneshot_kernel(Args const a)
         failed = 0;
     __syncthreads();
 
-    // 1. announce: this rank's partial was written by the kernel before this one on the stream
+    // 1. announce: this rank's partial was written by the kernel before this one on the stream, so
+    // it is already visible; the release store keeps the flag behind it for the peers
     if (blockIdx.x == 0 && threadIdx.x < a.world)
-    {
-        __threadfence_system();
         st_release_sys(a.flags[threadIdx.x] + a.rank, a.epoch);
-    }
     // 2. wait for every rank (own word included: it is written by the CTA above)
     if (threadIdx.x < a.world)
     {

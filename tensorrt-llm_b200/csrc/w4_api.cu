@@ -150,8 +150,11 @@ extern "C"
         if (!aligned16(p->act) || !aligned16(p->weight) || !aligned16(p->scales) || !aligned16(p->out)
             || !aligned16(p->act_scale) || !aligned16(p->zeros) || !aligned16(p->bias) || !aligned16(p->workspace))
             return W4_ERR_MISALIGNED;
-        size_t const need = w4_gemm_workspace_bytes(p->m, p->n, p->k, p->group_size, p->weight_bits, p->act_dtype,
-            p->act_scale != nullptr, p->regime);
+        // Mandatory part only (the scaled activation copy of the tensor-core path); the rest of
+        // w4_gemm_workspace_bytes() enables split-k and is optional.
+        size_t const need = resolve_regime(*p) == W4_REGIME_GEMM
+            ? w4::gemm_tc_workspace_min(p->m, p->k, p->act_scale != nullptr)
+            : 0;
         if (need > 0 && (!p->workspace || p->workspace_bytes < need))
             return W4_ERR_WORKSPACE;
         return W4_OK;

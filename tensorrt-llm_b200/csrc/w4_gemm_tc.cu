@@ -66,6 +66,11 @@ struct Args
     int group_shift; // log2(group size), 31 = per-channel
     int tiles_n, tiles_m;
     int num_stages;
+    // Split-k: an output tile's k range is cut into `splits` work items that run on different SMs;
+    // each stores its fp32 partial tile and a second small kernel adds them in split order.
+    int splits;       // 1 = off
+    int ksteps_split; // k steps per work item
+    float* partial;   // [splits, m, n] fp32 (workspace)
 };
 
 struct __align__(16) Barriers
@@ -73,7 +78,7 @@ struct __align__(16) Barriers
     uint64_t full[kMaxStages];    // TMA landed (tx bytes); watched by the conversion warps only
     uint64_t done[kMaxStages];    // the MMAs of the step completed: smem stage and TMEM stage are free
     uint64_t d_full;              // accumulator complete
-    uint64_t d_empty;             // 4 epilogue warps drained the accumulator
+    uint64_t d_empty;             // the epilogue warps drained the accumulator
     // Steps each conversion warp has finished storing into TMEM, [group][quadrant]. The MMA warp
     // polls these with plain acquire loads: an mbarrier test issued by the MMA warp right after its
     // tcgen05.commit is held back until the committed MMAs finish, which costs a full step.
@@ -314,8 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncthreads();
 #endif
-    int const num_tiles = a.tiles_n * a.tiles_m;
-    int const ksteps = (a.k + BK - 1) / BK; // a trailing 64-wide half reads as zeros (TMA fill)
+    int const num_tiles = a.tiles_n * a.tiles_m * a.splits; // work items: (tile, split), splits adjacent
+    int const ksteps_all = (a.k + BK - 1) / BK; // a trailing 64-wide half reads as zeros (TMA fill)
 
     if (threadIdx.x == 0)
     {
@@ -360,10 +365,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             uint32_t const smem_base = smem_u32(smem);
             uint32_t const full0 = smem_u32(&bars->full[0]), done0 = smem_u32(&bars->done[0]);
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
+            for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
             {
+                int const tile = item / a.splits, split = item - tile * a.splits;
                 int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
-                for (int ks = 0; ks < ksteps; ++ks)
+                int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
+                for (int ks = ks0; ks < ks1; ++ks)
                 {
                     W4_TC_TIMED(0, ok = spin_wait(done0 + 8 * s, ph ^ 1, abort_flag));
                     if (!ok)
@@ -409,8 +416,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             int s = 0;
             uint32_t ph = 0, dph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x, it = 0; tile < num_tiles && ok; tile += gridDim.x, ++it)
+            for (int item = blockIdx.x, it = 0; item < num_tiles && ok; item += gridDim.x, ++it)
             {
+                int const tile = item / a.splits, split = item - tile * a.splits;
+                int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
                 if (it > 0)
                 {
                     W4_TC_TIMED(3, ok = spin_wait(d_empty, dph, abort_flag));
@@ -420,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tc_fence_after();
                 }
                 uint32_t accumulate = 0;
-                for (int ks = 0; ks < ksteps; ++ks)
+                for (int ks = ks0; ks < ks1; ++ks)
                 {
                     // The conversion warps publish a step only after they have seen the stage's TMA
                     // barrier, so it covers the activations as well.
@@ -483,9 +492,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t ph = 0, dph = 0;
         uint32_t my_steps = 0; // steps this warp has stored into TMEM (published by lane 0)
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
+        for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
         {
+            int const tile = item / a.splits, split = item - tile * a.splits;
             int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
+            int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
             int const n = tn * BN + n_local;
             bool const n_ok = n < a.n;
             // Scale / zero of this thread's column, one pair per scale group. The loads come from
@@ -494,19 +505,20 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t s2 = 0, z2 = 0;
             uint32_t sq[kScaleLookahead], zq[kScaleLookahead];
             int const num_groups = a.group_shift >= 31 ? 1 : (a.k >> a.group_shift);
+            int const g_first = (ks0 * kHalves) >> gsh; // scale group of this work item's first half
 #pragma unroll
             for (int i = 0; i < kScaleLookahead; ++i)
             {
                 sq[i] = 0;
                 zq[i] = 0;
-                if (n_ok && i < num_groups)
+                if (n_ok && g_first + i < num_groups)
                 {
-                    sq[i] = scales[size_t(i) * a.n + n];
+                    sq[i] = scales[size_t(g_first + i) * a.n + n];
                     if (HAS_ZERO)
-                        zq[i] = zeros[size_t(i) * a.n + n];
+                        zq[i] = zeros[size_t(g_first + i) * a.n + n];
                 }
             }
-            for (int ks = 0; ks < ksteps; ++ks)
+            for (int ks = ks0; ks < ks1; ++ks)
             {
                 // (scale, zero) pairs of the step's two halves; a new scale group starts every
                 // 2^gsh halves: take the oldest prefetched pair, fetch the one furthest ahead.
@@ -515,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int h = 0; h < kHalves; ++h)
                 {
                     int const u = ks * kHalves + h;
-                    if ((u & ((1 << gsh) - 1)) == 0)
+                    if ((u & ((1 << gsh) - 1)) == 0 || (ks == ks0 && h == 0))
                     {
                         s2 = sq[0] | (sq[0] << 16);
                         z2 = zq[0] | (zq[0] << 16);
@@ -643,28 +655,60 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             float const bias_f = (bias && n_ok) ? P::to_float(bias[n]) : 0.f;
             int const m0 = tm * BM;
-#pragma unroll 1
-            for (int c0 = cgroup * 32; c0 < BM; c0 += 32 * kConvGroups)
+            if (a.splits == 1)
             {
-                if (m0 + c0 >= a.m)
-                    break; // warp-uniform
-                uint32_t v[32];
-                tc_ld32(lane_addr + c0, v);
-                if (n_ok)
+#pragma unroll 1
+                for (int c0 = cgroup * 32; c0 < BM; c0 += 32 * kConvGroups)
                 {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    if (m0 + c0 >= a.m)
+                        break; // warp-uniform
+                    uint32_t v[32];
+                    tc_ld32(lane_addr + c0, v);
+                    if (n_ok)
                     {
-                        int const mrow = m0 + c0 + j;
-                        if (mrow < a.m)
-                            out[size_t(mrow) * a.n + n] = P::from_float(fmaf(a.alpha, __uint_as_float(v[j]), bias_f));
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                        {
+                            int const mrow = m0 + c0 + j;
+                            if (mrow < a.m)
+                                out[size_t(mrow) * a.n + n]
+                                    = P::from_float(fmaf(a.alpha, __uint_as_float(v[j]), bias_f));
+                        }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&bars->d_empty);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&bars->d_empty);
+            else
+            {
+                // Split-k: store the fp32 partial tile; splitk_reduce_kernel, next on the stream,
+                // adds the partial tiles in split order (deterministic) and writes the output.
+                float* part = a.partial + size_t(split) * a.m * a.n;
+#pragma unroll 1
+                for (int c0 = cgroup * 32; c0 < BM; c0 += 32 * kConvGroups)
+                {
+                    if (m0 + c0 >= a.m)
+                        break;
+                    uint32_t v[32];
+                    tc_ld32(lane_addr + c0, v);
+                    if (n_ok)
+                    {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                        {
+                            int const mrow = m0 + c0 + j;
+                            if (mrow < a.m)
+                                __stcg(part + size_t(mrow) * a.n + n, __uint_as_float(v[j]));
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&bars->d_empty);
+            }
         }
     }
 
@@ -704,6 +748,65 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
+static size_t split_align(size_t bytes)
+{
+    return (bytes + 255) & ~size_t(255);
+}
+
+// Workspace for split-k: `splits` fp32 copies of the output.
+static size_t split_bytes(int m, int n, int splits)
+{
+    return size_t(splits) * m * n * sizeof(float);
+}
+
+// out[m, n] = alpha * sum over splits (in order) of partial[s, m, n] + bias[n]; four columns per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(T* out, float const* partial, T const* bias, float alpha, size_t mn_vec, int n_vec, int splits)
+{
+    using P = Pair<T>;
+    size_t const i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= mn_vec)
+        return;
+    float4 const* src = reinterpret_cast<float4 const*>(partial) + i;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int sp = 0;
+    for (; sp + 4 <= splits; sp += 4)
+    {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            v[u] = __ldcg(src + size_t(sp + u) * mn_vec);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            acc.x += v[u].x;
+            acc.y += v[u].y;
+            acc.z += v[u].z;
+            acc.w += v[u].w;
+        }
+    }
+    for (; sp < splits; ++sp)
+    {
+        float4 const v = __ldcg(src + size_t(sp) * mn_vec);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias)
+    {
+        uint2 const bw = *reinterpret_cast<uint2 const*>(bias + size_t(i % n_vec) * 4);
+        P::unpack2(bw.x, b[0], b[1]);
+        P::unpack2(bw.y, b[2], b[3]);
+    }
+    uint2 o;
+    o.x = uint32_t(P::from_float(fmaf(alpha, acc.x, b[0]))) | (uint32_t(P::from_float(fmaf(alpha, acc.y, b[1]))) << 16);
+    o.y = uint32_t(P::from_float(fmaf(alpha, acc.z, b[2]))) | (uint32_t(P::from_float(fmaf(alpha, acc.w, b[3]))) << 16);
+    *reinterpret_cast<uint2*>(out + i * 4) = o;
+}
+
 template <typename T, int BITS, int BM, bool HAS_ZERO>
 static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
 {
@@ -723,6 +826,19 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
     a.group_shift = p.group_size == 64 ? 6 : (p.group_size == 128 ? 7 : 31);
     a.tiles_n = (p.n + BN - 1) / BN;
     a.tiles_m = (p.m + BM - 1) / BM;
+    {
+        // Split-k when the tiles alone would leave most SMs idle and the caller's workspace has
+        // room for the partial tiles (after the scaled copy of the activations, if there is one).
+        int const ksteps = (p.k + BK - 1) / BK;
+        int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms);
+        size_t const act_copy = (act != p.act) ? split_align(size_t(p.m) * p.k * 2) : 0;
+        if (splits > 1 && (!p.workspace || p.workspace_bytes < act_copy + split_bytes(p.m, p.n, splits)))
+            splits = 1;
+        a.ksteps_split = (ksteps + splits - 1) / splits;
+        a.splits = (ksteps + a.ksteps_split - 1) / a.ksteps_split; // no empty work items
+        if (a.splits > 1)
+            a.partial = reinterpret_cast<float*>(static_cast<char*>(p.workspace) + act_copy);
+    }
     size_t const fixed = sizeof(Barriers) + 1024; // + slack to align the ring to 1024 bytes
     int stages = int((size_t(dev.max_smem_optin) - fixed) / STAGE_BYTES);
     if (stages < 2)
@@ -758,9 +874,15 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
         if (dev.device >= 0 && dev.device < 64)
             configured[dev.device] = true;
     }
-    int const tiles = a.tiles_n * a.tiles_m;
+    int const tiles = a.tiles_n * a.tiles_m * a.splits;
     int const grid = tiles < dev.num_sms ? tiles : dev.num_sms;
     kernel<<<grid, kThreads, smem, stream>>>(a, tm_act, tm_w);
+    if (a.splits > 1)
+    {
+        size_t const mn_vec = size_t(p.m) * p.n / 4; // n is a multiple of 32
+        splitk_reduce_kernel<T><<<unsigned((mn_vec + 255) / 256), 256, 0, stream>>>(static_cast<T*>(p.out), a.partial,
+            static_cast<T const*>(p.bias), p.alpha, mn_vec, p.n / 4, a.splits);
+    }
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
@@ -808,9 +930,26 @@ static double step_us(int bm)
     return bm <= 128 ? 0.645 : (bm == 192 ? 0.70 : 1.06);
 }
 
-static double waves(int m, int n, int bm, int num_sms)
+// Split-k factor: used when the output tiles would occupy less than half of the SMs; every work
+// item keeps at least four k steps; only for m <= 256, where the fp32 partial tiles stay small.
+int gemm_tc_splits(int m, int n, int k, int num_sms)
 {
+    int const bm = gemm_tc_row_tile(m, n, num_sms);
     long const tiles = long((n + tc::BN - 1) / tc::BN) * long((m + bm - 1) / bm);
+    int const ksteps = (k + tc::BK - 1) / tc::BK;
+    if (tiles * 2 > num_sms || m > 256)
+        return 1;
+    long s = num_sms / tiles;
+    if (s > ksteps / 4)
+        s = ksteps / 4;
+    if (s > 16)
+        s = 16;
+    return s < 1 ? 1 : int(s);
+}
+
+static double waves(int m, int n, int bm, int num_sms, int splits = 1)
+{
+    long const tiles = long((n + tc::BN - 1) / tc::BN) * long((m + bm - 1) / bm) * splits;
     return double((tiles + num_sms - 1) / num_sms);
 }
 
@@ -840,15 +979,29 @@ int gemm_tc_row_tile(int m, int n, int num_sms)
 double gemm_tc_estimate_us(int m, int n, int k, int num_sms)
 {
     int const bm = gemm_tc_row_tile(m, n, num_sms);
-    return 7.0 + waves(m, n, bm, num_sms) * step_us(bm) * double((k + tc::BK - 1) / tc::BK);
+    int const splits = gemm_tc_splits(m, n, k, num_sms);
+    int const ksteps = (k + tc::BK - 1) / tc::BK;
+    int const per = (ksteps + splits - 1) / splits;
+    return 7.0 + (splits > 1 ? 3.0 : 0.0) + waves(m, n, bm, num_sms, splits) * step_us(bm) * double(per);
+}
+
+size_t gemm_tc_workspace_min(int m, int k, int has_act_scale)
+{
+    // the pre-quant scale is applied to a copy of the activations, as the reference plugin does
+    // (weightOnlyGroupwiseQuantMatmulPlugin.cpp:444-458 of the reference project)
+    return has_act_scale ? size_t(m) * k * 2 : 0;
 }
 
 size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale)
 {
-    (void) n;
-    // the pre-quant scale is applied to a copy of the activations, as the reference plugin does
-    // (weightOnlyGroupwiseQuantMatmulPlugin.cpp:444-458 of the reference project)
-    return has_act_scale ? size_t(m) * k * 2 : 0;
+    // what lets the kernel use split-k as well; with less (but at least the minimum) it runs unsplit
+    DeviceInfo const& dev = current_device_info();
+    int const sms = dev.num_sms > 0 ? dev.num_sms : 148;
+    int const splits = gemm_tc_splits(m, n, k, sms);
+    size_t bytes = gemm_tc_workspace_min(m, k, has_act_scale);
+    if (splits > 1)
+        bytes = tc::split_align(bytes) + tc::split_bytes(m, n, splits);
+    return bytes;
 }
 
 int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream)

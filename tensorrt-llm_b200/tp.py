@@ -270,23 +270,47 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                 torch.cuda.synchronize()
                 t_gemm.append(e0.elapsed_time(e1))
                 t_ar.append(e1.elapsed_time(e2))
-            t_one = []
+            # Row-parallel decode step as it runs in a serving loop: GEMM + reduce, back to back, no
+            # host in between (one CUDA graph of `reps` steps, replayed once: the one-shot kernel's
+            # call numbers are baked into the launches). Weights stay L2-warm here; the comparison
+            # of interest is the reduce. NCCL and the peer-memory kernel see the same GEMM.
             use_one = kind == "row" and world > 1 and one is not None and m * n_loc * 2 <= one.max_bytes
-            if use_one:
+            step_us = {}
+            if kind == "row" and world > 1:
                 y2 = torch.empty_like(y)
-                for _ in range(reps):
-                    flush.zero_()
-                    barrier()
+
+                def step_nccl():
+                    gemm()
+                    dist.all_reduce(y, op=dist.ReduceOp.SUM)
+
+                def step_one():
                     part = one.partial(m, n_loc)
                     ops.gemm_raw(x, w, s, part, n=n_loc, k=k_loc, weight_bits=4, group_size=group_size, zeros=z,
                                  workspace=ws)
-                    e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
-                    e1.record()
                     one.reduce(y2)
-                    e2.record()
-                    torch.cuda.synchronize()
-                    t_one.append(e1.elapsed_time(e2))
-                t_one.sort()
+
+                for label, fn in (("gemm", gemm), ("nccl", step_nccl)) + ((("oneshot", step_one),) if use_one else ()):
+                    try:
+                        st = torch.cuda.Stream(device=device)
+                        with torch.cuda.stream(st):
+                            for _ in range(3):
+                                fn()
+                            st.synchronize()
+                            barrier()
+                            graph = torch.cuda.CUDAGraph()
+                            with torch.cuda.graph(graph, stream=st):
+                                for _ in range(reps):
+                                    fn()
+                            e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+                            e1.record(st)
+                            graph.replay()
+                            e2.record(st)
+                            st.synchronize()
+                        step_us[label] = max_over_ranks(e1.elapsed_time(e2) * 1e3 / reps)
+                        del graph
+                    except Exception as e:  # capture not possible on this box: say so, keep going
+                        step_us[label] = f"unavailable: {type(e).__name__}: {e}"[:160]
+                        max_over_ranks(0.0)
             t_gemm.sort()
             t_ar.sort()
             gemm_us = max_over_ranks(t_gemm[len(t_gemm) // 2] * 1e3)
@@ -300,8 +324,9 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                 "regime": "gemv" if ops.select_regime(m, n_loc, k_loc, group_size, 4) == _lib.W4_REGIME_GEMV else "gemm",
             }
             if kind == "row" and world > 1:
-                out[f"{name}_m{m}"]["oneshot_allreduce_us"] = (
-                    max_over_ranks(t_one[len(t_one) // 2] * 1e3) if use_one else
-                    (one_err or "message above the one-shot limit: NCCL"))
+                out[f"{name}_m{m}"]["graph_step_us_gemm_only"] = step_us.get("gemm")
+                out[f"{name}_m{m}"]["graph_step_us_gemm_plus_nccl"] = step_us.get("nccl")
+                out[f"{name}_m{m}"]["graph_step_us_gemm_plus_oneshot"] = step_us.get("oneshot") if use_one else (
+                    one_err or "message above the one-shot limit: NCCL")
     del flush
     return out

@@ -96,3 +96,33 @@ def test_linearity_at_full_size():
     rows = torch.arange(0, m, 127)
     ref = oracle_out(dict(p, act=p["act"][rows].contiguous(), m=len(rows)))
     assert max_err(y1[rows].to(torch.bfloat16), ref) <= oracle.tolerance(ref)
+
+
+@pytest.mark.parametrize("m,n,k,bits,group,dtype", [
+    (64, 1280, 8192, 4, 128, torch.bfloat16),   # 10 tiles: 14-way split
+    (100, 512, 4096, 8, 64, torch.bfloat16),
+    (200, 1024, 2048, 8, 0, torch.float16),     # per-channel scales, splits start mid-matrix
+    (17, 256, 4160, 4, 64, torch.float16),      # k = 65 * 64: the last step of the last split is half empty
+    (256, 4096, 14336, 4, 128, torch.bfloat16),
+])
+def test_split_k(m, n, k, bits, group, dtype):
+    """Few output tiles: the k range is split over SMs (fp32 partial tiles in the workspace, added
+    in split order by a second kernel). Same oracle, same tolerance; and the same problem with only
+    the mandatory part of the workspace (no split) agrees to rounding."""
+    full = group != 0
+    p = make_problem(m, n, k, bits, group, dtype, zero=full, bias=full, prequant=full, seed=m + k)
+    lib = pkg._lib.lib()
+    dt = pkg._lib.W4_DTYPE_FP16 if dtype == torch.float16 else pkg._lib.W4_DTYPE_BF16
+    need = lib.w4_gemm_workspace_bytes(m, n, k, group, bits, dt, int(full), GEMM)
+    assert need > (m * k * 2 if full else 0), "this shape is expected to use split-k"
+    alpha = 0.5 if full else 1.0
+    _check(p, alpha=alpha)
+    # unsplit run of the same problem through the raw entry point with the minimal workspace
+    d = lambda t: None if t is None else t.cuda()
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    ws = torch.empty(max(m * k * 2, 16), dtype=torch.uint8, device="cuda") if full else None
+    pkg.ops.gemm_raw(d(p["act"]), d(p["processed"]), d(p["scales"]), out, n=n, k=k, weight_bits=bits, group_size=group,
+                     zeros=d(p["zeros"]), bias=d(p["bias"]), act_scale=d(p["ps"]), alpha=alpha, regime=GEMM,
+                     workspace=ws)
+    ref = oracle_out(p, alpha=alpha)
+    assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)

@@ -121,9 +121,14 @@ def test_launch_argument_validation(lib):
 def test_regime_heuristic(lib):
     for m in (1, 2, 4, 8):
         assert lib.w4_gemm_select_regime(m, 14336, 4096, 128, 4) == pkg.W4_REGIME_GEMV
-    # m = 16 goes to whichever kernel the cost model finds cheaper for the shape
-    assert lib.w4_gemm_select_regime(16, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMV
+    # above 8 rows the cost model decides: two decode passes against the (split-k) tensor-core kernel
     assert lib.w4_gemm_select_regime(16, 14336, 4096, 128, 4) == pkg.W4_REGIME_GEMM
+    assert lib.w4_gemm_select_regime(16, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMM
+    # a tiny weight: streaming it twice is cheaper than the tensor-core kernel's fixed cost
+    assert lib.w4_gemm_select_regime(16, 256, 512, 128, 4) == pkg.W4_REGIME_GEMV
+    # workspace: the split-k partial tiles are on top of the mandatory part
+    assert lib.w4_gemm_workspace_bytes(64, 1280, 8192, 128, 4, 1, 0, pkg.W4_REGIME_GEMM) >= 2 * 64 * 1280 * 4
+    assert lib.w4_gemm_workspace_bytes(4096, 4096, 14336, 128, 4, 1, 0, pkg.W4_REGIME_GEMM) == 0
     for m in (256, 4096, 8192):
         assert lib.w4_gemm_select_regime(m, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMM
 
