@@ -297,16 +297,19 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                                 fn()
                             st.synchronize()
                             barrier()
+                            greps = reps * (5 if m <= 64 else 1)  # long enough to hide the one-off graph upload
                             graph = torch.cuda.CUDAGraph()
                             with torch.cuda.graph(graph, stream=st):
-                                for _ in range(reps):
+                                for _ in range(greps):
                                     fn()
                             e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+                            st.synchronize()
+                            barrier()  # capture takes a different time on every rank: start together
                             e1.record(st)
                             graph.replay()
                             e2.record(st)
                             st.synchronize()
-                        step_us[label] = max_over_ranks(e1.elapsed_time(e2) * 1e3 / reps)
+                        step_us[label] = max_over_ranks(e1.elapsed_time(e2) * 1e3 / greps)
                         del graph
                     except Exception as e:  # capture not possible on this box: say so, keep going
                         step_us[label] = f"unavailable: {type(e).__name__}: {e}"[:160]
