@@ -112,18 +112,28 @@ __global__ void __launch_bounds__(kThreads) oneshot_kernel(Args const a)
     int const n_vec = a.n / 8;
     for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < vecs; i += size_t(gridDim.x) * kThreads)
     {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < a.world; ++r)
-        {
-            uint4 const v = ld_peer(static_cast<uint4 const*>(a.partials[r]) + i);
-            uint32_t const w[4] = {v.x, v.y, v.z, v.w};
+        // All peers' vectors are requested before the first is used: one NVLink round trip, not
+        // `world` of them back to back.
+        uint4 v[kMaxRanks];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < a.world)
+                v[r] = ld_peer(static_cast<uint4 const*>(a.partials[r]) + i);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+        {
+            if (r < a.world)
             {
-                float lo, hi;
-                P::unpack2(w[j], lo, hi);
-                acc[2 * j] += lo;
-                acc[2 * j + 1] += hi;
+                uint32_t const w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    float lo, hi;
+                    P::unpack2(w[j], lo, hi);
+                    acc[2 * j] += lo;
+                    acc[2 * j + 1] += hi;
+                }
             }
         }
         if (a.bias)

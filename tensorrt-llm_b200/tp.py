@@ -138,8 +138,8 @@ class WeightOnlyRowLinear(_ShardedLinear):
         GEMM then writes straight into the shared partial buffer); otherwise NCCL."""
         m = x_local.numel() // x_local.shape[-1]
         nbytes = m * self.n_local * x_local.element_size()
-        if (oneshot is not None and all_reduce and self.mapping.tp_size > 1 and nbytes <= oneshot.max_bytes
-                and self.matmul is None and self.group_size != 0 and nbytes % 16 == 0):
+        if (oneshot is not None and all_reduce and self.mapping.tp_size > 1 and oneshot.preferred(nbytes)
+                and self.matmul is None and self.group_size != 0):
             part = oneshot.partial(m, self.n_local)
             algo = (_lib.INT8_WEIGHT if self.bits == 8 else 0) | (_lib.ZERO if self.zeros is not None else 0) \
                 | (_lib.PRE_QUANT_SCALE if self.pre_quant_scale is not None else 0)
@@ -186,6 +186,16 @@ class OneShotAllReduce:
         dist.barrier(self.group)  # every rank's flags are zero before anyone announces call 1
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.epoch = 0
+
+    def preferred(self, nbytes: int) -> bool:
+        """The reference's choice between its one-shot kernel and NCCL
+        (plugins/ncclPlugin/allreducePlugin.cpp:258-283): always up to 2 ranks, below 1 MB up to 4,
+        below 500 kB beyond; and never above this buffer's capacity."""
+        if nbytes > self.max_bytes or nbytes % 16:
+            return False
+        if self.world <= 2:
+            return True
+        return nbytes < (1_000_000 if self.world <= 4 else 500_000)
 
     def _offset(self, epoch: int) -> int:
         return self.FLAG_BYTES + (epoch & 1) * self.max_bytes
@@ -274,7 +284,7 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
             # host in between (one CUDA graph of `reps` steps, replayed once: the one-shot kernel's
             # call numbers are baked into the launches). Weights stay L2-warm here; the comparison
             # of interest is the reduce. NCCL and the peer-memory kernel see the same GEMM.
-            use_one = kind == "row" and world > 1 and one is not None and m * n_loc * 2 <= one.max_bytes
+            use_one = kind == "row" and world > 1 and one is not None and one.preferred(m * n_loc * 2)
             step_us = {}
             if kind == "row" and world > 1:
                 y2 = torch.empty_like(y)
@@ -330,6 +340,6 @@ def bench_llama70b_layer_set(device, rank, world, barrier, max_over_ranks, ms=(1
                 out[f"{name}_m{m}"]["graph_step_us_gemm_only"] = step_us.get("gemm")
                 out[f"{name}_m{m}"]["graph_step_us_gemm_plus_nccl"] = step_us.get("nccl")
                 out[f"{name}_m{m}"]["graph_step_us_gemm_plus_oneshot"] = step_us.get("oneshot") if use_one else (
-                    one_err or "message above the one-shot limit: NCCL")
+                    one_err or "message above the one-shot threshold for this world size: NCCL")
     del flush
     return out
