@@ -412,7 +412,91 @@ def extra_points(pkg, p, sets, device, peaks, stream):
             points[f"c2_m{mm}"] = {"us": us, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                                    "frac_of_8TBs": gbs / 8000.0}
     points["c3_m4096"] = prefill_point(pkg, device, peaks)
+    points["prep_c2"] = prep_point(pkg, device, peaks)
+    points["splitk_m64_k8192_n1280"] = splitk_point(pkg, device)
     return points
+
+
+def prep_point(pkg, device, peaks):
+    """GPU-side weight preparation of a config-2 matrix (K=4096, N=14336): layout only (int4) and
+    quantise + layout from bf16, checked byte for byte against the host path, timed beside it."""
+    import time
+
+    from tensorrt_llm_b200 import quantize as Q
+    k, n = C2["k"], C2["n"]
+    g = torch.Generator().manual_seed(7)
+    raw = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, generator=g)
+    t0 = time.perf_counter()
+    ref = Q.preprocess_weights_for_mixed_gemm(raw, torch.quint4x2)
+    cpu_ms = (time.perf_counter() - t0) * 1e3
+    raw_d = raw.to(device)
+    out = Q.preprocess_weights_for_mixed_gemm_cuda(raw_d, torch.quint4x2)
+    if not torch.equal(out.cpu(), ref):
+        raise SystemExit("parity FAILED for the GPU layout kernel")
+    w = (torch.randn(k, n, generator=g) * 0.02).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    p_ref, s_ref = Q.symmetric_quantize_last_axis_of_batched_matrix(w, torch.quint4x2)
+    cpu_q_ms = (time.perf_counter() - t0) * 1e3
+    w_d = w.to(device)
+    p_gpu, s_gpu = Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w_d, torch.quint4x2)
+    if not (torch.equal(p_gpu.cpu(), p_ref) and torch.equal(s_gpu.cpu(), s_ref)):
+        raise SystemExit("parity FAILED for the GPU quantise kernel")
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    us_l = timed(lambda: Q.preprocess_weights_for_mixed_gemm_cuda(raw_d, torch.quint4x2))
+    us_q = timed(lambda: Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w_d, torch.quint4x2))
+    bytes_l = 2 * k * n // 2                      # read + write the packed matrix
+    bytes_q = 2 * k * n * 2 + k * n // 2          # two passes over the bf16 matrix (amax, quantise) + write
+    return {"layout_us": us_l, "layout_GB/s": bytes_l / us_l / 1e3,
+            "layout_frac_of_measured_hbm": bytes_l / us_l / 1e3 / peaks["hbm_gbs"],
+            "layout_cpu_ms_host_threads": cpu_ms,
+            "quantize_us": us_q, "quantize_GB/s": bytes_q / us_q / 1e3,
+            "quantize_frac_of_measured_hbm": bytes_q / us_q / 1e3 / peaks["hbm_gbs"],
+            "quantize_cpu_ms_host_threads": cpu_q_ms, "includes": "output allocation by the torch wrapper"}
+
+
+def splitk_point(pkg, device):
+    """A few-tile tensor-core shape (Llama-3-70B qkv shard at tp=8, M=64) with and without the
+    optional split-k workspace, graph-timed."""
+    from tensorrt_llm_b200 import ops
+    m, n, k = 64, 1280, 8192
+    w = torch.randint(0, 256, (k, n // 2), dtype=torch.uint8, device=device).view(torch.int8)
+    s = (torch.rand(k // 128, n, device=device) * 0.019 + 0.001).to(torch.bfloat16)
+    act = torch.randn(m, k, device=device).to(torch.bfloat16)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    res = {}
+    for label, nb in (("unsplit_us", 0), ("split_us", ops.workspace_bytes(m, n, k, 128, 4, torch.bfloat16, False,
+                                                                           pkg.W4_REGIME_GEMM))):
+        ws = torch.empty(nb, dtype=torch.uint8, device=device) if nb else None
+        st = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(st):
+            fn = lambda _i=0: ops.gemm_raw(act, w, s, out, n=n, k=k, weight_bits=4, group_size=128,  # noqa: E731
+                                           regime=pkg.W4_REGIME_GEMM, workspace=ws)
+            for _ in range(3):
+                fn()
+            st.synchronize()
+            g = graph_of(fn, 50, st)
+            g.replay()
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            g.replay()
+            e1.record(st)
+            st.synchronize()
+        res[label] = e0.elapsed_time(e1) * 1e3 / 50
+    res["workspace_bytes"] = int(nb)
+    return res
 
 
 def prefill_point(pkg, device, peaks):

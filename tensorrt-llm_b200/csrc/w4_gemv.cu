@@ -60,7 +60,7 @@ constexpr int kThreads = kConsumerThreads + 128; // + one producer warp group (o
 // Registers: a fifth warp per scheduler would cap every thread at 96 registers; the producer group
 // gives its share back (setmaxnreg) and the consumer groups take it.
 constexpr int kProducerRegs = 24, kConsumerRegs = 112; // 128 * 24 + 512 * 112 <= 640 * 96 (the launch-time pool)
-constexpr int kRedBytes = kWarps * 1024;        // shared memory for cross-warp partial sums
+constexpr int kRedBytes = 64 * 1024;            // shared memory for cross-warp partial sums
 constexpr int kCtasPerSm = kWarps <= 8 ? 2 : 1; // 8 warps: half an SM, so two launches can overlap
 constexpr int kScaleBoxCols = 24;               // columns per scale/zero box: 16 + slack to start on a 16-byte boundary
 
@@ -147,6 +147,7 @@ struct Args
     int groups_per_panel; // scale rows delivered with every tile (1 for per-channel)
     int box_stride;       // bytes between the scale box and the zero box (multiple of 128)
     int depth;            // tiles kept in flight ahead of the one being consumed
+    int red_bytes;        // shared memory for the cross-warp partial sums
 };
 
 // Shared flag: once any wait in the CTA timed out, every later wait returns at once.
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + size_t(a.num_slots) * a.slot_bytes);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(a.num_slots) * a.slot_bytes + kRedBytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(a.num_slots) * a.slot_bytes + a.red_bytes);
     uint64_t* empty_bar = full_bar + a.num_slots;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + a.num_slots);
 
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // rows exist (t < MT) are stored.
     int const MT = MB == 2 ? 4 : (a.m + 1) >> 1;
     int const per_cg = kWarps * MB * 4 * 8 * MT;
-    int const red_cap = max(1, (kRedBytes / 4) / per_cg); // column groups the reduction buffer holds
+    int const red_cap = max(1, (a.red_bytes / 4) / per_cg); // column groups the reduction buffer holds
     // Column groups that share one activation load (only matters with several k panels); the
     // reduction batch is a whole number of such sub-batches.
     int const cbe = min(CB, red_cap);
@@ -701,7 +702,20 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     args.groups_per_panel = a.group_shift >= 31 ? 1 : C::KP >> a.group_shift;
     args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
     args.slot_bytes = C::TILE_BYTES + 2 * args.box_stride;
-    size_t const fixed = kRedBytes + 64;
+    // 64 KB of partial sums (8 column groups at 8 rows, 32 at one): every reduction is a CTA-wide
+    // barrier, and fewer of them measured faster than the two ring slots this costs (four slots
+    // remain; ~72 KB are in flight at a time anyway).
+    args.red_bytes = kRedBytes;
+    {
+        static int const red_override = []
+        {
+            char const* e = getenv("W4_GEMV_RED_KB"); // tuning aid
+            return e ? atoi(e) : 0;
+        }();
+        if (red_override > 0)
+            args.red_bytes = red_override * 1024;
+    }
+    size_t const fixed = size_t(args.red_bytes) + 64;
     // Shared memory per CTA: all a block may have, or half of the SM's 228 KB less the 1 KB the
     // system reserves per block when two CTAs are to fit.
     size_t const smem_budget = kCtasPerSm == 1 ? size_t(dev.max_smem_optin) : size_t(233472 / 2 - 1024);
