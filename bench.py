@@ -342,11 +342,22 @@ def run_ours(args):
     d_ps = ps
     algo = pkg.ZERO | pkg.PRE_QUANT_SCALE
 
+    # End to end through the plugin-facing call (the mirror of the TensorRT plugin's enqueue:
+    # caller-owned device inputs / outputs / workspace, as the TensorRT runtime hands them over):
+    # every step copies the activations from pinned host memory, enqueues, reads the result back.
+    plugin = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(ops.TRT_BF16, algo, 128, 1.0)
+    d_act = torch.empty((m, C2["k"]), dtype=torch.bfloat16, device=device)
+    d_out = torch.empty((m, C2["n"]), dtype=torch.bfloat16, device=device)
+    ws_n = ops.workspace_bytes(m, C2["n"], C2["k"], 128, 4, torch.bfloat16, True)
+    d_ws = torch.empty(ws_n, dtype=torch.uint8, device=device) if ws_n else None
+
     def e2e_step(i):
         w, s, z = sets[i % len(sets)]
-        a = h_act.to(device, non_blocking=True)
-        o = ops.weight_only_groupwise_quant_matmul(a, d_ps, w, s, z, None, 1.0, algo, 128)
-        h_out.copy_(o, non_blocking=True)
+        d_act.copy_(h_act, non_blocking=True)
+        rc = plugin.enqueue([d_act, d_ps, w, s, z], [d_out], d_ws)
+        if rc != 0:
+            raise SystemExit(f"plugin enqueue failed with status {rc}")
+        h_out.copy_(d_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = min(args.steps, 2000)

@@ -283,7 +283,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr)
     return d;
 }
 
-template <typename T, int BITS, int BM, bool HAS_ZERO>
+template <typename T, int BITS, int BM, bool HAS_ZERO, bool SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_kernel(Args const a, __grid_constant__ CUtensorMap const tm_act, __grid_constant__ CUtensorMap const tm_w)
 {
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncthreads();
 #endif
-    int const num_tiles = a.tiles_n * a.tiles_m * a.splits; // work items: (tile, split), splits adjacent
+    int const num_tiles = a.tiles_n * a.tiles_m * (SPLITK ? a.splits : 1); // work items: (tile, split), splits adjacent
     int const ksteps_all = (a.k + BK - 1) / BK; // a trailing 64-wide half reads as zeros (TMA fill)
 
     if (threadIdx.x == 0)
@@ -367,9 +367,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t const full0 = smem_u32(&bars->full[0]), done0 = smem_u32(&bars->done[0]);
             for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
             {
-                int const tile = item / a.splits, split = item - tile * a.splits;
+                int const tile = SPLITK ? item / a.splits : item, split = SPLITK ? item - tile * a.splits : 0;
                 int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
-                int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
+                int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
                 for (int ks = ks0; ks < ks1; ++ks)
                 {
                     W4_TC_TIMED(0, ok = spin_wait(done0 + 8 * s, ph ^ 1, abort_flag));
@@ -418,8 +418,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             for (int item = blockIdx.x, it = 0; item < num_tiles && ok; item += gridDim.x, ++it)
             {
-                int const tile = item / a.splits, split = item - tile * a.splits;
-                int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
+                int const tile = SPLITK ? item / a.splits : item, split = SPLITK ? item - tile * a.splits : 0;
+                int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
                 if (it > 0)
                 {
                     W4_TC_TIMED(3, ok = spin_wait(d_empty, dph, abort_flag));
@@ -494,9 +494,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool ok = true;
         for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
         {
-            int const tile = item / a.splits, split = item - tile * a.splits;
+            int const tile = SPLITK ? item / a.splits : item, split = SPLITK ? item - tile * a.splits : 0;
             int const tn = tile % a.tiles_n, tm = tile / a.tiles_n;
-            int const ks0 = split * a.ksteps_split, ks1 = min(ksteps_all, ks0 + a.ksteps_split);
+            int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
             int const n = tn * BN + n_local;
             bool const n_ok = n < a.n;
             // Scale / zero of this thread's column, one pair per scale group. The loads come from
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t s2 = 0, z2 = 0;
             uint32_t sq[kScaleLookahead], zq[kScaleLookahead];
             int const num_groups = a.group_shift >= 31 ? 1 : (a.k >> a.group_shift);
-            int const g_first = (ks0 * kHalves) >> gsh; // scale group of this work item's first half
+            int const g_first = SPLITK ? (ks0 * kHalves) >> gsh : 0; // scale group of this work item's first half
 #pragma unroll
             for (int i = 0; i < kScaleLookahead; ++i)
             {
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int h = 0; h < kHalves; ++h)
                 {
                     int const u = ks * kHalves + h;
-                    if ((u & ((1 << gsh) - 1)) == 0 || (ks == ks0 && h == 0))
+                    if ((u & ((1 << gsh) - 1)) == 0 || (SPLITK && ks == ks0 && h == 0))
                     {
                         s2 = sq[0] | (sq[0] << 16);
                         z2 = zq[0] | (zq[0] << 16);
@@ -655,7 +655,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             float const bias_f = (bias && n_ok) ? P::to_float(bias[n]) : 0.f;
             int const m0 = tm * BM;
-            if (a.splits == 1)
+            if (!SPLITK)
             {
 #pragma unroll 1
                 for (int c0 = cgroup * 32; c0 < BM; c0 += 32 * kConvGroups)
@@ -807,12 +807,12 @@ __global__ void __launch_bounds__(256)
     *reinterpret_cast<uint2*>(out + i * 4) = o;
 }
 
-template <typename T, int BITS, int BM, bool HAS_ZERO>
-static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
+template <typename T, int BITS, int BM, bool HAS_ZERO, bool SPLITK>
+static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream, int splits)
 {
     constexpr int IL = BITS == 4 ? 4 : 2;
     constexpr int STAGE_BYTES = kHalves * (BM * 128 + (BN / IL) * 128);
-    auto kernel = gemm_kernel<T, BITS, BM, HAS_ZERO>;
+    auto kernel = gemm_kernel<T, BITS, BM, HAS_ZERO, SPLITK>;
 
     Args a{};
     a.scales = p.scales;
@@ -827,16 +827,13 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
     a.tiles_n = (p.n + BN - 1) / BN;
     a.tiles_m = (p.m + BM - 1) / BM;
     {
-        // Split-k when the tiles alone would leave most SMs idle and the caller's workspace has
-        // room for the partial tiles (after the scaled copy of the activations, if there is one).
+        // Split-k (chosen by the caller of this function): partial tiles go to the workspace, behind
+        // the scaled copy of the activations if there is one.
         int const ksteps = (p.k + BK - 1) / BK;
-        int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms);
         size_t const act_copy = (act != p.act) ? split_align(size_t(p.m) * p.k * 2) : 0;
-        if (splits > 1 && (!p.workspace || p.workspace_bytes < act_copy + split_bytes(p.m, p.n, splits)))
-            splits = 1;
         a.ksteps_split = (ksteps + splits - 1) / splits;
         a.splits = (ksteps + a.ksteps_split - 1) / a.ksteps_split; // no empty work items
-        if (a.splits > 1)
+        if (SPLITK)
             a.partial = reinterpret_cast<float*>(static_cast<char*>(p.workspace) + act_copy);
     }
     size_t const fixed = sizeof(Barriers) + 1024; // + slack to align the ring to 1024 bytes
@@ -874,10 +871,10 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
         if (dev.device >= 0 && dev.device < 64)
             configured[dev.device] = true;
     }
-    int const tiles = a.tiles_n * a.tiles_m * a.splits;
+    int const tiles = a.tiles_n * a.tiles_m * (SPLITK ? a.splits : 1);
     int const grid = tiles < dev.num_sms ? tiles : dev.num_sms;
     kernel<<<grid, kThreads, smem, stream>>>(a, tm_act, tm_w);
-    if (a.splits > 1)
+    if (SPLITK)
     {
         size_t const mn_vec = size_t(p.m) * p.n / 4; // n is a multiple of 32
         splitk_reduce_kernel<T><<<unsigned((mn_vec + 255) / 256), 256, 0, stream>>>(static_cast<T*>(p.out), a.partial,
@@ -895,13 +892,32 @@ static int dispatch_bm(W4GemmParams const& p, void const* act, DeviceInfo const&
         return e ? atoi(e) : 0;
     }();
     int const bm = bm_override ? bm_override : gemm_tc_row_tile(p.m, p.n, dev.num_sms);
+    // Split-k when the tiles alone would leave most SMs idle and the caller's workspace has room
+    // for the partial tiles; the unsplit kernel is a separate instantiation without any of it.
+    int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms);
+    if (splits > 1)
+    {
+        size_t const act_copy = (act != p.act) ? split_align(size_t(p.m) * p.k * 2) : 0;
+        if (!p.workspace || p.workspace_bytes < act_copy + split_bytes(p.m, p.n, splits))
+            splits = 1;
+    }
+    if (splits > 1)
+    {
+        if (bm == 64)
+            return launch_one<T, BITS, 64, HAS_ZERO, true>(p, act, dev, stream, splits);
+        if (bm == 128)
+            return launch_one<T, BITS, 128, HAS_ZERO, true>(p, act, dev, stream, splits);
+        if (bm == 192)
+            return launch_one<T, BITS, 192, HAS_ZERO, true>(p, act, dev, stream, splits);
+        return launch_one<T, BITS, 256, HAS_ZERO, true>(p, act, dev, stream, splits);
+    }
     if (bm == 64)
-        return launch_one<T, BITS, 64, HAS_ZERO>(p, act, dev, stream);
+        return launch_one<T, BITS, 64, HAS_ZERO, false>(p, act, dev, stream, 1);
     if (bm == 128)
-        return launch_one<T, BITS, 128, HAS_ZERO>(p, act, dev, stream);
+        return launch_one<T, BITS, 128, HAS_ZERO, false>(p, act, dev, stream, 1);
     if (bm == 192)
-        return launch_one<T, BITS, 192, HAS_ZERO>(p, act, dev, stream);
-    return launch_one<T, BITS, 256, HAS_ZERO>(p, act, dev, stream);
+        return launch_one<T, BITS, 192, HAS_ZERO, false>(p, act, dev, stream, 1);
+    return launch_one<T, BITS, 256, HAS_ZERO, false>(p, act, dev, stream, 1);
 }
 
 template <typename T>
