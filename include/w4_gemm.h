@@ -142,6 +142,11 @@ extern "C"
     size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
         int has_act_scale, int regime);
 
+    /* The largest w4_gemm_workspace_bytes() over m = 1..max_m: what a plugin reserves at configure
+     * time (getWorkspaceSize), since the optional split-k part peaks at small m, not at max_m. */
+    size_t w4_gemm_workspace_bytes_max(int max_m, int n, int k, int group_size, int weight_bits, int act_dtype,
+        int has_act_scale);
+
     /* W4_REGIME_GEMV or W4_REGIME_GEMM for this shape. */
     int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits);
 

@@ -24,6 +24,7 @@ EXPORTS = (
     "w4_gemm_select_regime", "w4_gemm_device_status", "w4_symmetric_quantize", "w4_preprocess_weights",
     "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
     "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce_oneshot",
+    "w4_gemm_workspace_bytes_max",
 )
 
 
@@ -77,6 +78,8 @@ def lib() -> ctypes.CDLL:
         l.w4_gemm_static_scratch_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 8
+        l.w4_gemm_workspace_bytes_max.restype = ctypes.c_size_t
+        l.w4_gemm_workspace_bytes_max.argtypes = [ctypes.c_int] * 7
         l.w4_gemm_select_regime.argtypes = [ctypes.c_int] * 5
         l.w4_symmetric_quantize.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                             ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]

@@ -188,6 +188,26 @@ extern "C"
         return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale);
     }
 
+    size_t w4_gemm_workspace_bytes_max(int max_m, int n, int k, int group_size, int weight_bits, int act_dtype,
+        int has_act_scale)
+    {
+        size_t best = 0;
+        // split-k is only used up to 256 rows; beyond that the size grows with m (or is zero)
+        for (int m = 1; m <= max_m && m <= 256; ++m)
+        {
+            size_t const b = w4_gemm_workspace_bytes(m, n, k, group_size, weight_bits, act_dtype, has_act_scale,
+                W4_REGIME_AUTO);
+            best = b > best ? b : best;
+        }
+        if (max_m > 256)
+        {
+            size_t const b = w4_gemm_workspace_bytes(max_m, n, k, group_size, weight_bits, act_dtype, has_act_scale,
+                W4_REGIME_GEMM);
+            best = b > best ? b : best;
+        }
+        return best;
+    }
+
     int w4_gemm_launch(const W4GemmParams* p, void* stream)
     {
         int const rc = w4_gemm_validate(p);

@@ -53,6 +53,13 @@ def workspace_bytes(m: int, n: int, k: int, group_size: int, weight_bits: int, d
                                                   int(has_act_scale), regime))
 
 
+def workspace_bytes_max(max_m: int, n: int, k: int, group_size: int, weight_bits: int, dtype: torch.dtype,
+                        has_act_scale: bool) -> int:
+    """Largest workspace over m = 1..max_m: what a plugin reserves at configure time."""
+    return int(_lib.lib().w4_gemm_workspace_bytes_max(max_m, n, k, group_size, weight_bits, _DTYPES[dtype],
+                                                      int(has_act_scale)))
+
+
 def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, group_size: int, zeros=None,
              bias=None, act_scale=None, alpha: float = 1.0, regime: int = W4_REGIME_AUTO, workspace=None,
              stream: Optional[int] = None) -> None:
@@ -179,7 +186,7 @@ class WeightOnlyQuantMatmulPlugin(_PluginBase):
         if self.dims is None:
             return 0
         _, mm, n, k = self.dims
-        return workspace_bytes(max_m or mm, n, k, 0, self.bits, self.dtype, False)
+        return workspace_bytes_max(max_m or mm, n, k, 0, self.bits, self.dtype, False)
 
     def enqueue(self, inputs, outputs, workspace=None, stream=None, regime=W4_REGIME_AUTO) -> int:
         """Returns 0 on success and a non-zero status instead of raising, as the noexcept
@@ -250,8 +257,8 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
         if self.dims is None:
             return 0
         _, mm, n, k = self.dims
-        return workspace_bytes(max_m or mm, n, k, self.group_size, self.bits, self.dtype,
-                               bool(self.quant_algo & PRE_QUANT_SCALE))
+        return workspace_bytes_max(max_m or mm, n, k, self.group_size, self.bits, self.dtype,
+                                   bool(self.quant_algo & PRE_QUANT_SCALE))
 
     def enqueue(self, inputs, outputs, workspace=None, stream=None, regime=W4_REGIME_AUTO) -> int:
         try:

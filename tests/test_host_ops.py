@@ -129,6 +129,10 @@ def test_regime_heuristic(lib):
     # workspace: the split-k partial tiles are on top of the mandatory part
     assert lib.w4_gemm_workspace_bytes(64, 1280, 8192, 128, 4, 1, 0, pkg.W4_REGIME_GEMM) >= 2 * 64 * 1280 * 4
     assert lib.w4_gemm_workspace_bytes(4096, 4096, 14336, 128, 4, 1, 0, pkg.W4_REGIME_GEMM) == 0
+    # a plugin sizes its workspace once, for every m up to the profile's maximum
+    big = lib.w4_gemm_workspace_bytes_max(4096, 1280, 8192, 128, 4, 1, 0)
+    assert big >= max(lib.w4_gemm_workspace_bytes(m, 1280, 8192, 128, 4, 1, 0, 0) for m in (1, 16, 64, 200, 256, 4096))
+    assert lib.w4_gemm_workspace_bytes_max(4096, 1280, 8192, 128, 4, 1, 1) >= 4096 * 8192 * 2
     for m in (256, 4096, 8192):
         assert lib.w4_gemm_select_regime(m, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMM
 
