@@ -4,7 +4,7 @@
 # compiled from the sources where they lie. Nothing is copied into this repository and nothing
 # is written outside oracle/_ref/.
 #
-#   usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $WOQ_REFERENCE_ROOT or /root/reference)
+#   usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $WOQ_REFERENCE_ROOT, else the reference checkout next to this repository)
 #
 # The reference needs CUTLASS headers for a handful of type traits only (half_t, uint4b_t,
 # sizeof_bits, arch tags, layout tags); its own copy is an un-vendored git submodule, so the

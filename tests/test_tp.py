@@ -111,3 +111,23 @@ def test_rank_that_never_joins_times_out():
         dist.init_process_group("gloo", rank=0, world_size=2, timeout=timedelta(seconds=2))
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def test_oneshot_policy_and_buffer_alternation():
+    """Host logic of the peer-memory all-reduce helper (no GPU): the reference's size thresholds per
+    world size and the alternation between the two partial buffers."""
+    from tensorrt_llm_b200 import tp, _lib
+
+    def helper(world):
+        h = object.__new__(tp.OneShotAllReduce)
+        h.world, h.max_bytes = world, _lib.W4_ONESHOT_MAX_BYTES
+        return h
+
+    assert helper(2).preferred(1 << 20) and not helper(2).preferred((1 << 20) + 16)
+    assert helper(4).preferred(999_984) and not helper(4).preferred(1 << 20)
+    assert helper(8).preferred(16384) and helper(8).preferred(499_984) and not helper(8).preferred(500_000)
+    assert not helper(8).preferred(16380)  # not a whole number of 16-byte vectors
+    h = helper(8)
+    offs = [h._offset(e) for e in (1, 2, 3, 4)]
+    assert offs[0] == offs[2] and offs[1] == offs[3] and offs[0] != offs[1]
+    assert min(offs) == tp.OneShotAllReduce.FLAG_BYTES and max(offs) == tp.OneShotAllReduce.FLAG_BYTES + h.max_bytes
