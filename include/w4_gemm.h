@@ -20,6 +20,10 @@
  *   w4_gemm_workspace_bytes  - CutlassFpAIntBGemmRunner::getWorkspaceSize (fpA_intB_gemm_template.h:577-581)
  *                              plus the smoothed-activation buffer the groupwise plugin adds
  *                              (weightOnlyGroupwiseQuantMatmulPlugin.cpp:377-379).
+ *   w4_gemm_workspace_bytes_max
+ *                            - the same, maximised over the optimisation profile's m range, which is
+ *                              what getWorkspaceSize reports at configure time
+ *                              (m_workspaceMaxSize in configurePlugin, weightOnlyGroupwiseQuantMatmulPlugin.cpp:377-379).
  *   w4_gemm_select_regime    - GemmPluginProfiler::getBestConfig, the reference's per-M choice
  *                              between its CUDA-core GEMV and a CUTLASS tactic
  *                              (cpp/tensorrt_llm/plugins/common/gemmPluginProfiler.cpp:221-250).
