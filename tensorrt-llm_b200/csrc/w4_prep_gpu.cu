@@ -85,39 +85,6 @@ __global__ void __launch_bounds__(kThreads) preprocess_kernel(uint32_t* out, uin
     emit_tile<BITS>(out, tile, k_tile, b0 * 8 / BITS, nbytes * 8 / BITS, K);
 }
 
-template <typename W>
-__device__ __forceinline__ float to_f32(W v);
-template <>
-__device__ __forceinline__ float to_f32<float>(float v)
-{
-    return v;
-}
-template <>
-__device__ __forceinline__ float to_f32<__half>(__half v)
-{
-    return __half2float(v);
-}
-template <>
-__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v)
-{
-    return __bfloat162float(v);
-}
-
-// Per-column max |w| over a slab of rows; non-negative floats order like their bit patterns, so
-// the slabs are merged with an integer atomic max (the result does not depend on the order).
-template <typename W>
-__global__ void __launch_bounds__(256) column_amax_kernel(float* amax, W const* w, int K, int N, int rows_per_block)
-{
-    int const c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= N)
-        return;
-    int const r0 = blockIdx.y * rows_per_block, r1 = min(K, r0 + rows_per_block);
-    float m = 0.f;
-    for (int r = r0; r < r1; ++r)
-        m = fmaxf(m, fabsf(to_f32(w[size_t(r) * N + c])));
-    atomicMax(reinterpret_cast<int*>(amax) + c, __float_as_int(m));
-}
-
 // amax -> scale = amax * 2^-(bits-1), in place, plus the copy rounded to the activation type.
 __global__ void finish_scales_kernel(float* scales, void* scales_t, int scales_dtype, int N, float range)
 {
@@ -135,39 +102,110 @@ __global__ void finish_scales_kernel(float* scales, void* scales_t, int scales_d
     }
 }
 
+// Eight consecutive weights of one row as floats (one or two 16-byte loads).
+template <typename W>
+__device__ __forceinline__ void load8(W const* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(float const* p, float (&x)[8])
+{
+    float4 const a = __ldg(reinterpret_cast<float4 const*>(p)), b = __ldg(reinterpret_cast<float4 const*>(p) + 1);
+    x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__half>(__half const* p, float (&x)[8])
+{
+    uint4 const v = __ldg(reinterpret_cast<uint4 const*>(p));
+    uint32_t const w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        Pair<__half>::unpack2(w[i], x[2 * i], x[2 * i + 1]);
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(__nv_bfloat16 const* p, float (&x)[8])
+{
+    uint4 const v = __ldg(reinterpret_cast<uint4 const*>(p));
+    uint32_t const w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        Pair<__nv_bfloat16>::unpack2(w[i], x[2 * i], x[2 * i + 1]);
+}
+
+// Per-column max |w| over a slab of rows, eight columns per thread (16-byte loads); non-negative
+// floats order like their bit patterns, so the slabs are merged with an integer atomic max (the
+// result does not depend on the order).
+template <typename W>
+__global__ void __launch_bounds__(256) column_amax_kernel(float* amax, W const* w, int K, int N, int rows_per_block)
+{
+    int const c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= N) // n is a multiple of 32: a thread's eight columns are all inside or all outside
+        return;
+    int const r0 = blockIdx.y * rows_per_block, r1 = min(K, r0 + rows_per_block);
+    float m[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = r0; r < r1; ++r)
+    {
+        float x[8];
+        load8<W>(w + size_t(r) * N + c0, x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            m[e] = fmaxf(m[e], fabsf(x[e]));
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+        atomicMax(reinterpret_cast<int*>(amax) + c0 + e, __float_as_int(m[e]));
+}
+
 // Quantises a tile (q = clamp(int(round(w / scale))), round half away from zero, zero column -> 0),
 // optionally stores it row-major (the reference's "unprocessed" output) and emits the kernel layout.
+// Eight columns per thread and step: 16-byte loads of the weights and the scales, one 4- or 8-byte
+// store of the packed result.
 template <typename W, int BITS>
 __global__ void __launch_bounds__(kThreads)
     quantize_kernel(uint32_t* out, uint8_t* unprocessed, W const* w, float const* scales, int K, int N)
 {
     __shared__ __align__(16) uint8_t tile[kTileK * kSmemPitch];
     constexpr int kCols = kTileBytes * 8 / BITS; // columns per tile
-    constexpr int kPer = 8 / BITS;               // columns per stored byte
+    constexpr int kVecPerRow = kCols / 8;
     int const row_bytes = N * BITS / 8;
     int const n0 = blockIdx.x * kCols;
-    int const cols = min(kCols, N - n0);
+    int const cols = min(kCols, N - n0); // a multiple of 32
     int const k_tile = blockIdx.y;
     int const lo = BITS == 8 ? -128 : -8, hi = BITS == 8 ? 127 : 7;
-    for (int i = threadIdx.x; i < kTileK * kTileBytes; i += kThreads)
+    for (int i = threadIdx.x; i < kTileK * kVecPerRow; i += kThreads)
     {
-        int const r = i / kTileBytes, b = i % kTileBytes; // consecutive threads: consecutive bytes of a row
-        if (b * kPer < cols)
-        {
-            uint32_t byte = 0;
+        int const r = i / kVecPerRow, c0 = (i % kVecPerRow) * 8;
+        if (c0 >= cols)
+            continue;
+        size_t const row = size_t(k_tile) * kTileK + r;
+        float x[8];
+        load8<W>(w + row * N + n0 + c0, x);
+        float4 const sa = __ldg(reinterpret_cast<float4 const*>(scales + n0 + c0));
+        float4 const sb = __ldg(reinterpret_cast<float4 const*>(scales + n0 + c0) + 1);
+        float const s[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+        uint32_t qv[8];
 #pragma unroll
-            for (int e = 0; e < kPer; ++e)
-            {
-                int const c = n0 + b * kPer + e;
-                float const s = scales[c];
-                float const x = to_f32(w[size_t(k_tile * kTileK + r) * N + c]);
-                float const v = s != 0.f ? roundf(__fdiv_rn(x, s)) : 0.f;
-                int const iv = max(lo, min(hi, int(v)));
-                byte |= (uint32_t(iv) & (BITS == 8 ? 0xFFu : 0xFu)) << (BITS * e);
-            }
-            tile[r * kSmemPitch + b] = uint8_t(byte);
+        for (int e = 0; e < 8; ++e)
+        {
+            float const v = s[e] != 0.f ? roundf(__fdiv_rn(x[e], s[e])) : 0.f;
+            qv[e] = uint32_t(max(lo, min(hi, int(v))));
+        }
+        if (BITS == 4)
+        {
+            uint32_t word = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                word |= (qv[e] & 0xFu) << (4 * e); // even column in the low nibble
+            *reinterpret_cast<uint32_t*>(tile + r * kSmemPitch + c0 / 2) = word;
             if (unprocessed)
-                unprocessed[size_t(k_tile * kTileK + r) * row_bytes + n0 / kPer + b] = uint8_t(byte);
+                *reinterpret_cast<uint32_t*>(unprocessed + row * row_bytes + (n0 + c0) / 2) = word;
+        }
+        else
+        {
+            uint2 word;
+            word.x = (qv[0] & 0xFFu) | ((qv[1] & 0xFFu) << 8) | ((qv[2] & 0xFFu) << 16) | (qv[3] << 24);
+            word.y = (qv[4] & 0xFFu) | ((qv[5] & 0xFFu) << 8) | ((qv[6] & 0xFFu) << 16) | (qv[7] << 24);
+            *reinterpret_cast<uint2*>(tile + r * kSmemPitch + c0) = word;
+            if (unprocessed)
+                *reinterpret_cast<uint2*>(unprocessed + row * row_bytes + n0 + c0) = word;
         }
     }
     __syncthreads();
@@ -186,8 +224,8 @@ int quantize_typed(void* processed, void* unprocessed, float* scales, void* scal
 {
     if (cudaMemsetAsync(scales, 0, size_t(n) * sizeof(float), stream) != cudaSuccess)
         return W4_ERR_CUDA;
-    int const rows_per_block = 256;
-    dim3 const ga((n + 255) / 256, (k + rows_per_block - 1) / rows_per_block);
+    int const rows_per_block = 64;
+    dim3 const ga((n + 2047) / 2048, (k + rows_per_block - 1) / rows_per_block);
     column_amax_kernel<W><<<ga, 256, 0, stream>>>(scales, w, k, n, rows_per_block);
     finish_scales_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scales, scales_t, scales_dtype, n,
         1.f / float(1 << (bits - 1)));
@@ -245,7 +283,9 @@ extern "C"
             return W4_ERR_BAD_DTYPE;
         if (!shape_ok(long(k), long(n), bits))
             return W4_ERR_BAD_SHAPE;
-        if (reinterpret_cast<uintptr_t>(processed) & 15u)
+        if ((reinterpret_cast<uintptr_t>(processed) | reinterpret_cast<uintptr_t>(unprocessed)
+                | reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(weight))
+            & 15u)
             return W4_ERR_MISALIGNED;
         cudaStream_t const s = static_cast<cudaStream_t>(stream);
         switch (weight_dtype)
