@@ -96,6 +96,22 @@ extern "C"
     };
 
     /*
+     * W4GemmParams.flags.
+     * W4_GEMM_WEIGHTS_STATIC: weight, scales, zeros and act_scale were completely written before the
+     * kernel that precedes this GEMM on the stream was launched (true for inference weights, which
+     * are written once at load time). The decode kernel is a programmatic dependent launch: with
+     * this bit it starts fetching those tensors while the preceding kernel is still running and
+     * waits for that kernel only before it reads `act` and writes `out`. Without the bit it waits
+     * before its first fetch, which is always safe - set it only when the statement above holds
+     * (it does NOT hold for a GEMM enqueued right behind w4_symmetric_quantize_device,
+     * w4_preprocess_weights_device or any other kernel that writes the weights).
+     */
+    enum
+    {
+        W4_GEMM_WEIGHTS_STATIC = 1
+    };
+
+    /*
      * out[m, n] = alpha * sum_k (act[m, k] * act_scale[k]) * (q[k, n] * scales[g(k), n] + zeros[g(k), n]) + bias[n]
      *
      *   act        [m, k] row-major, fp16 or bf16 (act_dtype)            device, mandatory
@@ -131,6 +147,7 @@ extern "C"
         int regime;      /* W4_REGIME_* */
         void* workspace;
         size_t workspace_bytes;
+        unsigned flags; /* W4_GEMM_* bits, 0 = none */
     } W4GemmParams;
 
     int w4_gemm_version(void);

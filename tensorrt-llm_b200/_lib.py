@@ -35,9 +35,12 @@ class W4GemmParams(ctypes.Structure):
         ("out", ctypes.c_void_p), ("alpha", ctypes.c_float), ("m", ctypes.c_int), ("n", ctypes.c_int),
         ("k", ctypes.c_int), ("group_size", ctypes.c_int), ("weight_bits", ctypes.c_int),
         ("act_dtype", ctypes.c_int), ("regime", ctypes.c_int), ("workspace", ctypes.c_void_p),
-        ("workspace_bytes", ctypes.c_size_t),
+        ("workspace_bytes", ctypes.c_size_t), ("flags", ctypes.c_uint),
     ]
 
+
+# W4GemmParams.flags
+W4_GEMM_WEIGHTS_STATIC = 1
 
 W4_MAX_RANKS = 8
 W4_ONESHOT_MAX_BYTES = 1 << 20

@@ -100,7 +100,7 @@ extern "C"
 
     int w4_gemm_version(void)
     {
-        return 100;
+        return 110;
     }
 
     const char* w4_status_string(int status)

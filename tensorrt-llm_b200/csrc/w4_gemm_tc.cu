@@ -32,7 +32,7 @@
 // against ~40 from a converged warp; scale/zero loads need several groups of lookahead because a
 // step is shorter than an L2 round trip.
 // All waits are bounded; a timeout sets the device status word and the CTA drains and exits.
-#include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "w4_common.cuh"
@@ -85,48 +85,8 @@ struct __align__(16) Barriers
     alignas(16) uint32_t ready[kConvGroups][4];
     uint32_t tmem_base;
     int abort_flag;
-#ifdef W4_DBG_TRACE
-    long long issue_time[kMaxStages];
-    long long tl[8][16]; // [event][step - 100] time line of tile 0, steps 100..115
-#endif
 };
 
-#ifdef W4_DBG_TRACE
-// Debug build only: cycles CTA 0 spent in each kind of wait, per role.
-__device__ long long g_tc_trace[192];
-#define W4_TC_TIMED(slot_, expr_)                                                                                     \
-    do                                                                                                                 \
-    {                                                                                                                  \
-        long long t0_ = clock64();                                                                                     \
-        expr_;                                                                                                         \
-        dbg_acc[(slot_) & 3] += clock64() - t0_;                                                                       \
-    } while (0)
-#define W4_TC_TL(ev_, ks_, first_)                                                                                     \
-    do                                                                                                                 \
-    {                                                                                                                  \
-        if (blockIdx.x == 0 && (first_) && (ks_) >= 100 && (ks_) < 116)                                                \
-            bars->tl[ev_][(ks_) -100] = clock64();                                                                     \
-    } while (0)
-#define W4_TC_PHASE(i_)                                                                                                \
-    do                                                                                                                 \
-    {                                                                                                                  \
-        long long now_ = clock64();                                                                                    \
-        dbg_ph[i_] += now_ - dbg_last;                                                                                 \
-        dbg_last = now_;                                                                                               \
-    } while (0)
-#define W4_TC_FLUSH(base_)                                                                                             \
-    do                                                                                                                 \
-    {                                                                                                                  \
-        if (blockIdx.x == 0 && lane == 0)                                                                              \
-            for (int i_ = 0; i_ < 4; ++i_)                                                                             \
-                g_tc_trace[(base_) + i_] = dbg_acc[i_];                                                                \
-    } while (0)
-#else
-#define W4_TC_TIMED(slot_, expr_) expr_
-#define W4_TC_FLUSH(base_)
-#define W4_TC_PHASE(i_)
-#define W4_TC_TL(ev_, ks_, first_)
-#endif
 
 __device__ __forceinline__ bool wait_flag(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
@@ -307,18 +267,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile int* abort_flag = &bars->abort_flag;
 
     int const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef W4_DBG_TRACE
-    long long dbg_acc[4] = {0, 0, 0, 0};
-    long long dbg_ph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long dbg_last = clock64();
-    if (blockIdx.x == 0 && threadIdx.x == 0)
-    {
-        for (int i = 0; i < 32; ++i)
-            g_tc_trace[i] = 0;
-        g_tc_trace[33] = clock64();
-    }
-    __syncthreads();
-#endif
     int const num_tiles = a.tiles_n * a.tiles_m * (SPLITK ? a.splits : 1); // work items: (tile, split), splits adjacent
     int const ksteps_all = (a.k + BK - 1) / BK; // a trailing 64-wide half reads as zeros (TMA fill)
 
@@ -372,21 +320,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
                 for (int ks = ks0; ks < ks1; ++ks)
                 {
-                    W4_TC_TIMED(0, ok = spin_wait(done0 + 8 * s, ph ^ 1, abort_flag));
+                    ok = spin_wait(done0 + 8 * s, ph ^ 1, abort_flag);
                     if (!ok)
                         break;
-                    W4_TC_TL(0, ks, tile == 0 && lane == 0);
                     uint32_t const stage = smem_base + uint32_t(s) * STAGE_BYTES;
                     uint32_t const full = full0 + 8 * s;
-#ifdef W4_DBG_TRACE
-                    if (lane == 0)
-                        bars->issue_time[s] = clock64();
-#endif
                     elect_expect_tx(full, STAGE_BYTES);
                     elect_tma_load_2d(stage, &tm_act, ks * BK, tm * BM, full);
                     elect_tma_load_2d(stage + ACT_HALF, &tm_act, ks * BK + 64, tm * BM, full);
                     elect_tma_load_2d(stage + ACT_BYTES, &tm_w, ks * 128 * kHalves, tn * (BN / IL), full);
-                    W4_TC_TL(1, ks, tile == 0 && lane == 0);
                     if (++s == a.num_stages)
                     {
                         s = 0;
@@ -422,7 +364,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
                 if (it > 0)
                 {
-                    W4_TC_TIMED(3, ok = spin_wait(d_empty, dph, abort_flag));
+                    ok = spin_wait(d_empty, dph, abort_flag);
                     if (!ok)
                         break;
                     dph ^= 1;
@@ -435,13 +377,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                     // barrier, so it covers the activations as well.
                     uint32_t const grp = uint32_t(ks) % kConvGroups; // the group that converts this step
                     uint32_t const needed = ++issued[grp];
-                    W4_TC_TIMED(2, ok = spin_ready(ready0 + 16 * grp, needed, abort_flag));
+                    ok = spin_ready(ready0 + 16 * grp, needed, abort_flag);
                     if (!ok)
                         break;
-                    W4_TC_TL(3, ks, tile == 0 && lane == 0);
-                    W4_TC_PHASE(0);
                     tc_fence_after();
-                    W4_TC_PHASE(1);
                     tc_mma_ts_elect(tmem, a_col, desc, kIdesc, accumulate);
                     tc_mma_ts_elect(tmem, a_col + 8, desc + 2, kIdesc, 1u);
                     tc_mma_ts_elect(tmem, a_col + 16, desc + 4, kIdesc, 1u);
@@ -452,10 +391,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tc_mma_ts_elect(tmem, a_col + 48, desc + kDescHalf + 4, kIdesc, 1u);
                     tc_mma_ts_elect(tmem, a_col + 56, desc + kDescHalf + 6, kIdesc, 1u);
                     accumulate = 1u;
-                    W4_TC_PHASE(2);
                     tc_commit_elect(done); // frees the shared-memory stage and the TMEM stage
-                    W4_TC_PHASE(3);
-                    W4_TC_TL(4, ks, tile == 0 && lane == 0);
                     desc += kDescStage;
                     a_col += 32 * kHalves;
                     done += 8;
@@ -550,16 +486,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                     s2h[h] = s2;
                     z2h[h] = z2;
                 }
-                if ((ks % kConvGroups) == cgroup)
+                // A group converts every second k step. With an odd number of stages it would meet a
+                // given stage's barrier only in every second phase and always ask for the same parity,
+                // which a late copy of the phase in between could satisfy early; in that case both groups
+                // observe every phase (the group that does not convert the step merely waits for it).
+                bool const mine = (ks % kConvGroups) == cgroup;
+                if (mine || (a.num_stages & 1))
                 {
-                    W4_TC_PHASE(0); // idle / skipped steps
-                    W4_TC_TIMED(4 + 4 * quad, ok = wait_flag_warp(&bars->full[s], ph, abort_flag, lane));
+                    ok = wait_flag_warp(&bars->full[s], ph, abort_flag, lane);
                     if (!ok)
                         break;
-                    W4_TC_PHASE(1); // waited for TMA
-#ifdef W4_DBG_TRACE
-                    dbg_ph[6] += clock64() - bars->issue_time[s];
-#endif
+                }
+                if (mine)
+                {
                     uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
                     constexpr int CHUNKS = SEG / 16; // 16-byte chunks per half: 2 (int4) or 4 (int8)
                     uint4 raw[kHalves][CHUNKS];
@@ -568,7 +507,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                         for (int c = 0; c < CHUNKS; ++c)
                             raw[h][c] = *reinterpret_cast<uint4 const*>(wsm + h * 128 + c * 16);
-                    W4_TC_PHASE(2); // shared loads + release
                     // Convert into registers first; only the stores have to wait for the TMEM stage.
                     // v[2h + x] holds TMEM columns 32h + 16x .. +15 (k = 64h + 32x .. +31).
                     uint32_t v[2 * kHalves][16];
@@ -615,12 +553,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                                 }
                         }
                     }
-                    W4_TC_PHASE(3); // conversion
-                    W4_TC_TIMED(5 + 4 * quad, ok = wait_flag_warp(&bars->done[s], ph ^ 1, abort_flag, lane));
+                    ok = wait_flag_warp(&bars->done[s], ph ^ 1, abort_flag, lane);
                     if (!ok)
                         break;
                     tc_fence_after();
-                    W4_TC_PHASE(4); // waited for the TMEM stage
                     uint32_t const a_addr = lane_addr + kACol0 + s * (32 * kHalves); // warp-uniform column address
 #pragma unroll
                     for (int x = 0; x < 2 * kHalves; ++x)
@@ -635,8 +571,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                                      "r"(my_steps)
                                      : "memory");
                     }
-                    W4_TC_PHASE(5); // tcgen05.st + wait + signal
-                    W4_TC_TL((quad == 0 ? 2 : 4 + quad), ks, tile == 0 && lane == 0);
                 }
                 if (++s == a.num_stages)
                 {
@@ -648,7 +582,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
 
             // ---- epilogue: this thread owns output column n for all BM rows of the tile
-            W4_TC_TIMED(6 + 4 * quad, ok = wait_flag_warp(&bars->d_full, dph, abort_flag, lane));
+            ok = wait_flag_warp(&bars->d_full, dph, abort_flag, lane);
             if (!ok)
                 break;
             dph ^= 1;
@@ -712,31 +646,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     }
 
-#ifdef W4_DBG_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0)
-        g_tc_trace[32] = clock64();
-#endif
-#ifdef W4_DBG_TRACE
-    if (warp == 2 && blockIdx.x == 0 && lane == 0)
-        for (int i = 0; i < 8; ++i)
-            g_tc_trace[48 + i] = dbg_ph[i];
-    if (warp == 1 && blockIdx.x == 0 && lane == 0)
-        for (int i = 0; i < 4; ++i)
-            g_tc_trace[56 + i] = dbg_ph[i];
-#endif
-    if (warp == 0)
-        W4_TC_FLUSH(40);
-    else if (warp == 1)
-        W4_TC_FLUSH(0);
-    else if (warp < 6)
-        W4_TC_FLUSH(4 + 4 * (warp & 3));
     // Teardown: everyone meets here (also after a timeout), then the allocating warp frees TMEM.
     tc_fence_before();
     __syncthreads();
-#ifdef W4_DBG_TRACE
-    if (blockIdx.x == 0 && threadIdx.x < 128)
-        g_tc_trace[64 + threadIdx.x] = bars->tl[threadIdx.x >> 4][threadIdx.x & 15];
-#endif
     if (warp == 1)
     {
         tc_fence_after();
@@ -841,13 +753,6 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
     if (stages < 2)
         return W4_ERR_CUDA;
     a.num_stages = stages > kMaxStages ? kMaxStages : stages;
-    static int const st_override = []
-    {
-        char const* e = getenv("W4_TC_STAGES"); // tuning aid: fewer pipeline stages
-        return e ? atoi(e) : 0;
-    }();
-    if (st_override > 1 && st_override < a.num_stages)
-        a.num_stages = st_override;
     size_t const smem = size_t(a.num_stages) * STAGE_BYTES + fixed;
 
     // Activations [m, k] of T, boxes of 64 k x BM rows, 128-byte swizzle (rows past m read as 0).
@@ -862,14 +767,19 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
             uint64_t(p.k) * 2, 128 * kHalves, BN / IL, CU_TENSOR_MAP_SWIZZLE_NONE))
         return W4_ERR_CUDA;
 
-    static bool configured[64] = {};
-    if (dev.device < 0 || dev.device >= 64 || !configured[dev.device])
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin)
-            != cudaSuccess)
-            return W4_ERR_CUDA;
-        if (dev.device >= 0 && dev.device < 64)
-            configured[dev.device] = true;
+        // per-function, per-device attribute: set once (this block is instantiated once per kernel)
+        static std::mutex mu;
+        static bool configured[64] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev.device < 0 || dev.device >= 64 || !configured[dev.device])
+        {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin)
+                != cudaSuccess)
+                return W4_ERR_CUDA;
+            if (dev.device >= 0 && dev.device < 64)
+                configured[dev.device] = true;
+        }
     }
     int const tiles = a.tiles_n * a.tiles_m * (SPLITK ? a.splits : 1);
     int const grid = tiles < dev.num_sms ? tiles : dev.num_sms;
@@ -886,12 +796,7 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
 template <typename T, int BITS, bool HAS_ZERO>
 static int dispatch_bm(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
 {
-    static int const bm_override = []
-    {
-        char const* e = getenv("W4_TC_BM"); // tuning aid: force the activation-row tile
-        return e ? atoi(e) : 0;
-    }();
-    int const bm = bm_override ? bm_override : gemm_tc_row_tile(p.m, p.n, dev.num_sms);
+    int const bm = gemm_tc_row_tile(p.m, p.n, dev.num_sms);
     // Split-k when the tiles alone would leave most SMs idle and the caller's workspace has room
     // for the partial tiles; the unsplit kernel is a separate instantiation without any of it.
     int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms);
@@ -931,12 +836,6 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 
 } // namespace tc
 
-#ifdef W4_DBG_TRACE
-extern "C" int w4_dbg_read_tc_trace(long long* out)
-{
-    return cudaMemcpyFromSymbol(out, tc::g_tc_trace, sizeof(long long) * 192) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // Microseconds one CTA spends per 128-wide k step, by row tile (measured on B200, bf16 x int4,
 // group 128): up to 192 rows the step is bound by the conversion / hand-off pipeline, not by its

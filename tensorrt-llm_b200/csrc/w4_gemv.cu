@@ -40,7 +40,7 @@
 //    max|ref| bound this path is held to.
 // In both, the pre-quant scale product is rounded to T (utility.h:116) and alpha * acc + bias is
 // formed in fp32 (utility.h:256-266).
-#include <cstdlib>
+#include <mutex>
 
 #include "w4_common.cuh"
 #include "w4_internal.h"
@@ -148,6 +148,7 @@ struct Args
     int box_stride;       // bytes between the scale box and the zero box (multiple of 128)
     int depth;            // tiles kept in flight ahead of the one being consumed
     int red_bytes;        // shared memory for the cross-warp partial sums
+    int weights_static;   // weights / scales / zeros were complete before the preceding kernel started
 };
 
 // Shared flag: once any wait in the CTA timed out, every later wait returns at once.
@@ -163,24 +164,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     *abort_flag = 1;
     atomicExch(&g_device_status, kDeviceTimeout);
     return false;
-}
-
-#ifdef W4_DBG_TRACE
-// Debug build only: per-warp time stamps of CTA 0 (never compiled into the product library).
-__device__ long long g_trace[16 * 64];
-#define W4_STAMP(slot_)                                                                                                \
-    do                                                                                                                 \
-    {                                                                                                                  \
-        if (blockIdx.x == 0 && lane == 0 && (slot_) < 60 + 4 * ((slot_) >= 60))                                                               \
-            g_trace[warp * 64 + (slot_)] = clock64();                                                                  \
-    } while (0)
-#else
-#define W4_STAMP(slot_)
-#endif
-
-__device__ __forceinline__ void prefetch_l2(void const* p)
-{
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
@@ -272,12 +255,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         if (HAS_ZERO)
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_zeros) : "memory");
     }
-    W4_STAMP(0);
     __syncthreads();
-    W4_STAMP(1);
     // Programmatic dependent launch: let the next kernel in the stream begin its own prologue as
-    // SMs free up. Everything up to the activation load touches only weights, scales and zeros,
-    // which no earlier kernel writes, so it may run ahead of the kernel before this one.
+    // SMs free up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---------------------------------------------------------------------- producer
@@ -285,13 +265,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // and (b) tile j - depth has fully arrived: only `depth` tiles share the memory pipe, so they
     // land in order and early enough to overlap with the arithmetic (the copy engine serves all
     // outstanding copies side by side: started together they would also all finish together).
-    // The producer touches only weights, scales and zeros, so it does not wait for the preceding
-    // kernel.
+    // The producer touches only weights, scales and zeros; it runs ahead of the preceding kernel
+    // only when the caller declared them static (W4_GEMM_WEIGHTS_STATIC).
     if (warp >= kWarps)
     {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProducerRegs));
         if (warp == kWarps && lane == 0)
         {
+            // Weights that the preceding kernel may still be writing must not be fetched early.
+            if (!a.weights_static)
+                asm volatile("griddepcontrol.wait;" ::: "memory");
             int slot = 0, use = 0;
             for (int j = 0; j < num_tiles; ++j)
             {
@@ -575,15 +558,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         }
     };
 
-    W4_STAMP(2);
     // Activations (and, later, the output) belong to the preceding kernels: wait for them here.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (num_cg > 0)
         load_act(0);
-    W4_STAMP(3);
 
     bool ok = true;
-    int slot = 0, use = 0, tile_index = 0;
+    int slot = 0, use = 0;
     bool first_act = true; // the first activation fragments were loaded above
     for (int cg0 = 0; cg0 < num_cg; cg0 += batch)
     {
@@ -615,17 +596,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                         ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
                     }
                     uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
-                    W4_STAMP(4 + 2 * tile_index);
-#ifndef W4_DBG_NOCOMPUTE
 #pragma unroll
                     for (int j = 0; j < C::UPW; ++j)
                         process_unit(j, cg, tile, acc[ci]);
-#endif
-                    W4_STAMP(5 + 2 * tile_index);
                     __syncwarp();
                     if (lane == 0)
                         mbar_arrive(&empty_bar[slot]);
-                    ++tile_index;
                     if (++slot == a.num_slots)
                     {
                         slot = 0;
@@ -651,9 +627,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         }
 
         // Combine the 16 warps' partial sums in a fixed order and write this batch of columns.
-        W4_STAMP(60);
         named_bar_sync(1, kConsumerThreads);
-        W4_STAMP(61);
         constexpr int MPAD = 8 * MB;
         for (int o = tid; o < nb * 16 * MPAD; o += kConsumerThreads)
         {
@@ -678,7 +652,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         }
         if (cg0 + batch < num_cg)
             named_bar_sync(1, kConsumerThreads);
-        W4_STAMP(62);
     }
 }
 
@@ -706,15 +679,6 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     // barrier, and fewer of them measured faster than the two ring slots this costs (four slots
     // remain; ~72 KB are in flight at a time anyway).
     args.red_bytes = kRedBytes;
-    {
-        static int const red_override = []
-        {
-            char const* e = getenv("W4_GEMV_RED_KB"); // tuning aid
-            return e ? atoi(e) : 0;
-        }();
-        if (red_override > 0)
-            args.red_bytes = red_override * 1024;
-    }
     size_t const fixed = size_t(args.red_bytes) + 64;
     // Shared memory per CTA: all a block may have, or half of the SM's 228 KB less the 1 KB the
     // system reserves per block when two CTAs are to fit.
@@ -726,13 +690,8 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
         slots = 12;
     args.num_slots = slots;
     // Tiles in flight ahead of the consumers: about 72 KB per SM covers the HBM latency-bandwidth
-    // product with margin. W4_GEMV_DEPTH overrides it (tuning aid).
-    static int const depth_override = []
-    {
-        char const* e = getenv("W4_GEMV_DEPTH");
-        return e ? atoi(e) : 0;
-    }();
-    int depth = depth_override > 0 ? depth_override : (72 * 1024 + args.slot_bytes / 2) / args.slot_bytes;
+    // product with margin.
+    int depth = (72 * 1024 + args.slot_bytes / 2) / args.slot_bytes;
     args.depth = depth < 1 ? 1 : (depth > slots - 1 ? slots - 1 : depth);
     size_t const smem = size_t(slots) * args.slot_bytes + fixed + size_t(slots) * 16;
 
@@ -750,14 +709,18 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
         return W4_ERR_CUDA;
 
     // The opt-in shared-memory limit is a per-function, per-device attribute: set it once.
-    static bool configured[64] = {};
-    if (dev.device < 0 || dev.device >= 64 || !configured[dev.device])
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin)
-            != cudaSuccess)
-            return W4_ERR_CUDA;
-        if (dev.device >= 0 && dev.device < 64)
-            configured[dev.device] = true;
+        static std::mutex mu;
+        static bool configured[64] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev.device < 0 || dev.device >= 64 || !configured[dev.device])
+        {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin)
+                != cudaSuccess)
+                return W4_ERR_CUDA;
+            if (dev.device >= 0 && dev.device < 64)
+                configured[dev.device] = true;
+        }
     }
     int const grid = args.num_rows < dev.num_sms ? args.num_rows : dev.num_sms;
     {
@@ -768,12 +731,7 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
             return W4_ERR_BAD_SHAPE;
     }
     // Launched as a programmatic dependent of whatever precedes it in the stream (the kernel
-    // orders itself with griddepcontrol.wait). W4_GEMV_PDL=0 turns the attribute off.
-    static bool const use_pdl = []
-    {
-        char const* e = getenv("W4_GEMV_PDL");
-        return !(e && e[0] == '0');
-    }();
+    // orders itself with griddepcontrol.wait).
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -783,7 +741,7 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = use_pdl ? 1 : 0;
+    cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kernel, args, tm_scales, tm_zeros) != cudaSuccess)
         return W4_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
@@ -827,13 +785,6 @@ static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev,
 
 } // namespace gemv
 
-#ifdef W4_DBG_TRACE
-extern "C" int w4_dbg_read_trace(long long* out)
-{
-    return cudaMemcpyFromSymbol(out, gemv::g_trace, sizeof(long long) * 16 * 64) == cudaSuccess ? 0 : -1;
-}
-#endif
-
 int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
 {
     DeviceInfo const& dev = current_device_info();
@@ -845,6 +796,14 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
     for (int m0 = 0; m0 < p.m; m0 += 8)
     {
         int const rows = p.m - m0 < 8 ? p.m - m0 : 8;
+        // Activations small enough to stay in shared memory: the second form of the kernel.
+        if (gemv2::supports(p, rows, dev))
+        {
+            int const rc = gemv2::launch(p, m0, rows, dev, stream);
+            if (rc != W4_OK)
+                return rc;
+            continue;
+        }
         gemv::Args a{};
         a.weight = static_cast<uint8_t const*>(p.weight);
         a.act = static_cast<char const*>(p.act) + size_t(m0) * p.k * elt;
@@ -860,6 +819,7 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
         a.group_shift = p.group_size == 64 ? 6 : (p.group_size == 128 ? 7 : 31);
         a.num_groups = p.group_size ? p.k / p.group_size : 1;
         a.num_rows = p.n / (p.weight_bits == 4 ? 4 : 2);
+        a.weights_static = (p.flags & W4_GEMM_WEIGHTS_STATIC) ? 1 : 0;
         int const mb = 1;
         int const rc = p.act_dtype == W4_DTYPE_FP16 ? gemv::dispatch_bits<__half>(a, p.weight_bits, mb, dev, stream)
                                                     : gemv::dispatch_bits<__nv_bfloat16>(a, p.weight_bits, mb, dev, stream);

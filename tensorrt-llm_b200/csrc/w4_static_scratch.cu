@@ -9,6 +9,8 @@
 //
 // The array costs W4_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library,
 // from load until the process exits, whether or not this entry point is ever called.
+#include <mutex>
+
 #include "w4_common.cuh"
 #include "w4_internal.h"
 

@@ -62,14 +62,17 @@ def workspace_bytes_max(max_m: int, n: int, k: int, group_size: int, weight_bits
 
 def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, group_size: int, zeros=None,
              bias=None, act_scale=None, alpha: float = 1.0, regime: int = W4_REGIME_AUTO, workspace=None,
-             stream: Optional[int] = None) -> None:
-    """Thin wrapper of w4_gemm_launch: borrows every pointer, allocates nothing, returns at once."""
+             stream: Optional[int] = None, weights_static: bool = False) -> None:
+    """Thin wrapper of w4_gemm_launch: borrows every pointer, allocates nothing, returns at once.
+    ``weights_static`` sets W4_GEMM_WEIGHTS_STATIC: weight / scales / zeros / act_scale were written
+    before the kernel preceding this call on the stream was launched (inference weights)."""
     m = act.numel() // k if k else 0
     params = W4GemmParams(
         act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros),
         bias=_p(bias), out=_p(out), alpha=float(alpha), m=m, n=n, k=k, group_size=group_size,
         weight_bits=weight_bits, act_dtype=_DTYPES[act.dtype], regime=regime, workspace=_p(workspace),
-        workspace_bytes=workspace.numel() * workspace.element_size() if workspace is not None else 0)
+        workspace_bytes=workspace.numel() * workspace.element_size() if workspace is not None else 0,
+        flags=_lib.W4_GEMM_WEIGHTS_STATIC if weights_static else 0)
     if stream is None:
         stream = torch.cuda.current_stream(act.device).cuda_stream
     with torch.cuda.device(act.device):
@@ -77,7 +80,8 @@ def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, grou
     _lib.check(rc, "w4_gemm_launch")
 
 
-def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime, out=None):
+def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime, out=None,
+         weights_static=False):
     for name, t in (("act", act), ("weight", weight), ("scales", scales)):
         _require_cuda(t, name)
     if act.dtype not in _DTYPES:
@@ -103,23 +107,26 @@ def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_
     ws_bytes = workspace_bytes(m, n, k, group_size, weight_bits, act.dtype, act_scale is not None, regime)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=act.device) if ws_bytes else None
     gemm_raw(act, weight, scales, out, n=n, k=k, weight_bits=weight_bits, group_size=group_size, zeros=zeros,
-             bias=bias, act_scale=act_scale, alpha=alpha, regime=regime, workspace=ws)
+             bias=bias, act_scale=act_scale, alpha=alpha, regime=regime, workspace=ws,
+             weights_static=weights_static)
     return out
 
 
 def weight_only_quant_matmul(act: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor,
-                             weight_type_id: int, regime: int = W4_REGIME_AUTO) -> torch.Tensor:
+                             weight_type_id: int, regime: int = W4_REGIME_AUTO,
+                             weights_static: bool = False) -> torch.Tensor:
     """Per-channel W8A16 / W4A16: act [.., K] x weight int8 [K, N*bits/8] (preprocessed) with
-    scales [N]. weight_type_id: 1 = int8, 2 = int4."""
+    scales [N]. weight_type_id: 1 = int8, 2 = int4. ``weights_static``: see ``gemm_raw``."""
     if weight_type_id not in (WEIGHT_TYPE_INT8, WEIGHT_TYPE_INT4):
         raise RuntimeError(f"wTypeId={weight_type_id} is not supported")
     bits = 8 if weight_type_id == WEIGHT_TYPE_INT8 else 4
-    return _run(act, weight, scales, None, None, None, 1.0, bits, 0, regime)
+    return _run(act, weight, scales, None, None, None, 1.0, bits, 0, regime, weights_static=weights_static)
 
 
 def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zeros, bias, alpha: float,
                                        quant_algo: int, group_size: int,
-                                       regime: int = W4_REGIME_AUTO, out=None) -> torch.Tensor:
+                                       regime: int = W4_REGIME_AUTO, out=None,
+                                       weights_static: bool = False) -> torch.Tensor:
     """Groupwise W4A16 / W8A16 (GPTQ / AWQ). quant_algo bits: 1 bias, 2 zero, 4 pre-quant scale,
     8 fp8 alpha (W4A8, not supported), 16 int8 weight. Optional tensors must be present exactly
     when their bit is set. The weight may be viewed as the activation dtype, as the plugin takes it."""
@@ -132,7 +139,8 @@ def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zer
         if bool(quant_algo & bit) != (t is not None):
             raise RuntimeError(f"{name} must be given exactly when its quant_algo bit is set")
     bits = 8 if quant_algo & INT8_WEIGHT else 4
-    return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime, out)
+    return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime, out,
+                weights_static=weights_static)
 
 
 class _PluginBase:
@@ -147,6 +155,10 @@ class _PluginBase:
         self.type_id = type_id
         self.dtype = _TRT_TO_TORCH[type_id]
         self.dims = None  # (minM, maxM, n, k) once configured
+        # TensorRT-LLM feeds these plugins engine constants (weights, scales, zeros, pre-quant
+        # scale are network parameters), so the decode kernel may fetch them ahead of the
+        # preceding layer's kernel. Clear it when a layer computes the weights on the fly.
+        self.weights_static = True
 
     def get_nb_outputs(self) -> int:
         return 1
@@ -198,7 +210,7 @@ class WeightOnlyQuantMatmulPlugin(_PluginBase):
             if act.numel() == 0:
                 return 0
             gemm_raw(act, weight, scales, outputs[0], n=n, k=k, weight_bits=self.bits, group_size=0,
-                     regime=regime, workspace=workspace, stream=stream)
+                     regime=regime, workspace=workspace, stream=stream, weights_static=self.weights_static)
             return 0
         except _lib.W4Error as e:
             return e.status
@@ -273,7 +285,8 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
                      zeros=inputs[self.zeros_idx] if self.quant_algo & ZERO else None,
                      bias=inputs[self.bias_idx] if self.quant_algo & BIAS else None,
                      act_scale=inputs[self.pre_quant_scale_idx] if self.quant_algo & PRE_QUANT_SCALE else None,
-                     alpha=self.alpha, regime=regime, workspace=workspace, stream=stream)
+                     alpha=self.alpha, regime=regime, workspace=workspace, stream=stream,
+                     weights_static=self.weights_static)
             return 0
         except _lib.W4Error as e:
             return e.status

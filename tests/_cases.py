@@ -50,3 +50,40 @@ def run_gpu(p, regime=0, alpha=1.0, device="cuda"):
 
 def max_err(out, ref):
     return float((out.to(torch.float64) - ref.to(torch.float64)).abs().max())
+
+
+def oracle_subset(p, rows, cols, alpha=1.0):
+    """The tight oracle on a sample of activation rows and output columns (large shapes: the
+    float64 reference of the whole problem would take minutes on the host)."""
+    rows = torch.as_tensor(rows, dtype=torch.long)
+    cols = torch.as_tensor(cols, dtype=torch.long)
+    pick = (lambda t: None if t is None else t[..., cols])
+    return oracle.kernel_rounding_ref(p["act"][rows], p["q"][:, cols], pick(p["scales"]), zeros=pick(p["zeros"]),
+                                      bias=pick(p["bias"]), pre_quant_scale=p["ps"], group_size=p["group"], alpha=alpha)
+
+
+def sample_rows(m, tile=192, extra=8, seed=0):
+    """Row sample that hits the first and last row of every `tile`-row block (the prefill kernel's
+    largest row tile is 256, its usual one 192; both boundaries are included), the ragged last block
+    and a few random rows."""
+    if m <= 64:
+        return list(range(m))
+    rows = {0, m - 1}
+    for t in (128, 192, 256):
+        for b in range(0, m, t):
+            rows.update((b, min(m - 1, b + t - 1)))
+    g = torch.Generator().manual_seed(seed)
+    rows.update(int(x) for x in torch.randint(0, m, (extra,), generator=g))
+    rows = sorted(rows)
+    if len(rows) > 96:  # keep the oracle cheap: boundaries of a spread of blocks
+        step = len(rows) / 96.0
+        rows = sorted({rows[int(i * step)] for i in range(96)} | {0, m - 1})
+    return rows
+
+
+def sample_cols(n, count=384, seed=0):
+    """First and last 128-column tile plus random columns."""
+    cols = set(range(min(n, 128))) | set(range(max(0, n - 128), n))
+    g = torch.Generator().manual_seed(seed + 1)
+    cols.update(int(x) for x in torch.randint(0, n, (count,), generator=g))
+    return sorted(cols)

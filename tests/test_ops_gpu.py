@@ -1,0 +1,120 @@
+"""The operator boundary on the GPU (needs a B200): the C++ torch.ops.trtllm GEMM ops and both
+plugin mirrors' enqueue, every quant_algo input layout, against the CPU oracle."""
+import itertools
+
+import pytest
+import torch
+
+import tensorrt_llm_b200 as pkg
+import tensorrt_llm_b200.torch_ops  # noqa: F401  (loads the C++ registrations)
+from tensorrt_llm_b200 import ops
+from oracle import woq_oracle as oracle
+from _cases import make_problem, max_err, oracle_out
+
+pytestmark = pytest.mark.gpu
+
+
+def _d(t):
+    return None if t is None else t.to("cuda")
+
+
+def _assert_close(out, p, alpha=1.0):
+    ref = oracle_out(p, alpha=alpha)
+    assert out.shape == ref.shape and out.dtype == ref.dtype
+    assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)  # 1e-2 * max|ref|
+    assert pkg._lib.lib().w4_gemm_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m", [1, 16, 300])
+def test_torch_op_per_channel(dtype, bits, m):
+    p = make_problem(m, 1024, 512, bits, 0, dtype, seed=m, scale_lo=0.0005, scale_hi=0.002)
+    out = torch.ops.trtllm.weight_only_quant_gemm(_d(p["act"]), _d(p["processed"]), _d(p["scales"]),
+                                                  1 if bits == 8 else 2)
+    _assert_close(out, p)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 12, 256])
+@pytest.mark.parametrize("bias,zero,prequant,int8", list(itertools.product([False, True], repeat=4)))
+def test_torch_op_groupwise_every_algo(dtype, m, bias, zero, prequant, int8):
+    p = make_problem(m, 512, 1024, 8 if int8 else 4, 128, dtype, zero=zero, bias=bias, prequant=prequant, seed=3 + m)
+    algo = (pkg.BIAS if bias else 0) | (pkg.ZERO if zero else 0) | (pkg.PRE_QUANT_SCALE if prequant else 0) \
+        | (pkg.INT8_WEIGHT if int8 else 0)
+    out = torch.ops.trtllm.weight_only_groupwise_quant_gemm(
+        _d(p["act"]), _d(p["ps"]), _d(p["processed"]), _d(p["scales"]), _d(p["zeros"]), _d(p["bias"]), 0.75, algo, 128,
+        weights_static=True)
+    _assert_close(out, p, alpha=0.75)
+
+
+def test_torch_op_leading_dims_and_weight_viewed_as_activation_type():
+    """[B, S, K] activations; the weight viewed as fp16 as the groupwise plugin receives it."""
+    p = make_problem(6, 512, 256, 4, 64, torch.float16, zero=True, seed=2)
+    act = _d(p["act"]).reshape(2, 3, 256)
+    w = _d(p["processed"]).view(torch.float16)
+    out = torch.ops.trtllm.weight_only_groupwise_quant_gemm(act, None, w, _d(p["scales"]), _d(p["zeros"]), None, 1.0,
+                                                            pkg.ZERO, 64)
+    assert out.shape == (2, 3, 512)
+    _assert_close(out.reshape(6, 512), p)
+
+
+def test_torch_op_errors():
+    p = make_problem(2, 256, 256, 4, 128, torch.float16, zero=True, seed=1)
+    a, w, s, z = _d(p["act"]), _d(p["processed"]), _d(p["scales"]), _d(p["zeros"])
+    with pytest.raises(RuntimeError, match="zeros must be given exactly"):
+        torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, None, None, 1.0, pkg.ZERO, 128)
+    with pytest.raises(RuntimeError, match="FP8_ALPHA"):
+        torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, z, None, 1.0, pkg.ZERO | pkg.FP8_ALPHA, 128)
+    with pytest.raises(RuntimeError, match="group_size"):
+        torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, z, None, 1.0, pkg.ZERO, 32)
+    with pytest.raises(RuntimeError, match="wTypeId"):
+        torch.ops.trtllm.weight_only_quant_gemm(a, w, s[0].contiguous(), 3)
+    with pytest.raises(RuntimeError):  # no CPU implementation of the GEMM: a dispatch error, not a fallback
+        torch.ops.trtllm.weight_only_quant_gemm(p["act"], p["processed"], p["scales"][0].contiguous(), 2)
+    empty = torch.ops.trtllm.weight_only_groupwise_quant_gemm(a[:0], None, w, s, z, None, 1.0, pkg.ZERO, 128)
+    assert empty.shape == (0, 256)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 9, 200])
+@pytest.mark.parametrize("bias,zero,prequant,int8", list(itertools.product([False, True], repeat=4)))
+def test_groupwise_plugin_mirror_enqueue(dtype, m, bias, zero, prequant, int8):
+    """Inputs in the plugin's order [act, (pre_quant_scale), weight, scales, (zeros), (bias)],
+    caller-owned output and workspace, status code instead of an exception."""
+    n, k = 512, 1024
+    p = make_problem(m, n, k, 8 if int8 else 4, 128, dtype, zero=zero, bias=bias, prequant=prequant, seed=11 + m)
+    algo = (pkg.BIAS if bias else 0) | (pkg.ZERO if zero else 0) | (pkg.PRE_QUANT_SCALE if prequant else 0) \
+        | (pkg.INT8_WEIGHT if int8 else 0)
+    plugin = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(ops.TRT_HALF if dtype == torch.float16 else ops.TRT_BF16, algo, 128)
+    plugin.configure_plugin(1, 256, n, k)
+    inputs = [_d(p["act"])] + ([_d(p["ps"])] if prequant else []) + [_d(p["processed"]).view(dtype), _d(p["scales"])] \
+        + ([_d(p["zeros"])] if zero else []) + ([_d(p["bias"])] if bias else [])
+    assert len(inputs) == plugin.nb_inputs
+    out = torch.empty((m, n), dtype=dtype, device="cuda")
+    nws = plugin.get_workspace_size()
+    ws = torch.empty(max(nws, 1), dtype=torch.uint8, device="cuda")
+    assert plugin.enqueue(inputs, [out], ws if nws else None) == 0
+    _assert_close(out, p)
+    # a missing input is a status code, not an exception
+    assert plugin.enqueue(inputs[:-1], [out], ws if nws else None) != 0
+    # serialise -> deserialise keeps the behaviour
+    twin = pkg.WeightOnlyGroupwiseQuantMatmulPlugin.deserialize(plugin.serialize())
+    out2 = torch.empty_like(out)
+    assert twin.enqueue(inputs, [out2], ws if nws else None) == 0
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("wtype,m", [(1, 1), (1, 4), (1, 33), (2, 2), (2, 16), (2, 130)])
+def test_per_channel_plugin_mirror_enqueue(dtype, wtype, m):
+    n, k = 1024, 512
+    p = make_problem(m, n, k, 8 if wtype == 1 else 4, 0, dtype, seed=7, scale_lo=0.0005, scale_hi=0.002)
+    plugin = pkg.WeightOnlyQuantMatmulPlugin(ops.TRT_HALF if dtype == torch.float16 else ops.TRT_BF16, wtype)
+    plugin.configure_plugin(1, 256, n, k)
+    out = torch.empty((m, n), dtype=dtype, device="cuda")
+    nws = plugin.get_workspace_size()
+    ws = torch.empty(max(nws, 1), dtype=torch.uint8, device="cuda")
+    assert plugin.enqueue([_d(p["act"]), _d(p["processed"]), _d(p["scales"])], [out], ws if nws else None) == 0
+    _assert_close(out, p)
+    assert plugin.enqueue([_d(p["act"])[:0], _d(p["processed"]), _d(p["scales"])], [out[:0]], None) == 0  # m == 0

@@ -84,3 +84,52 @@ def test_error_codes():
     assert lib.w4_preprocess_weights_device(b.data_ptr(), a.data_ptr(), 64, 64, 5, None) == pkg._lib.W4_ERR_BAD_DTYPE
     assert lib.w4_preprocess_weights_device(b.data_ptr(), a.data_ptr(), 48, 64, 4, None) == pkg._lib.W4_ERR_BAD_SHAPE
     assert lib.w4_preprocess_weights_device(a.data_ptr(), a.data_ptr(), 64, 64, 4, None) == pkg._lib.W4_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("bits,m", [(4, 1), (8, 4)])
+def test_gemm_right_behind_weight_preparation_on_one_stream(bits, m):
+    """The decode kernel is a programmatic dependent launch that may fetch weights before the
+    kernel in front of it has finished - but only when the caller declares them static. Here the
+    kernel in front WRITES the weights: quantise (fresh values each round, same buffers) -> GEMM,
+    200 times back to back on one stream without the static flag. Every output must equal the one
+    the same weights give when the GEMM runs alone."""
+    lib = pkg._lib.lib()
+    import ctypes
+    torch.manual_seed(5)
+    k, n = 2048, 2048
+    dev = "cuda"
+    variants = [(torch.randn(k, n, device=dev) * (0.01 * (i + 1))).to(torch.bfloat16) for i in range(4)]
+    act = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    processed = torch.empty((k, n * bits // 8), dtype=torch.int8, device=dev)
+    s32 = torch.empty((n,), dtype=torch.float32, device=dev)
+    scales = torch.empty((n,), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream()
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    def quantise(w):
+        rc = lib.w4_symmetric_quantize_device(processed.data_ptr(), None, s32.data_ptr(), scales.data_ptr(), 1,
+                                              w.data_ptr(), 1, k, n, bits, sp)
+        assert rc == 0
+
+    def gemm(out):
+        pkg.ops.gemm_raw(act, processed, scales, out, n=n, k=k, weight_bits=bits, group_size=0,
+                         regime=pkg.W4_REGIME_GEMV, weights_static=False)
+
+    alone = []
+    for w in variants:
+        quantise(w)
+        torch.cuda.synchronize()
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        gemm(out)
+        torch.cuda.synchronize()
+        alone.append(out)
+    assert not torch.equal(alone[0], alone[1])
+    rounds = 200
+    outs = torch.empty((rounds, m, n), dtype=torch.bfloat16, device=dev)
+    for i in range(rounds):
+        quantise(variants[i % 4])
+        gemm(outs[i])
+    torch.cuda.synchronize()
+    for i in range(rounds):
+        assert torch.equal(outs[i], alone[i % 4]), f"round {i}: the GEMM saw weights of another round"
+    assert lib.w4_gemm_device_status() == 0
