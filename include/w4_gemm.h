@@ -34,10 +34,10 @@
  *                            - the same two functions as CUDA kernels on device buffers (the
  *                              reference runs them on one CPU thread only,
  *                              cutlass_preprocessors.cpp:685-758); byte-identical results.
- *   w4_allreduce_oneshot     - the ncclAllReduce that follows the plugin in a row-parallel layer
- *                              (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407), for
- *                              latency-bound message sizes, as a peer-memory kernel in the manner of
- *                              oneShotAllReduceKernel (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307).
+ *   w4_allreduce             - the ncclAllReduce that follows the plugin in a row-parallel layer
+ *                              (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407), as a
+ *                              peer-memory kernel in the manner of the reference's one-shot / two-shot
+ *                              kernels (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307,1426).
  *   w4_pack_int4 / w4_unpack_int4
  *                            - pack_int8_tensor_to_packed_int4 / unpack_int4_packed_tensor_to_int8
  *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:284-353).
@@ -182,9 +182,10 @@ extern "C"
      * Same contract as w4_gemm_launch, for callers that can neither allocate device memory nor
      * pass a workspace (allocation-free regions of a serving loop, plugin hosts that granted no
      * workspace, processes in which another component owns the allocator). It always runs the
-     * tensor-core kernel and keeps that kernel's only scratch - the activations multiplied by the
-     * AWQ pre-quant scale, m * k * 2 bytes - in a W4_STATIC_SCRATCH_BYTES (8 MiB) array that is
-     * part of the library image. This entry point has no counterpart in the reference.
+     * tensor-core kernel and keeps that kernel's scratch - the activations multiplied by the AWQ
+     * pre-quant scale, m * k * 2 bytes, and, for shapes with few output tiles when the rest of the
+     * array has room, the fp32 partial tiles of its split-k behind them - in a
+     * W4_STATIC_SCRATCH_BYTES (8 MiB) array that is part of the library image. This entry point has no counterpart in the reference.
      *   - p->workspace / p->workspace_bytes are ignored; nothing is allocated or freed, here or
      *     in any library it calls.
      *   - m * k * 2 > W4_STATIC_SCRATCH_BYTES with act_scale set returns W4_ERR_STATIC_SCRATCH
@@ -231,39 +232,64 @@ extern "C"
     /* ---- row-parallel reduce over peer memory (one process per GPU, one node) ---- */
 
 #define W4_MAX_RANKS 8
-#define W4_ONESHOT_MAX_BYTES (1u << 20) /* larger messages are bandwidth-bound: use the library collective */
+#define W4_ONESHOT_MAX_BYTES (1u << 20) /* largest message the one-shot form takes */
+#define W4_ALLREDUCE_MAX_CTAS 128       /* chunks a message (one-shot) or a slice (two-shot) is cut into */
+
+    enum
+    {
+        W4_ALLREDUCE_AUTO = 0,     /* by message size, the reference's rule (allreducePlugin.cpp:258-283) */
+        W4_ALLREDUCE_ONE_SHOT = 1, /* push the whole partial to every peer, reduce locally */
+        W4_ALLREDUCE_TWO_SHOT = 2  /* push slices to their owners, reduce, pull the reduced slices */
+    };
 
     /*
-     * out[i] = sum over ranks r = 0..world-1 (in that order, fp32) of partials[r][i]  (+ bias[i % n])
+     * out[i] = sum over ranks r = 0..world-1 (in that order, fp32) of partial_r[i]  (+ bias[i % n])
+     * on every rank, bit-identical across ranks.
      *
-     *   partials[r]  rank r's [count] partial sums (fp16 / bf16) as mapped into THIS process: the
-     *                local buffer for r == rank, a peer mapping (CUDA IPC / symmetric memory) else.
-     *                The local GEMM writes partials[rank] directly (pass it as W4GemmParams.out).
-     *   flags[r]     rank r's W4_MAX_RANKS 32-bit flag words, mapped the same way; zero before the
-     *                first call (and all ranks must have seen the zeroing before anyone calls).
-     *   epoch        call number: 1 for the first call, +1 for every call, the same on every rank.
-     *                Alternate between two partial buffers from call to call.
-     *   timeout_ms   bound on the wait for the peers (0 = 2000). When it expires the kernel leaves
-     *                `out` untouched and w4_gemm_device_status() returns W4_ERR_DEVICE_TIMEOUT.
-     * count % 8 == 0, n % 8 == 0, count % n == 0, count * 2 <= W4_ONESHOT_MAX_BYTES, all data
-     * pointers 16-byte aligned. Stream-ordered after the GEMM that produced partials[rank];
-     * allocates nothing.
+     *   partial      THIS rank's [count] partial sums (fp16 / bf16): plain local device memory, typically
+     *                the W4GemmParams.out of the row-parallel GEMM enqueued just before on the same stream.
+     *   workspace[r] rank r's workspace block as mapped into THIS process: the local block for
+     *                r == rank, a peer mapping (CUDA IPC / symmetric memory) otherwise. Every block is
+     *                w4_allreduce_workspace_bytes(max_message_bytes, world) bytes, 256-byte aligned and
+     *                ZERO before the first call (all ranks must have seen the zeroing before anyone calls).
+     *                workspace_bytes is that size.
+     *   mode         W4_ALLREDUCE_*; must be the same on every rank for a given call.
+     *   timeout_ms   bound on every wait for the peers (0 = 2000). When it expires the kernel gives up,
+     *                `out` is undefined, w4_gemm_device_status() returns W4_ERR_DEVICE_TIMEOUT and the
+     *                workspace must be zeroed again on all ranks before further use.
+     * count % 8 == 0, n % 8 == 0, count % n == 0; partial, out, bias 16-byte aligned; count * 2 bytes must
+     * not exceed the max_message_bytes the workspace was sized for (one-shot: W4_ONESHOT_MAX_BYTES).
+     * All ranks make the same sequence of calls. The call number is kept in the workspace on the device,
+     * so a captured CUDA graph containing these calls can be replayed any number of times. Calls that
+     * share a workspace must not overlap on the GPU (one stream). Allocates nothing.
+     * Stands in for the ncclAllReduce behind the plugin in a row-parallel layer
+     * (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407), in the manner of the reference's
+     * custom all-reduce kernels (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307,1426).
      */
     typedef struct W4AllReduceParams
     {
-        const void* partials[W4_MAX_RANKS];
-        uint32_t* flags[W4_MAX_RANKS];
+        const void* partial;
+        void* workspace[W4_MAX_RANKS];
+        size_t workspace_bytes;
         const void* bias; /* optional, [n] */
         void* out;        /* local, [count] */
         size_t count;
         int n;
         int rank, world;
         int act_dtype; /* W4_DTYPE_FP16 / W4_DTYPE_BF16 */
-        uint32_t epoch;
+        int mode;      /* W4_ALLREDUCE_* */
         uint32_t timeout_ms;
     } W4AllReduceParams;
 
-    int w4_allreduce_oneshot(const W4AllReduceParams* p, void* stream);
+    /* Bytes of one rank's workspace block for messages of up to max_message_bytes. 0 for bad arguments. */
+    size_t w4_allreduce_workspace_bytes(size_t max_message_bytes, int world);
+
+    int w4_allreduce(const W4AllReduceParams* p, void* stream);
+
+    /* The calls of all `world` ranks as ONE cooperative launch on the current GPU: ranks[r] describes
+     * rank r, every workspace pointer is local memory. For machines with fewer GPUs than ranks (tests,
+     * debugging): separate launches that wait for one another must never share a GPU. */
+    int w4_allreduce_emulated(const W4AllReduceParams* ranks, int world, void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,7 +23,8 @@ EXPORTS = (
     "w4_gemm_version", "w4_status_string", "w4_gemm_validate", "w4_gemm_launch", "w4_gemm_workspace_bytes",
     "w4_gemm_select_regime", "w4_gemm_device_status", "w4_symmetric_quantize", "w4_preprocess_weights",
     "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
-    "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce_oneshot",
+    "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce", "w4_allreduce_emulated",
+    "w4_allreduce_workspace_bytes",
     "w4_gemm_workspace_bytes_max",
 )
 
@@ -44,15 +45,17 @@ W4_GEMM_WEIGHTS_STATIC = 1
 
 W4_MAX_RANKS = 8
 W4_ONESHOT_MAX_BYTES = 1 << 20
+W4_ALLREDUCE_MAX_CTAS = 128
 W4_ERR_DEVICE_TIMEOUT = -10
+W4_ALLREDUCE_AUTO, W4_ALLREDUCE_ONE_SHOT, W4_ALLREDUCE_TWO_SHOT = 0, 1, 2
 
 
 class W4AllReduceParams(ctypes.Structure):
     _fields_ = [
-        ("partials", ctypes.c_void_p * W4_MAX_RANKS), ("flags", ctypes.c_void_p * W4_MAX_RANKS),
-        ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p), ("count", ctypes.c_size_t), ("n", ctypes.c_int),
-        ("rank", ctypes.c_int), ("world", ctypes.c_int), ("act_dtype", ctypes.c_int), ("epoch", ctypes.c_uint32),
-        ("timeout_ms", ctypes.c_uint32),
+        ("partial", ctypes.c_void_p), ("workspace", ctypes.c_void_p * W4_MAX_RANKS),
+        ("workspace_bytes", ctypes.c_size_t), ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("count", ctypes.c_size_t), ("n", ctypes.c_int), ("rank", ctypes.c_int), ("world", ctypes.c_int),
+        ("act_dtype", ctypes.c_int), ("mode", ctypes.c_int), ("timeout_ms", ctypes.c_uint32),
     ]
 
 
@@ -93,7 +96,10 @@ def lib() -> ctypes.CDLL:
         l.w4_symmetric_quantize_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                    ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                                    ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
-        l.w4_allreduce_oneshot.argtypes = [ctypes.POINTER(W4AllReduceParams), ctypes.c_void_p]
+        l.w4_allreduce.argtypes = [ctypes.POINTER(W4AllReduceParams), ctypes.c_void_p]
+        l.w4_allreduce_emulated.argtypes = [ctypes.POINTER(W4AllReduceParams), ctypes.c_int, ctypes.c_void_p]
+        l.w4_allreduce_workspace_bytes.restype = ctypes.c_size_t
+        l.w4_allreduce_workspace_bytes.argtypes = [ctypes.c_size_t, ctypes.c_int]
         l.w4_pack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.restype = None

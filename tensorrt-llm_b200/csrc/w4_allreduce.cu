@@ -1,25 +1,36 @@
-// One-shot all-reduce over peer memory for the row-parallel weight-only GEMM: every rank's GEMM
-// writes its [m, n] partial sums into a buffer that the other GPUs of the node have mapped
-// (NVLink 5 through NVSwitch); this kernel, next on the same stream, tells the peers that the
-// partial is complete, waits for theirs, and then every CTA pulls its slice of all partials with
-// ordinary 16-byte loads, adds them in rank order in fp32 (the same order on every rank, so all
-// ranks hold bit-identical results), adds the layer bias and stores the local output.
+// All-reduce over peer memory for the row-parallel weight-only GEMM (one process per GPU, one node,
+// NVLink 5 through NVSwitch). It takes the place of the ncclAllReduce that follows the plugin in the
+// reference (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407) and follows the idea of the
+// reference's own custom all-reduce for dense layers (one-shot and two-shot kernels,
+// cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307,1426; selection by message size,
+// allreducePlugin.cpp:258-283), which the reference never applies to this path. Plain peer loads
+// and stores only: no multicast objects, no cluster multicast.
 //
-// It takes the place of the ncclAllReduce that follows the plugin in the reference
-// (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407) for messages small enough that the
-// collective is latency-bound; it follows the idea of the reference's own one-shot kernel for dense
-// layers (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307), which the reference never
-// applies to this path. No multicast objects and no cluster multicast: plain peer loads and stores.
+// Every rank owns a workspace block that all ranks have mapped: a control area, two sets of arrival
+// flags, an inbox and (two-shot) a buffer of reduced values, each in two copies used by alternate
+// calls. One kernel per call and rank:
 //
-// Synchronisation. Each rank owns kMaxRanks flag words; rank s announces call number `epoch` by
-// storing it (release, system scope) into word s of every peer's flags.
-// A CTA starts reducing once all words of its own rank's flags have reached `epoch`. Call numbers
-// only grow, so flags are never reset. Callers alternate between two partial buffers: a rank can
-// only reach call e + 2 after every peer has announced call e + 1, which a peer does after its call
-// e (and with it all its reads of the buffers of call e) has finished.
-// The wait is bounded in time; when it expires the kernel records W4_ERR_DEVICE_TIMEOUT in the
-// device status word and returns without touching the output (a peer that never arrives must not
-// hang this GPU).
+//   one-shot (latency-bound sizes): CTA c PUSHES chunk c of the local partial sums into the inbox of
+//     every peer (one NVLink traversal), then raises flag (sender, c) there; it waits for the same
+//     chunk from every peer in its own inbox (local polling, local loads) and adds the chunks in rank
+//     order in fp32, so all ranks hold bit-identical results.
+//   two-shot (bandwidth-bound sizes): the message is cut into one slice per rank. Phase 1: every rank
+//     pushes slice j of its partial sums to rank j. Phase 2: rank j adds the world copies of its slice
+//     (rank order, fp32, + bias), writes the rounded result to its `reduced` buffer and to its own
+//     output, and raises flag2 at every peer. Phase 3: every rank pulls the other slices from their
+//     owners. Each rank sends and receives about 2 * bytes instead of (world - 1) * bytes.
+//
+// Call numbers live in DEVICE memory (control word 0), not in a launch argument: every CTA reads the
+// number at start, the last CTA to finish advances it. A captured CUDA graph can therefore be replayed
+// any number of times, and the inbox / flag copy a call uses follows from the number's parity. Why two
+// copies are enough: a rank can only start call e + 2 after every peer has taken part in call e + 1,
+// which a peer does after its call e (and all its reads of copy e & 1) has finished.
+//
+// Nobody waits before having pushed everything it owes, and a CTA only ever waits for peers, never for
+// another CTA of its own launch; grids are at most kMaxCtas <= SM count, so all CTAs are resident.
+// Waits are bounded in time: when one expires the kernel records W4_ERR_DEVICE_TIMEOUT in the device
+// status word, skips the rest and returns (a peer that never arrives must not hang this GPU); `out` is
+// then undefined and the workspace must be cleared on all ranks before it is used again.
 #include "w4_common.cuh"
 #include "w4_internal.h"
 
@@ -29,18 +40,58 @@ namespace ar
 {
 
 constexpr int kMaxRanks = W4_MAX_RANKS;
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
+constexpr int kMaxCtas = W4_ALLREDUCE_MAX_CTAS; // chunks per message (one-shot) or per slice (two-shot)
+constexpr size_t kCtrlBytes = 256;
+constexpr size_t kFlagBytes = size_t(2) * kMaxRanks * kMaxCtas * sizeof(uint32_t);
+constexpr size_t kHeaderBytes = kCtrlBytes + 2 * kFlagBytes; // control, flags, flags2
 
-struct Args
+struct Layout
 {
-    void const* partials[kMaxRanks];
-    uint32_t* flags[kMaxRanks];
+    size_t inbox_bytes;   // one copy of the inbox: world sender slots
+    size_t slot_bytes;    // one sender's slot inside the inbox
+    size_t reduced_bytes; // one copy of the reduced-slice buffer
+    size_t total;
+};
+
+__host__ __device__ inline size_t align256(size_t v)
+{
+    return (v + 255) & ~size_t(255);
+}
+
+// Workspace for messages up to max_bytes: a sender slot holds a whole one-shot message (up to
+// W4_ONESHOT_MAX_BYTES) or one slice of a two-shot message, whichever is larger.
+__host__ __device__ inline Layout layout_for(size_t max_bytes, int world)
+{
+    Layout l;
+    size_t const one = max_bytes < size_t(W4_ONESHOT_MAX_BYTES) ? max_bytes : size_t(W4_ONESHOT_MAX_BYTES);
+    size_t const slice = (max_bytes + world - 1) / world + 16;
+    l.slot_bytes = align256(one > slice ? one : slice);
+    l.inbox_bytes = l.slot_bytes * world;
+    l.reduced_bytes = align256(slice);
+    l.total = kHeaderBytes + 2 * l.inbox_bytes + 2 * l.reduced_bytes;
+    return l;
+}
+
+struct RankArgs
+{
+    void const* partial;
+    uint8_t* ws[kMaxRanks]; // ws[r]: rank r's workspace block as mapped into this process
     void const* bias;
     void* out;
     size_t count;
     int n;
-    int rank, world;
-    uint32_t epoch;
+    int rank;
+};
+
+struct Batch
+{
+    RankArgs r[kMaxRanks]; // one entry per rank served by this launch (1 in production)
+    int ranks_in_launch;
+    int ctas_per_rank;
+    int world;
+    int two_shot;
+    size_t slot_bytes, inbox_bytes, reduced_bytes;
     unsigned long long timeout_ns;
 };
 
@@ -63,8 +114,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(uint32_t const* p)
     return v;
 }
 
-// Peer data is read around L1: the same addresses are rewritten by another GPU every second call.
-__device__ __forceinline__ uint4 ld_peer(void const* p)
+// Data that another GPU writes (inbox) or owns (reduced) is accessed around L1.
+__device__ __forceinline__ uint4 ld_sys(void const* p)
 {
     uint4 v;
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -74,139 +125,380 @@ __device__ __forceinline__ uint4 ld_peer(void const* p)
     return v;
 }
 
+__device__ __forceinline__ void st_sys(void* p, uint4 v)
+{
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads) oneshot_kernel(Args const a)
+__device__ __forceinline__ void add8(float (&acc)[8], uint4 v)
+{
+    uint32_t const w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        float lo, hi;
+        Pair<T>::unpack2(w[j], lo, hi);
+        acc[2 * j] += lo;
+        acc[2 * j + 1] += hi;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack8(float const (&acc)[8])
 {
     using P = Pair<T>;
-    __shared__ int failed;
-    if (threadIdx.x == 0)
-        failed = 0;
-    __syncthreads();
+    uint4 o;
+    o.x = uint32_t(P::from_float(acc[0])) | (uint32_t(P::from_float(acc[1])) << 16);
+    o.y = uint32_t(P::from_float(acc[2])) | (uint32_t(P::from_float(acc[3])) << 16);
+    o.z = uint32_t(P::from_float(acc[4])) | (uint32_t(P::from_float(acc[5])) << 16);
+    o.w = uint32_t(P::from_float(acc[6])) | (uint32_t(P::from_float(acc[7])) << 16);
+    return o;
+}
 
-    // 1. announce: this rank's partial was written by the kernel before this one on the stream, so
-    // it is already visible; the release store keeps the flag behind it for the peers
-    if (blockIdx.x == 0 && threadIdx.x < a.world)
-        st_release_sys(a.flags[threadIdx.x] + a.rank, a.epoch);
-    // 2. wait for every rank (own word included: it is written by the CTA above)
-    if (threadIdx.x < a.world)
+// Waits (threads 0..world-1, one flag word each) until every peer's flag for this chunk has reached
+// `epoch`; returns false for the whole CTA when the time limit expired.
+__device__ __forceinline__ bool wait_peers(uint32_t const* flags, int world, int rank, int chunk, uint32_t epoch,
+    unsigned long long timeout_ns, int* failed)
+{
+    if (int(threadIdx.x) < world && int(threadIdx.x) != rank)
     {
-        uint32_t const* word = a.flags[a.rank] + threadIdx.x;
+        uint32_t const* word = flags + size_t(threadIdx.x) * kMaxCtas + chunk;
         unsigned long long const t0 = global_timer_ns();
         uint32_t polls = 0;
-        while (int32_t(ld_acquire_sys(word) - a.epoch) < 0)
+        while (int32_t(ld_acquire_sys(word) - epoch) < 0)
         {
-            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > a.timeout_ns)
+            if ((++polls & 63u) == 0 && global_timer_ns() - t0 > timeout_ns)
             {
-                failed = 1;
+                *failed = 1;
                 atomicExch(&g_device_status, kDeviceTimeout);
                 break;
             }
         }
     }
     __syncthreads();
-    if (failed)
-        return;
+    return *failed == 0;
+}
 
-    // 3. pull and add, eight elements per thread and step
-    size_t const vecs = a.count / 8;
+template <typename T>
+__global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
+{
+    __shared__ int failed;
+    int const which = int(blockIdx.x) / b.ctas_per_rank; // which of the launch's ranks this CTA serves
+    int const c = int(blockIdx.x) - which * b.ctas_per_rank;
+    int const C = b.ctas_per_rank;
+    RankArgs const& a = b.r[which];
+    int const world = b.world, rank = a.rank;
+    uint8_t* const mine = a.ws[rank];
+    uint32_t* const ctrl = reinterpret_cast<uint32_t*>(mine);
+
+    if (threadIdx.x == 0)
+        failed = 0;
+    // Call number: read by every CTA before any CTA of this launch can advance it (see the end).
+    uint32_t const epoch = *reinterpret_cast<volatile uint32_t*>(ctrl) + 1u;
+    int const h = int(epoch & 1u);
+    __syncthreads();
+
+    auto flags_of = [&](uint8_t* ws, int set) // set 0: arrival flags, set 1: "reduced slice published"
+    { return reinterpret_cast<uint32_t*>(ws + kCtrlBytes + size_t(set) * kFlagBytes) + size_t(h) * kMaxRanks * kMaxCtas; };
+    auto inbox_of = [&](uint8_t* ws, int sender)
+    { return ws + kHeaderBytes + size_t(h) * b.inbox_bytes + size_t(sender) * b.slot_bytes; };
+    auto reduced_of = [&](uint8_t* ws) { return ws + kHeaderBytes + 2 * b.inbox_bytes + size_t(h) * b.reduced_bytes; };
+
+    size_t const V = a.count / 8; // 16-byte vectors in the message
     int const n_vec = a.n / 8;
-    for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < vecs; i += size_t(gridDim.x) * kThreads)
+    uint4 const* partial = static_cast<uint4 const*>(a.partial);
+    uint4* out = static_cast<uint4*>(a.out);
+    bool ok = true;
+
+    if (!b.two_shot)
     {
-        // All peers' vectors are requested before the first is used: one NVLink round trip, not
-        // `world` of them back to back.
-        uint4 v[kMaxRanks];
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < a.world)
-                v[r] = ld_peer(static_cast<uint4 const*>(a.partials[r]) + i);
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
+        // ---- push chunk c to every peer's inbox, slot `rank`
+        size_t const v0 = V * size_t(c) / C, v1 = V * size_t(c + 1) / C;
+        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
         {
-            if (r < a.world)
-            {
-                uint32_t const w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+            uint4 const v = partial[i];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                {
-                    float lo, hi;
-                    P::unpack2(w[j], lo, hi);
-                    acc[2 * j] += lo;
-                    acc[2 * j + 1] += hi;
-                }
+            for (int p = 0; p < kMaxRanks; ++p)
+                if (p < world && p != rank)
+                    st_sys(reinterpret_cast<uint4*>(inbox_of(a.ws[p], rank)) + i, v);
+        }
+        __syncthreads();
+        if (int(threadIdx.x) < world && int(threadIdx.x) != rank)
+        {
+            __threadfence_system();
+            st_release_sys(flags_of(a.ws[threadIdx.x], 0) + size_t(rank) * kMaxCtas + c, epoch);
+        }
+        // ---- wait for the peers' chunk c, add in rank order
+        ok = wait_peers(flags_of(mine, 0), world, rank, c, epoch, b.timeout_ns, &failed);
+        if (ok)
+        {
+            for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+            {
+                uint4 v[kMaxRanks];
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world)
+                        v[r] = r == rank ? partial[i] : ld_sys(reinterpret_cast<uint4 const*>(inbox_of(mine, r)) + i);
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world)
+                        add8<T>(acc, v[r]);
+                if (a.bias)
+                    add8<T>(acc, __ldg(static_cast<uint4 const*>(a.bias) + (i % n_vec)));
+                out[i] = pack8<T>(acc);
             }
         }
-        if (a.bias)
-        {
-            uint4 const b = __ldg(static_cast<uint4 const*>(a.bias) + (i % n_vec));
-            uint32_t const w[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-            {
-                float lo, hi;
-                P::unpack2(w[j], lo, hi);
-                acc[2 * j] += lo;
-                acc[2 * j + 1] += hi;
-            }
-        }
-        uint4 o;
-        o.x = uint32_t(P::from_float(acc[0])) | (uint32_t(P::from_float(acc[1])) << 16);
-        o.y = uint32_t(P::from_float(acc[2])) | (uint32_t(P::from_float(acc[3])) << 16);
-        o.z = uint32_t(P::from_float(acc[4])) | (uint32_t(P::from_float(acc[5])) << 16);
-        o.w = uint32_t(P::from_float(acc[6])) | (uint32_t(P::from_float(acc[7])) << 16);
-        static_cast<uint4*>(a.out)[i] = o;
     }
+    else
+    {
+        // slice j = vectors [V j / world, V (j+1) / world); chunk c of a slice likewise
+        auto slice_begin = [&](int j) { return V * size_t(j) / world; };
+        // ---- phase 1: push chunk c of slice j to its owner j, slot `rank`, at the slice-relative offset
+        for (int dj = 1; dj < world; ++dj)
+        {
+            int const j = (rank + dj) % world; // start with the next rank: spreads the traffic
+            size_t const s0 = slice_begin(j), len = slice_begin(j + 1) - s0;
+            size_t const v0 = len * size_t(c) / C, v1 = len * size_t(c + 1) / C;
+            uint4* dst = reinterpret_cast<uint4*>(inbox_of(a.ws[j], rank));
+            for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+                st_sys(dst + i, partial[s0 + i]);
+        }
+        __syncthreads();
+        if (int(threadIdx.x) < world && int(threadIdx.x) != rank)
+        {
+            __threadfence_system();
+            st_release_sys(flags_of(a.ws[threadIdx.x], 0) + size_t(rank) * kMaxCtas + c, epoch);
+        }
+        // ---- phase 2: reduce chunk c of the own slice, publish it
+        size_t const s0 = slice_begin(rank), len = slice_begin(rank + 1) - s0;
+        size_t const v0 = len * size_t(c) / C, v1 = len * size_t(c + 1) / C;
+        ok = wait_peers(flags_of(mine, 0), world, rank, c, epoch, b.timeout_ns, &failed);
+        if (ok)
+        {
+            uint4* red = reinterpret_cast<uint4*>(reduced_of(mine));
+            for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+            {
+                uint4 v[kMaxRanks];
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world)
+                        v[r] = r == rank ? partial[s0 + i] : ld_sys(reinterpret_cast<uint4 const*>(inbox_of(mine, r)) + i);
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world)
+                        add8<T>(acc, v[r]);
+                if (a.bias)
+                    add8<T>(acc, __ldg(static_cast<uint4 const*>(a.bias) + ((s0 + i) % n_vec)));
+                uint4 const o = pack8<T>(acc);
+                st_sys(red + i, o);
+                out[s0 + i] = o;
+            }
+        }
+        __syncthreads();
+        if (ok && int(threadIdx.x) < world && int(threadIdx.x) != rank)
+        {
+            __threadfence_system();
+            st_release_sys(flags_of(a.ws[threadIdx.x], 1) + size_t(rank) * kMaxCtas + c, epoch);
+        }
+        // ---- phase 3: pull chunk c of every other slice from its owner
+        if (ok)
+            ok = wait_peers(flags_of(mine, 1), world, rank, c, epoch, b.timeout_ns, &failed);
+        if (ok)
+        {
+            for (int dj = 1; dj < world; ++dj)
+            {
+                int const j = (rank + dj) % world;
+                size_t const t0 = slice_begin(j), tl = slice_begin(j + 1) - t0;
+                size_t const w0 = tl * size_t(c) / C, w1 = tl * size_t(c + 1) / C;
+                uint4 const* src = reinterpret_cast<uint4 const*>(reduced_of(a.ws[j]));
+                for (size_t i = w0 + threadIdx.x; i < w1; i += kThreads)
+                    out[t0 + i] = ld_sys(src + i);
+            }
+        }
+    }
+
+    // ---- the last CTA of this rank's launch advances the call number
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        uint32_t const ticket = atomicAdd(ctrl + 1, 1u);
+        if (ticket == uint32_t(C) - 1u)
+        {
+            ctrl[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(ctrl) = epoch;
+        }
+    }
+}
+
+static int check_one(W4AllReduceParams const& p)
+{
+    if (!p.out || !p.partial)
+        return W4_ERR_NULL_POINTER;
+    if (p.world < 1 || p.world > kMaxRanks || p.rank < 0 || p.rank >= p.world)
+        return W4_ERR_BAD_SHAPE;
+    if (p.act_dtype != W4_DTYPE_FP16 && p.act_dtype != W4_DTYPE_BF16)
+        return W4_ERR_BAD_DTYPE;
+    if (p.mode != W4_ALLREDUCE_AUTO && p.mode != W4_ALLREDUCE_ONE_SHOT && p.mode != W4_ALLREDUCE_TWO_SHOT)
+        return W4_ERR_BAD_REGIME;
+    if (p.count % 8 != 0 || p.n <= 0 || p.n % 8 != 0 || p.count % size_t(p.n) != 0)
+        return W4_ERR_BAD_SHAPE;
+    for (int r = 0; r < p.world; ++r)
+    {
+        if (!p.workspace[r])
+            return W4_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(p.workspace[r]) & 255u)
+            return W4_ERR_MISALIGNED;
+    }
+    if ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.partial))
+        & 15u)
+        return W4_ERR_MISALIGNED;
+    return W4_OK;
+}
+
+// 1 = two-shot. AUTO follows the reference's size rule for its one-shot kernel
+// (allreducePlugin.cpp:258-283): always up to 2 ranks, below 1 MB up to 4, below 500 kB beyond.
+static int pick_two_shot(int mode, size_t bytes, int world)
+{
+    if (world == 1 || mode == W4_ALLREDUCE_ONE_SHOT)
+        return 0;
+    if (mode == W4_ALLREDUCE_TWO_SHOT)
+        return 1;
+    if (bytes > size_t(W4_ONESHOT_MAX_BYTES))
+        return 1;
+    if (world <= 2)
+        return 0;
+    return bytes < (world <= 4 ? size_t(1000000) : size_t(500000)) ? 0 : 1;
+}
+
+static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStream_t stream)
+{
+    W4AllReduceParams const& p0 = ranks[0];
+    size_t const bytes = p0.count * 2;
+    Batch b{};
+    b.world = p0.world;
+    b.ranks_in_launch = ranks_in_launch;
+    b.two_shot = pick_two_shot(p0.mode, bytes, p0.world);
+    if (!b.two_shot && bytes > size_t(W4_ONESHOT_MAX_BYTES))
+        return W4_ERR_UNSUPPORTED; // a one-shot message must fit one sender slot
+    // The workspace was sized for some largest message: recover the layout from its size.
+    size_t const body = p0.workspace_bytes > kHeaderBytes ? p0.workspace_bytes - kHeaderBytes : 0;
+    // total - header = 2 * world * slot + 2 * reduced; the caller passes what
+    // w4_allreduce_workspace_bytes(max_bytes, world) returned, so invert by search over max_bytes' two regimes
+    Layout l{};
+    {
+        // capacity is monotone in max_bytes: find the largest max_bytes whose layout fits (binary search)
+        size_t lo = 0, hi = size_t(1) << 34;
+        while (lo < hi)
+        {
+            size_t const mid = lo + (hi - lo + 1) / 2;
+            if (layout_for(mid, p0.world).total <= p0.workspace_bytes)
+                lo = mid;
+            else
+                hi = mid - 1;
+        }
+        if (lo < bytes || body == 0)
+            return W4_ERR_WORKSPACE;
+        l = layout_for(lo, p0.world);
+    }
+    b.slot_bytes = l.slot_bytes;
+    b.inbox_bytes = l.inbox_bytes;
+    b.reduced_bytes = l.reduced_bytes;
+    b.timeout_ns = p0.timeout_ms > 0 ? (unsigned long long) (p0.timeout_ms) * 1000000ull : 2000000000ull;
+
+    w4::DeviceInfo const& dev = w4::current_device_info();
+    if (dev.num_sms <= 0)
+        return W4_ERR_CUDA;
+    // Chunks: at least 512 vectors (8 KB) each, at most kMaxCtas; all ranks derive the same number
+    // from the message size alone. Several ranks in one launch (single-GPU emulation) must all be
+    // resident at once, so the number is capped by the SMs available per rank.
+    size_t const unit = b.two_shot ? (p0.count / 8) / p0.world : p0.count / 8;
+    int ctas = int(unit / 512);
+    ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
+    if (ctas > dev.num_sms / ranks_in_launch)
+        ctas = dev.num_sms / ranks_in_launch;
+    if (ctas < 1)
+        return W4_ERR_UNSUPPORTED;
+    b.ctas_per_rank = ctas;
+    for (int i = 0; i < ranks_in_launch; ++i)
+    {
+        W4AllReduceParams const& p = ranks[i];
+        RankArgs& a = b.r[i];
+        a.partial = p.partial;
+        for (int r = 0; r < p.world; ++r)
+            a.ws[r] = static_cast<uint8_t*>(p.workspace[r]);
+        a.bias = p.bias;
+        a.out = p.out;
+        a.count = p.count;
+        a.n = p.n;
+        a.rank = p.rank;
+    }
+    dim3 const grid(unsigned(ctas * ranks_in_launch)), block(kThreads);
+    void* args[] = {&b};
+    cudaError_t rc;
+    if (ranks_in_launch > 1)
+    {
+        // CTAs of different emulated ranks wait for one another: they must be co-resident.
+        rc = p0.act_dtype == W4_DTYPE_FP16
+            ? cudaLaunchCooperativeKernel(reinterpret_cast<void*>(allreduce_kernel<__half>), grid, block, args, 0, stream)
+            : cudaLaunchCooperativeKernel(reinterpret_cast<void*>(allreduce_kernel<__nv_bfloat16>), grid, block, args, 0,
+                stream);
+    }
+    else
+    {
+        if (p0.act_dtype == W4_DTYPE_FP16)
+            allreduce_kernel<__half><<<grid, block, 0, stream>>>(b);
+        else
+            allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(b);
+        rc = cudaGetLastError();
+    }
+    return rc == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
 } // namespace ar
 } // namespace w4
 
-extern "C" int w4_allreduce_oneshot(const W4AllReduceParams* p, void* stream)
+extern "C" size_t w4_allreduce_workspace_bytes(size_t max_message_bytes, int world)
 {
-    using namespace w4::ar;
-    if (!p || !p->out)
+    if (world < 1 || world > w4::ar::kMaxRanks || max_message_bytes == 0)
+        return 0;
+    return w4::ar::layout_for(max_message_bytes, world).total;
+}
+
+extern "C" int w4_allreduce(const W4AllReduceParams* p, void* stream)
+{
+    if (!p)
         return W4_ERR_NULL_POINTER;
-    if (p->world < 1 || p->world > kMaxRanks || p->rank < 0 || p->rank >= p->world)
-        return W4_ERR_BAD_SHAPE;
-    if (p->act_dtype != W4_DTYPE_FP16 && p->act_dtype != W4_DTYPE_BF16)
-        return W4_ERR_BAD_DTYPE;
+    int const rc = w4::ar::check_one(*p);
+    if (rc != W4_OK)
+        return rc;
     if (p->count == 0)
         return W4_OK;
-    if (p->count % 8 != 0 || p->n <= 0 || p->n % 8 != 0 || p->count % size_t(p->n) != 0)
+    return w4::ar::launch(p, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int w4_allreduce_emulated(const W4AllReduceParams* ranks, int world, void* stream)
+{
+    if (!ranks)
+        return W4_ERR_NULL_POINTER;
+    if (world < 1 || world > w4::ar::kMaxRanks)
         return W4_ERR_BAD_SHAPE;
-    if (p->count * 2 > size_t(W4_ONESHOT_MAX_BYTES))
-        return W4_ERR_UNSUPPORTED; // bandwidth-bound sizes belong to the library collective
-    Args a{};
-    for (int r = 0; r < p->world; ++r)
+    for (int r = 0; r < world; ++r)
     {
-        if (!p->partials[r] || !p->flags[r])
-            return W4_ERR_NULL_POINTER;
-        if (reinterpret_cast<uintptr_t>(p->partials[r]) & 15u)
-            return W4_ERR_MISALIGNED;
-        a.partials[r] = p->partials[r];
-        a.flags[r] = p->flags[r];
+        int const rc = w4::ar::check_one(ranks[r]);
+        if (rc != W4_OK)
+            return rc;
+        if (ranks[r].world != world || ranks[r].rank != r || ranks[r].count != ranks[0].count
+            || ranks[r].act_dtype != ranks[0].act_dtype || ranks[r].mode != ranks[0].mode
+            || ranks[r].workspace_bytes != ranks[0].workspace_bytes)
+            return W4_ERR_BAD_SHAPE;
     }
-    if ((reinterpret_cast<uintptr_t>(p->out) | reinterpret_cast<uintptr_t>(p->bias)) & 15u)
-        return W4_ERR_MISALIGNED;
-    a.bias = p->bias;
-    a.out = p->out;
-    a.count = p->count;
-    a.n = p->n;
-    a.rank = p->rank;
-    a.world = p->world;
-    a.epoch = p->epoch;
-    a.timeout_ns = p->timeout_ms > 0 ? (unsigned long long) (p->timeout_ms) * 1000000ull : 2000000000ull;
-    w4::DeviceInfo const& dev = w4::current_device_info();
-    if (dev.num_sms <= 0)
-        return W4_ERR_CUDA;
-    size_t const vecs = p->count / 8;
-    size_t blocks = (vecs + kThreads - 1) / kThreads;
-    if (blocks > size_t(dev.num_sms))
-        blocks = size_t(dev.num_sms);
-    cudaStream_t const s = static_cast<cudaStream_t>(stream);
-    if (p->act_dtype == W4_DTYPE_FP16)
-        oneshot_kernel<__half><<<unsigned(blocks), kThreads, 0, s>>>(a);
-    else
-        oneshot_kernel<__nv_bfloat16><<<unsigned(blocks), kThreads, 0, s>>>(a);
-    return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
+    if (ranks[0].count == 0)
+        return W4_OK;
+    return w4::ar::launch(ranks, world, static_cast<cudaStream_t>(stream));
 }

@@ -46,7 +46,7 @@ namespace gemv2
 
 constexpr int kWarps = 16; // consumer warps
 constexpr int kConsumerThreads = kWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32; // + the producer warp (one lane of it works)
+constexpr int kThreads = kConsumerThreads + 64; // + the producer warp and the watcher warp (one lane of each works)
 constexpr int kBoxCols = 16;                    // columns per scale/zero box = one column group
 constexpr int kZeroBoxOff = 512;                // bytes from a slot's scale box to its zero box (16 groups x 32 B)
 // Shared memory one CTA may use when two are to share an SM: half of 228 KB less the 1 KB the
@@ -122,28 +122,68 @@ __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile i
     return false;
 }
 
-// One non-blocking-ish probe of a barrier phase (1 = complete). The result comes back after a few
-// hundred cycles, so the consumers probe the NEXT tile's barrier before working on the current one.
-__device__ __forceinline__ uint32_t probe_bar(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
-    if (probe_bar(bar, parity))
-        return true;
     return wait_slow(bar, parity, abort_flag);
+}
+
+// Progress counters in shared memory. An mbarrier instruction holds the issuing warp for several
+// hundred cycles even when the phase is long complete (measured: ~500 cycles for try_wait, ~200 for
+// arrive), which at one tile per ~700 cycles would be most of a consumer warp's time. So only the
+// watcher warp waits on the mbarriers the bulk copies complete; it publishes the number of tiles
+// that have landed in a plain word, the consumer warps publish the tiles they have finished in one
+// word each, and everybody else polls those words with ordinary acquire loads.
+__device__ __forceinline__ void publish(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t observe(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Waits until the counter at `addr` has reached `needed`. Bounded; returns false after a timeout
+// anywhere in the CTA.
+__device__ __noinline__ bool wait_count_slow(uint32_t addr, uint32_t needed, volatile int* abort_flag)
+{
+    for (uint32_t i = 0; i < kMaxSpinPolls; ++i)
+    {
+        if (int32_t(observe(addr) - needed) >= 0)
+            return true;
+        if ((i & 4095u) == 4095u && *abort_flag)
+            return false;
+    }
+    *abort_flag = 1;
+    atomicExch(&g_device_status, kDeviceTimeout);
+    return false;
+}
+
+__device__ __forceinline__ bool wait_count(uint32_t addr, uint32_t needed, volatile int* abort_flag)
+{
+    if (int32_t(observe(addr) - needed) >= 0)
+        return true;
+    return wait_count_slow(addr, needed, abort_flag);
+}
+
+// All sixteen consumer warps have finished at least `needed` tiles (four 16-byte acquire loads).
+__device__ __forceinline__ bool all_done(uint32_t addr, uint32_t needed)
+{
+    bool ok = true;
+#pragma unroll
+    for (int q = 0; q < kWarps / 4; ++q)
+    {
+        uint32_t a, b, c, d;
+        asm volatile("ld.acquire.cta.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                     : "r"(addr + 16 * q)
+                     : "memory");
+        ok = ok && int32_t(a - needed) >= 0 && int32_t(b - needed) >= 0 && int32_t(c - needed) >= 0
+            && int32_t(d - needed) >= 0;
+    }
+    return ok;
 }
 
 // Shared-memory loads through 32-bit addresses with immediate offsets.
@@ -234,9 +274,12 @@ __global__ void __launch_bounds__(kThreads, 2)
     // (f, P, Q) table: 32 bytes per (unit, row pair): {f0, f1, P0, P1, Q0, Q1, -, -}.
     float* const tab = reinterpret_cast<float*>(smem + a.off_tab);
     float* const red = reinterpret_cast<float*>(smem + a.off_red);
-    uint64_t* const full_bar = reinterpret_cast<uint64_t*>(smem + a.off_bar);
-    uint64_t* const empty_bar = full_bar + a.num_slots;
-    volatile int* const abort_flag = reinterpret_cast<volatile int*>(empty_bar + a.num_slots);
+    // Synchronisation area: done[16] (tiles finished per consumer warp), landed, abort flag, then
+    // one mbarrier per slot for the bulk copies.
+    uint32_t* const sync_words = reinterpret_cast<uint32_t*>(smem + a.off_bar);
+    uint32_t const done0 = smem_u32(sync_words), landed_addr = done0 + 64;
+    volatile int* const abort_flag = reinterpret_cast<volatile int*>(sync_words + 17);
+    uint64_t* const full_bar = reinterpret_cast<uint64_t*>(smem + a.off_bar + 128);
 
     int const tid = threadIdx.x;
     int const warp = tid >> 5, lane = tid & 31;
@@ -256,11 +299,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (tid == 0)
     {
         for (int s = 0; s < a.num_slots; ++s)
-        {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kWarps);
-        }
-        *abort_flag = 0;
+        for (int i = 0; i < 18; ++i)
+            sync_words[i] = 0u;
         mbar_fence_init();
     }
     else if (tid == 32)
@@ -285,23 +326,32 @@ __global__ void __launch_bounds__(kThreads, 2)
             // Weights that the preceding kernel may still be writing must not be fetched early.
             if (!a.weights_static)
                 asm volatile("griddepcontrol.wait;" ::: "memory");
-            int slot = 0, use = 0, cg = 0, panel = 0;
+            int slot = 0, cg = 0, panel = 0;
             uint32_t const box_bytes = uint32_t(a.groups_per_panel) * kBoxCols * 2;
             for (int j = 0; j < num_tiles; ++j)
             {
                 if (j >= a.num_slots)
                 {
-                    if (!wait_bar(smem_u32(&empty_bar[slot]), (use - 1) & 1, abort_flag))
+                    // every consumer warp has finished the tile that used this slot before
+                    uint32_t const needed = uint32_t(j - a.num_slots + 1);
+                    uint32_t polls = 0;
+                    bool free_now = all_done(done0, needed);
+                    while (!free_now)
+                    {
+                        if ((++polls & 4095u) == 0 && (*abort_flag || polls >= kMaxSpinPolls))
+                            break;
+                        free_now = all_done(done0, needed);
+                    }
+                    if (!free_now)
+                    {
+                        *abort_flag = 1;
+                        atomicExch(&g_device_status, kDeviceTimeout);
                         break;
+                    }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                if (j >= a.depth)
-                {
-                    int const sd = slot >= a.depth ? slot - a.depth : slot - a.depth + a.num_slots;
-                    int const ud = slot >= a.depth ? use : use - 1;
-                    if (!wait_bar(smem_u32(&full_bar[sd]), ud & 1, abort_flag))
-                        break;
-                }
+                if (j >= a.depth && !wait_count(landed_addr, uint32_t(j - a.depth + 1), abort_flag))
+                    break;
                 int const row_first = (c0 + cg) * C::RPG;
                 int const kp_len = min(C::KP, a.k - panel * C::KP);
                 uint32_t const bytes = 2u * kp_len;
@@ -324,9 +374,29 @@ __global__ void __launch_bounds__(kThreads, 2)
                     ++cg;
                 }
                 if (++slot == a.num_slots)
+                    slot = 0;
+            }
+        }
+        return;
+    }
+    // ---------------------------------------------------------------------- watcher
+    // The only warp that waits on the copies' mbarriers: tiles land in order, so it walks the slots
+    // and publishes how many tiles have arrived.
+    if (warp == kWarps + 1)
+    {
+        if (lane == 0)
+        {
+            int slot = 0;
+            uint32_t parity = 0;
+            for (int j = 0; j < num_tiles; ++j)
+            {
+                if (!wait_bar(smem_u32(&full_bar[slot]), parity, abort_flag))
+                    break;
+                publish(landed_addr, uint32_t(j + 1));
+                if (++slot == a.num_slots)
                 {
                     slot = 0;
-                    ++use;
+                    parity ^= 1;
                 }
             }
         }
@@ -358,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     // (f, P, Q) entries of the activation rows 2t, 2t+1 behind this thread's accumulator columns.
     uint32_t tab0 = smem_u32(tab) + (t < MT ? t : MT - 1) * 32;
     int const tstride = MT * 32;
-    uint32_t const full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+    uint32_t const my_done = done0 + 4 * warp;
     // These per-thread addresses are used once per tile; keep them in registers (the compiler would
     // otherwise recompute them from the thread index inside the loop, some thirty instructions per tile).
     keep_in_register(wA0);
@@ -368,11 +438,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     keep_in_register(ustride);
     keep_in_register(tab0);
 
-    // Activations (and, later, the output) belong to the preceding kernels: wait for them here.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
     // ---- stage the activations: act * pre-quant scale (rounded to T) -> fp16, per (row, unit).
-    // One warp per (row, unit) job, JB jobs at a time with all their global loads issued first.
+    // One warp per (row, unit) job, JB jobs at a time with all their global loads issued first. The
+    // pre-quant scale is a weight-like constant: when the caller declared the weights static, the
+    // first batch's scales are fetched before the wait for the preceding kernel.
     {
         T const* act = static_cast<T const*>(a.act);
         T const* ps = static_cast<T const*>(a.act_scale);
@@ -381,6 +450,32 @@ __global__ void __launch_bounds__(kThreads, 2)
         int const jobs = a.m * units;
         constexpr int VPL = C::UK / 32; // values per lane: 4 (int4) or 2 (int8)
         constexpr int JB = 4;
+        uint2 scv[JB];
+        auto load_scales = [&](int job0)
+        {
+#pragma unroll
+            for (int j = 0; j < JB; ++j)
+            {
+                int const job = job0 + j * kWarps;
+                scv[j] = make_uint2(0u, 0u);
+                if (job < jobs)
+                {
+                    int const u = job % units;
+                    int const k0 = u * C::UK + lane * VPL;
+                    if (VPL == 4)
+                        scv[j] = __ldg(reinterpret_cast<uint2 const*>(ps + k0));
+                    else
+                        scv[j].x = __ldg(reinterpret_cast<uint32_t const*>(ps + k0));
+                }
+            }
+        };
+        bool const ps_early = ps != nullptr && a.weights_static;
+        if (ps_early)
+            load_scales(warp);
+
+        // Activations (and, later, the output) belong to the preceding kernels: wait for them here.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+
         for (int job0 = warp; job0 < jobs; job0 += kWarps * JB)
         {
             uint2 x[JB];
@@ -397,17 +492,18 @@ __global__ void __launch_bounds__(kThreads, 2)
                         x[j] = __ldg(reinterpret_cast<uint2 const*>(act + size_t(row) * a.k + k0));
                     else
                         x[j].x = __ldg(reinterpret_cast<uint32_t const*>(act + size_t(row) * a.k + k0));
-                    if (ps)
-                    {
-                        if (VPL == 4)
-                        {
-                            uint2 const sc = __ldg(reinterpret_cast<uint2 const*>(ps + k0));
-                            x[j].x = P::mul(x[j].x, sc.x);
-                            x[j].y = P::mul(x[j].y, sc.y);
-                        }
-                        else
-                            x[j].x = P::mul(x[j].x, __ldg(reinterpret_cast<uint32_t const*>(ps + k0)));
-                    }
+                }
+            }
+            if (ps)
+            {
+                if (!(ps_early && job0 == warp))
+                    load_scales(job0);
+#pragma unroll
+                for (int j = 0; j < JB; ++j)
+                {
+                    x[j].x = P::mul(x[j].x, scv[j].x);
+                    if (VPL == 4)
+                        x[j].y = P::mul(x[j].y, scv[j].y);
                 }
             }
 #pragma unroll
@@ -494,19 +590,11 @@ __global__ void __launch_bounds__(kThreads, 2)
     int const batch = max(1, (a.red_bytes / 4) / per_cg); // column groups per reduction
     bool ok = true;
     int s = 0, panel = 0, cb = 0, cg = 0;
-    uint32_t phase = 0;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t ready = num_tiles > 0 ? probe_bar(full0, 0) : 1u; // probe of the tile about to be consumed
     for (int tile = 0; tile < num_tiles; ++tile)
     {
-        if (ok && !ready)
-            ok = wait_slow(full0 + 8 * s, phase, abort_flag);
-        // Probe the next tile's barrier now: the answer is back by the time this tile is done.
-        {
-            int const sn = s + 1 == a.num_slots ? 0 : s + 1;
-            uint32_t const pn = s + 1 == a.num_slots ? phase ^ 1 : phase;
-            ready = tile + 1 < num_tiles ? probe_bar(full0 + 8 * sn, pn) : 1u;
-        }
+        if (ok)
+            ok = wait_count(landed_addr, uint32_t(tile + 1), abort_flag);
         uint32_t const so = uint32_t(s) * uint32_t(a.slot_bytes);
         int const u = panel * kWarps + warp;
         if (u < units)
@@ -516,6 +604,26 @@ __global__ void __launch_bounds__(kThreads, 2)
             uint32_t const ra[4] = {wa.x, wa.y, wa.z, wa.w};
             uint32_t const rb[4] = {wb.x, wb.y, wb.z, wb.w};
             uint32_t const au = act0 + u * ustride;
+            // scale / zero words of the thread's two columns and the unit's (f, P, Q) entries: fetched
+            // up front so that their latency hides behind the nibble extraction
+            uint32_t s_word, z_word = 0;
+            if (BITS == 4)
+            {
+                s_word = lds32<0>(sc0 + so);
+                if (HAS_ZERO)
+                    z_word = lds32<kZeroBoxOff>(sc0 + so);
+            }
+            else
+            {
+                s_word = lds16<0>(sc0 + so) | (lds16<16>(sc0 + so) << 16);
+                if (HAS_ZERO)
+                    z_word = lds16<kZeroBoxOff>(sc0 + so) | (lds16<kZeroBoxOff + 16>(sc0 + so) << 16);
+            }
+            uint32_t const ta = tab0 + u * tstride;
+            uint4 const fp = lds128<0>(ta); // f0, f1, P0, P1
+            uint2 q2 = make_uint2(0u, 0u);  // Q0, Q1
+            if (HAS_ZERO)
+                q2 = lds64<16>(ta);
             float S[2][4];
             if (BITS == 4)
             {
@@ -568,25 +676,10 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
             }
             // scale, zero and the magic / storage-offset correction on the fp32 unit sums
-            uint32_t s_word, z_word = 0;
-            if (BITS == 4)
-            {
-                s_word = lds32<0>(sc0 + so);
-                if (HAS_ZERO)
-                    z_word = lds32<kZeroBoxOff>(sc0 + so);
-            }
-            else
-            {
-                s_word = lds16<0>(sc0 + so) | (lds16<16>(sc0 + so) << 16);
-                if (HAS_ZERO)
-                    z_word = lds16<kZeroBoxOff>(sc0 + so) | (lds16<kZeroBoxOff + 16>(sc0 + so) << 16);
-            }
             float sA, sB, zA = 0.f, zB = 0.f;
             P::unpack2(s_word, sA, sB);
             if (HAS_ZERO)
                 P::unpack2(z_word, zA, zB);
-            uint32_t const ta = tab0 + u * tstride;
-            uint4 const fp = lds128<0>(ta); // f0, f1, P0, P1
             float const f0 = __uint_as_float(fp.x), f1 = __uint_as_float(fp.y);
             float const p0 = __uint_as_float(fp.z), p1 = __uint_as_float(fp.w);
             acc[0] = fmaf(sA, fmaf(S[0][0] + S[1][0], f0, -p0), acc[0]);
@@ -595,7 +688,6 @@ __global__ void __launch_bounds__(kThreads, 2)
             acc[3] = fmaf(sB, fmaf(S[0][3] + S[1][3], f1, -p1), acc[3]);
             if (HAS_ZERO)
             {
-                uint2 const q2 = lds64<16>(ta); // Q0, Q1
                 float const q0 = __uint_as_float(q2.x), q1 = __uint_as_float(q2.y);
                 acc[0] = fmaf(zA, q0, acc[0]);
                 acc[1] = fmaf(zA, q1, acc[1]);
@@ -605,12 +697,9 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         __syncwarp();
         if (lane == 0)
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+            publish(my_done, uint32_t(tile + 1));
         if (++s == a.num_slots)
-        {
             s = 0;
-            phase ^= 1;
-        }
         if (++panel < num_panels)
             continue;
 
@@ -691,7 +780,7 @@ static bool plan(Args& a, DeviceInfo const& dev, int grid, size_t* smem_bytes)
         red = red_cap / per_cg * per_cg;
     a.red_bytes = red;
     int const fixed_front = act_bytes + 128 + fpq_bytes + round_up(red, 128);
-    auto slots_for = [&](int budget) { return (budget - fixed_front - 256) / a.slot_bytes; };
+    auto slots_for = [&](int budget) { return (budget - fixed_front - 384) / a.slot_bytes; };
     int slots = slots_for(kHalfSmSmem);
     if (slots >= 5)
         slots = slots > 6 ? 6 : slots; // two CTAs (of consecutive launches) per SM
@@ -711,7 +800,7 @@ static bool plan(Args& a, DeviceInfo const& dev, int grid, size_t* smem_bytes)
     a.off_tab = a.off_zero + 128;
     a.off_red = a.off_tab + fpq_bytes;
     a.off_bar = a.off_red + round_up(red, 128);
-    *smem_bytes = size_t(a.off_bar) + size_t(slots) * 16 + 16;
+    *smem_bytes = size_t(a.off_bar) + 128 + size_t(slots) * 8;
     return true;
 }
 

@@ -304,24 +304,51 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
         return self
 
 
-def allreduce_oneshot(partial_ptrs, flag_ptrs, out: torch.Tensor, n: int, rank: int, epoch: int, bias=None,
-                      timeout_ms: int = 0, stream=None) -> None:
-    """out = sum over ranks (rank order, fp32) of the [count] partials behind ``partial_ptrs`` (+ bias).
-    ``partial_ptrs[r]`` / ``flag_ptrs[r]``: device addresses of rank r's partial buffer and flag
-    words as mapped into this process (see ``tp.OneShotAllReduce``). Mirrors the custom all-reduce the
-    reference uses behind dense row-parallel layers (kernels/customAllReduceKernels.cu:1307)."""
-    world = len(partial_ptrs)
-    if world != len(flag_ptrs) or not 1 <= world <= _lib.W4_MAX_RANKS:
-        raise RuntimeError("allreduce_oneshot: need 1..8 ranks and as many flag pointers as partial pointers")
+def allreduce_workspace_bytes(max_message_bytes: int, world: int) -> int:
+    """Size of one rank's peer-mapped workspace block for messages of up to ``max_message_bytes``."""
+    return int(_lib.lib().w4_allreduce_workspace_bytes(int(max_message_bytes), int(world)))
+
+
+def _allreduce_params(partial, workspace_ptrs, workspace_bytes, out, n, rank, bias, mode, timeout_ms):
+    world = len(workspace_ptrs)
+    if not 1 <= world <= _lib.W4_MAX_RANKS:
+        raise RuntimeError("allreduce: need 1..8 ranks")
     p = _lib.W4AllReduceParams()
+    p.partial = partial.data_ptr()
     for r in range(world):
-        p.partials[r] = int(partial_ptrs[r])
-        p.flags[r] = int(flag_ptrs[r])
+        p.workspace[r] = int(workspace_ptrs[r])
+    p.workspace_bytes = int(workspace_bytes)
     p.bias = bias.data_ptr() if bias is not None else None
     p.out = out.data_ptr()
     p.count, p.n, p.rank, p.world = out.numel(), n, rank, world
-    p.act_dtype, p.epoch, p.timeout_ms = _DTYPES[out.dtype], epoch & 0xFFFFFFFF, timeout_ms
+    p.act_dtype, p.mode, p.timeout_ms = _DTYPES[out.dtype], mode, timeout_ms
+    return p
+
+
+def allreduce(partial: torch.Tensor, workspace_ptrs, workspace_bytes: int, out: torch.Tensor, n: int, rank: int,
+              bias=None, mode: int = _lib.W4_ALLREDUCE_AUTO, timeout_ms: int = 0, stream=None) -> None:
+    """out = sum over ranks (rank order, fp32) of every rank's ``partial`` (+ bias), through peer memory.
+    ``workspace_ptrs[r]``: device address of rank r's workspace block as mapped into this process (see
+    ``tp.PeerAllReduce``). Mirrors the custom all-reduce the reference uses behind dense row-parallel
+    layers (kernels/customAllReduceKernels.cu:1307,1426)."""
+    p = _allreduce_params(partial, workspace_ptrs, workspace_bytes, out, n, rank, bias, mode, timeout_ms)
     s = stream if stream is not None else torch.cuda.current_stream(out.device)
     with torch.cuda.device(out.device):
-        rc = _lib.lib().w4_allreduce_oneshot(ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
-    _lib.check(rc, "allreduce_oneshot")
+        rc = _lib.lib().w4_allreduce(ctypes.byref(p), ctypes.c_void_p(s.cuda_stream))
+    _lib.check(rc, "allreduce")
+
+
+def allreduce_emulated(partials, workspaces, outs, n: int, biases=None, mode: int = _lib.W4_ALLREDUCE_AUTO,
+                       timeout_ms: int = 0, stream=None) -> None:
+    """All ranks of an all-reduce as one cooperative launch on the current GPU (every buffer local):
+    ``partials[r]``, ``workspaces[r]`` (uint8 tensors), ``outs[r]`` belong to rank r."""
+    world = len(partials)
+    arr = (_lib.W4AllReduceParams * world)()
+    ptrs = [w.data_ptr() for w in workspaces]
+    for r in range(world):
+        arr[r] = _allreduce_params(partials[r], ptrs, workspaces[r].numel(), outs[r], n, r,
+                                   None if biases is None else biases[r], mode, timeout_ms)
+    s = stream if stream is not None else torch.cuda.current_stream(outs[0].device)
+    with torch.cuda.device(outs[0].device):
+        rc = _lib.lib().w4_allreduce_emulated(arr, world, ctypes.c_void_p(s.cuda_stream))
+    _lib.check(rc, "allreduce_emulated")

@@ -1,10 +1,12 @@
-"""GPU: the one-shot peer-memory all-reduce behind row-parallel layers (w4_allreduce_oneshot).
+"""GPU: the peer-memory all-reduce behind row-parallel layers (w4_allreduce).
 
-On one GPU the ranks are emulated by one launch over all ranks' data: every "peer" buffer is local
-and the flag words of the other ranks are set from the host before the launch, so no kernel ever
-waits for another kernel. The bounded wait is exercised with a flag that nothing sets and a short
-limit: the kernel must give up, leave the output alone and report the timeout through the device
-status word. With two or more GPUs the real thing runs as child processes against NCCL."""
+On one GPU the ranks are emulated by ONE cooperative launch over all ranks' buffers
+(w4_allreduce_emulated): every "peer" block is local memory and the CTAs of all ranks are
+co-resident, so no kernel ever waits for another kernel. The call number lives in the workspace on the
+device: the same launch is repeated (and replayed from a CUDA graph) without any host-side counter.
+The bounded wait is exercised with a single-rank launch whose peer never pushes and a short limit:
+the kernel must give up and report the timeout through the device status word. With two or more
+GPUs the real thing runs as child processes against NCCL."""
 import os
 import subprocess
 import sys
@@ -17,80 +19,126 @@ from tensorrt_llm_b200 import ops
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+L = pkg._lib
 
 
-def _emulated(world, m, n, dtype, rank, epoch, bias):
-    torch.manual_seed(world * 100 + m + epoch)
+def _setup(world, m, n, dtype, max_bytes, seed, bias=False):
+    torch.manual_seed(seed)
     dev = "cuda"
     parts = [torch.randn(m, n, device=dev).to(dtype) for _ in range(world)]
-    flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(world)]
-    # every rank has "announced" (word `rank` is also written by the kernel); int32 view of the uint32 call number
-    flags[rank][:world] = epoch - (1 << 32) if epoch >= (1 << 31) else epoch
-    out = torch.zeros(m, n, dtype=dtype, device=dev)
+    nws = ops.allreduce_workspace_bytes(max_bytes, world)
+    wss = [torch.zeros(nws, dtype=torch.uint8, device=dev) for _ in range(world)]
+    outs = [torch.zeros(m, n, dtype=dtype, device=dev) for _ in range(world)]
     b = torch.randn(n, device=dev).to(dtype) if bias else None
-    ops.allreduce_oneshot([p.data_ptr() for p in parts], [f.data_ptr() for f in flags], out, n, rank, epoch, bias=b)
-    torch.cuda.synchronize()
-    acc = torch.zeros(m, n, dtype=torch.float32, device=dev)
+    return parts, wss, outs, b
+
+
+def _expected(parts, b):
+    acc = torch.zeros_like(parts[0], dtype=torch.float32)
     for p in parts:  # rank order, fp32: the kernel's order
         acc += p.float()
-    if bias:
+    if b is not None:
         acc += b.float()
-    # what the kernel told the "peers": word `rank` of every rank's flags
-    announced = [int(f[rank]) & 0xFFFFFFFF for f in flags]
-    return out, acc.to(dtype), announced
+    return acc.to(parts[0].dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
-@pytest.mark.parametrize("m,n", [(1, 8192), (3, 1024), (64, 8192)])
-def test_emulated_ranks_bit_exact(dtype, world, m, n):
-    rank, epoch = world - 1, 5
-    out, ref, announced = _emulated(world, m, n, dtype, rank, epoch, bias=(m == 3))
-    assert torch.equal(out, ref)
-    assert announced == [epoch] * world
-    assert pkg._lib.lib().w4_gemm_device_status() == 0
+@pytest.mark.parametrize("mode", [L.W4_ALLREDUCE_ONE_SHOT, L.W4_ALLREDUCE_TWO_SHOT])
+@pytest.mark.parametrize("m,n", [(1, 8192), (3, 1024), (64, 8192), (7, 4104)])
+def test_emulated_ranks_bit_exact(dtype, world, mode, m, n):
+    parts, wss, outs, b = _setup(world, m, n, dtype, max(m * n * 2, 1 << 16), world * 100 + m, bias=(m == 3))
+    biases = None if b is None else [b] * world
+    for call in range(3):  # consecutive calls use alternate copies of the inbox and the flags
+        for p in parts:
+            p.add_(1.0)
+        ops.allreduce_emulated(parts, wss, outs, n, biases=biases, mode=mode)
+        torch.cuda.synchronize()
+        ref = _expected(parts, b)
+        for r in range(world):
+            assert torch.equal(outs[r], ref), f"call {call}, rank {r}"
+        # the device-side call number of every rank
+        assert [int(w[:4].view(torch.int32)[0]) for w in wss] == [call + 1] * world
+    assert L.lib().w4_gemm_device_status() == 0
 
 
-def test_epoch_wraps():
-    out, ref, _ = _emulated(2, 1, 1024, torch.bfloat16, 0, 0xFFFFFFFF, bias=False)
-    assert torch.equal(out, ref)
+@pytest.mark.parametrize("mode,m", [(L.W4_ALLREDUCE_AUTO, 1), (L.W4_ALLREDUCE_AUTO, 64), (L.W4_ALLREDUCE_TWO_SHOT, 512)])
+def test_large_and_auto_modes(mode, m):
+    """AUTO picks by size (16 KB one-shot, 1 MB two-shot at 8 ranks); 8 MB through the two-shot path."""
+    world, n = 8, 8192
+    parts, wss, outs, _ = _setup(world, m, n, torch.bfloat16, 8 << 20, m)
+    ops.allreduce_emulated(parts, wss, outs, n, mode=mode)
+    torch.cuda.synchronize()
+    ref = _expected(parts, None)
+    for r in range(world):
+        assert torch.equal(outs[r], ref)
+
+
+def test_graph_replay_needs_no_host_counter():
+    """A captured launch replayed many times: every replay is a new call (fresh inputs each time)."""
+    world, m, n = 4, 2, 4096
+    parts, wss, outs, _ = _setup(world, m, n, torch.bfloat16, 1 << 20, 3)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        ops.allreduce_emulated(parts, wss, outs, n, stream=st)  # warm-up outside the capture
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            ops.allreduce_emulated(parts, wss, outs, n, stream=st)
+        for it in range(7):
+            for p in parts:
+                p.mul_(-0.5).add_(float(it))
+            g.replay()
+            st.synchronize()
+            ref = _expected(parts, None)
+            assert all(torch.equal(o, ref) for o in outs), f"replay {it}"
+    assert int(wss[0][:4].view(torch.int32)[0]) == 8  # 1 warm-up + 7 replays (the capture itself runs nothing)
 
 
 def test_peer_that_never_arrives_times_out():
-    dev = "cuda"
+    """Rank 0 of a 2-rank group launched alone: rank 1 never pushes. The wait must run out (20 ms)."""
     n = 1024
-    parts = [torch.ones(1, n, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    flags = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]  # rank 1 never announces
-    out = torch.full((1, n), 7.0, dtype=torch.bfloat16, device=dev)
-    ops.allreduce_oneshot([p.data_ptr() for p in parts], [f.data_ptr() for f in flags], out, n, 0, 1, timeout_ms=20)
+    parts, wss, outs, _ = _setup(2, 1, n, torch.bfloat16, 1 << 16, 9)
+    ops.allreduce(parts[0], [w.data_ptr() for w in wss], wss[0].numel(), outs[0], n, 0, timeout_ms=20)
     torch.cuda.synchronize()
-    assert pkg._lib.lib().w4_gemm_device_status() == pkg._lib.W4_ERR_DEVICE_TIMEOUT
-    assert pkg._lib.lib().w4_gemm_device_status() == 0  # reading clears it
-    assert bool((out == 7.0).all())  # untouched
-    # the context is still usable
-    out2, ref2, _ = _emulated(2, 1, n, torch.bfloat16, 0, 2, bias=False)
-    assert torch.equal(out2, ref2)
+    assert L.lib().w4_gemm_device_status() == L.W4_ERR_DEVICE_TIMEOUT
+    assert L.lib().w4_gemm_device_status() == 0  # reading clears it
+    # rank 0 did push its partial into rank 1's inbox before waiting (inbox copy of call 1 is copy 1)
+    # the context is still usable, and a cleared workspace works again
+    for w in wss:
+        w.zero_()
+    ops.allreduce_emulated(parts, wss, outs, n)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], _expected(parts, None)) and torch.equal(outs[1], outs[0])
 
 
 def test_argument_errors():
     dev = "cuda"
     a = torch.zeros(1, 1024, dtype=torch.bfloat16, device=dev)
-    f = torch.zeros(8, dtype=torch.int32, device=dev)
-    with pytest.raises(pkg._lib.W4Error):  # count not a multiple of 8
-        ops.allreduce_oneshot([a.data_ptr()], [f.data_ptr()], a[:, :1020].contiguous(), 1020, 0, 1)
-    big = torch.zeros(1024, 1024, dtype=torch.bfloat16, device=dev)  # 2 MiB > one-shot limit
-    with pytest.raises(pkg._lib.W4Error):
-        ops.allreduce_oneshot([big.data_ptr()], [f.data_ptr()], big, 1024, 0, 1)
+    ws = torch.zeros(ops.allreduce_workspace_bytes(1 << 16, 1), dtype=torch.uint8, device=dev)
+    with pytest.raises(L.W4Error):  # count not a multiple of 8
+        ops.allreduce(a[:, :1020].contiguous(), [ws.data_ptr()], ws.numel(), a[:, :1020].contiguous(), 1020, 0)
+    big = torch.zeros(64, 1024, dtype=torch.bfloat16, device=dev)  # 128 KiB > the 64 KiB the workspace was sized for
+    with pytest.raises(L.W4Error):
+        ops.allreduce(big, [ws.data_ptr()], ws.numel(), big, 1024, 0)
     with pytest.raises(RuntimeError):
-        ops.allreduce_oneshot([a.data_ptr()] * 9, [f.data_ptr()] * 9, a, 1024, 0, 1)
+        ops.allreduce(a, [ws.data_ptr()] * 9, ws.numel(), a, 1024, 0)
+    with pytest.raises(L.W4Error):  # one-shot forced above its limit
+        huge = torch.zeros(1024, 1024, dtype=torch.bfloat16, device=dev)
+        ws2 = torch.zeros(ops.allreduce_workspace_bytes(4 << 20, 2), dtype=torch.uint8, device=dev)
+        ops.allreduce(huge, [ws2.data_ptr()] * 2, ws2.numel(), huge, 1024, 0, mode=L.W4_ALLREDUCE_ONE_SHOT)
+    assert ops.allreduce_workspace_bytes(0, 2) == 0 and ops.allreduce_workspace_bytes(1024, 9) == 0
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpus_against_nccl():
-    """Row-parallel layer on 2 GPUs: GEMM into the shared buffer + one-shot reduce vs GEMM + NCCL."""
+def test_real_gpus_against_nccl():
+    """Row-parallel layer on all visible GPUs (2..8): GEMM + peer-memory reduce vs GEMM + NCCL, several
+    sizes through both forms, and a replayed CUDA graph of GEMM + reduce steps."""
+    n = min(torch.cuda.device_count(), 8)
+    n = 8 if n >= 8 else (4 if n >= 4 else 2)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", "_oneshot_worker.py")]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr",
+           "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", "_peer_allreduce_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "ONESHOT_OK" in r.stdout
+    assert "PEER_ALLREDUCE_OK" in r.stdout

@@ -93,9 +93,25 @@ def test_linearity_at_full_size():
     y12 = run_gpu(dict(p, act=s), regime=GEMM).float()
     scale = float(y12.abs().max())
     assert float((y12 - y1 - y2).abs().max()) <= 2e-2 * scale + float(resid.abs().max()) * k * 0.1
-    rows = torch.arange(0, m, 127)
+    # rows at the boundaries of every candidate row tile (128 / 192 / 256, the ragged last tile
+    # included: 4096 = 21 * 192 + 64) and a few random ones
+    from _cases import sample_rows
+    rows = torch.tensor(sample_rows(m, seed=4))
     ref = oracle_out(dict(p, act=p["act"][rows].contiguous(), m=len(rows)))
     assert max_err(y1[rows].to(torch.bfloat16), ref) <= oracle.tolerance(ref)
+
+
+@pytest.mark.parametrize("m,n,k,bits", [(1024, 4096, 4096, 4), (2048, 4096, 2048, 4), (176, 2048, 4096, 8),
+                                        (192, 2048, 4096, 8)])
+def test_odd_stage_counts_over_a_long_ring(m, n, k, bits):
+    """Row tiles whose shared-memory ring has three stages (int4 with 256 rows, int8 with 192), with
+    16 to 32 k steps: each conversion group meets a stage's barrier in every second phase only, so it
+    has to observe the phases in between as well."""
+    p = make_problem(m, n, k, bits, 128, torch.bfloat16, zero=True, seed=m + bits)
+    rows = list(range(0, m, 37)) + [m - 1]
+    out = run_gpu(p, regime=GEMM)
+    ref = oracle_out(dict(p, act=p["act"][rows].contiguous(), m=len(rows)))
+    assert max_err(out[rows], ref) <= oracle.tolerance(ref)
 
 
 @pytest.mark.parametrize("m,n,k,bits,group,dtype", [

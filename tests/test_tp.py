@@ -113,21 +113,26 @@ def test_rank_that_never_joins_times_out():
         dist.destroy_process_group()
 
 
-def test_oneshot_policy_and_buffer_alternation():
-    """Host logic of the peer-memory all-reduce helper (no GPU): the reference's size thresholds per
-    world size and the alternation between the two partial buffers."""
-    from tensorrt_llm_b200 import tp, _lib
+def test_peer_allreduce_workspace_sizing():
+    """Host logic of the peer-memory all-reduce (no GPU): the workspace grows monotonically with the
+    largest message, holds a whole one-shot message per sender or a slice of a two-shot one, and the
+    helper refuses messages beyond it."""
+    from tensorrt_llm_b200 import tp, ops, _lib
 
-    def helper(world):
-        h = object.__new__(tp.OneShotAllReduce)
-        h.world, h.max_bytes = world, _lib.W4_ONESHOT_MAX_BYTES
-        return h
-
-    assert helper(2).preferred(1 << 20) and not helper(2).preferred((1 << 20) + 16)
-    assert helper(4).preferred(999_984) and not helper(4).preferred(1 << 20)
-    assert helper(8).preferred(16384) and helper(8).preferred(499_984) and not helper(8).preferred(500_000)
-    assert not helper(8).preferred(16380)  # not a whole number of 16-byte vectors
-    h = helper(8)
-    offs = [h._offset(e) for e in (1, 2, 3, 4)]
-    assert offs[0] == offs[2] and offs[1] == offs[3] and offs[0] != offs[1]
-    assert min(offs) == tp.OneShotAllReduce.FLAG_BYTES and max(offs) == tp.OneShotAllReduce.FLAG_BYTES + h.max_bytes
+    header = 256 + 2 * (2 * _lib.W4_MAX_RANKS * _lib.W4_ALLREDUCE_MAX_CTAS * 4)
+    prev = 0
+    for world in (1, 2, 4, 8):
+        for mb in (16384, 1 << 20, (1 << 20) + 16, 8 << 20, 32 << 20):
+            nbytes = ops.allreduce_workspace_bytes(mb, world)
+            assert nbytes % 256 == 0 and nbytes > header
+            one = min(mb, _lib.W4_ONESHOT_MAX_BYTES)
+            # two copies of: world sender slots (a one-shot message or a slice) + the reduced slice
+            assert nbytes >= header + 2 * world * max(one, -(-mb // world)) + 2 * -(-mb // world)
+            if mb > 16384:
+                assert nbytes >= prev
+            prev = nbytes
+        prev = 0
+    assert ops.allreduce_workspace_bytes(1 << 20, 0) == 0 and ops.allreduce_workspace_bytes(1 << 20, 9) == 0
+    h = object.__new__(tp.PeerAllReduce)
+    h.max_bytes = 1 << 20
+    assert h.fits(1 << 20) and h.fits(16384) and not h.fits((1 << 20) + 16) and not h.fits(16380)

@@ -42,6 +42,10 @@ def test_static_scratch_matches_workspace_path_twice():
     problems = [
         make_problem(384, 256, 1024, 4, 128, torch.bfloat16, zero=True, bias=True, prequant=True, seed=31),
         make_problem(100, 512, 512, 8, 64, torch.float16, zero=True, bias=False, prequant=True, seed=32),
+        # few output tiles: the kernel also parks the fp32 partial tiles of its split-k in the array,
+        # behind the scaled activations (1 MiB + 4.4 MiB here); run twice in a row
+        make_problem(64, 1280, 8192, 4, 128, torch.bfloat16, zero=True, bias=True, prequant=True, seed=33),
+        make_problem(64, 1280, 8192, 4, 128, torch.bfloat16, zero=True, bias=True, prequant=True, seed=34),
     ]
     for p in problems:
         need = lib.w4_gemm_workspace_bytes(p["m"], p["n"], p["k"], p["group"], p["bits"],
@@ -54,10 +58,18 @@ def test_static_scratch_matches_workspace_path_twice():
 
         out = torch.zeros_like(ref_out)
         params2, keep2 = _params(p, dev, out, None)  # no workspace at all
+        # a first call resolves the array's address and loads the kernels; the device's free memory
+        # (driver view: catches a cudaMalloc inside the library, which torch's own counter would not)
+        # must not move across the second
+        assert lib.w4_gemm_launch_static_scratch(ctypes.byref(params2), stream) == 0
+        torch.cuda.synchronize()
+        out.zero_()
+        free_before, _ = torch.cuda.mem_get_info(dev)
         before = torch.cuda.memory_allocated(dev)
         assert lib.w4_gemm_launch_static_scratch(ctypes.byref(params2), stream) == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before
+        assert torch.cuda.mem_get_info(dev)[0] >= free_before  # nothing was taken from the device
         assert lib.w4_gemm_device_status() == 0
         assert torch.equal(out, ref_out), float((out.float() - ref_out.float()).abs().max())
         assert float(out.float().abs().max()) > 0
