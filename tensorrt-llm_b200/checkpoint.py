@@ -12,9 +12,19 @@ Restates, for one linear layer, what TensorRT-LLM does when it loads a 4-bit GPT
            0,4,1,5,2,6,3,7), ``qzeros`` int32 [K/G, N/8] in the same order, ``scales`` [K/G, N];
            w = (u - z) * s
 
-Both become signed int4 weights q = u - 8 with ``zero = (8 - z [- 1 for GPTQ]) * s`` already
+* ModelOpt-AWQ (TensorRT-LLM unified checkpoints): ``weight`` uint8 [N/2, K] holding two's-complement
+           int4 pairs of adjacent output features (low nibble first), ``weight_scale`` [N, K/G],
+           ``input_quantizer._pre_quant_scale`` [K]; no zeros;  w = q * s on activations x * pre_quant_scale
+
+GPTQ and HF-AWQ become signed int4 weights q = u - 8 with ``zero = (8 - z [- 1 for GPTQ]) * s`` already
 multiplied by the scale, which is the form the kernels (and the reference's plugin) take. Host-side
 tensor code only; the layout transform and the GEMM run through the library.
+
+``convert_llama_layer`` applies this to the seven linears of one Hugging Face Llama decoder layer and
+emits the TensorRT-LLM parameter names (q/k/v fused into ``attention.qkv``, ``o_proj`` ->
+``attention.dense``, ``gate_proj`` -> ``mlp.fc``, ``up_proj`` -> ``mlp.gate``, ``down_proj`` ->
+``mlp.proj``; tensorrt_llm/models/model_weights_loader.py:56-62 of the reference), sharded for one
+tensor-parallel rank.
 """
 from __future__ import annotations
 
@@ -65,6 +75,75 @@ def hf_awq_to_signed(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.
     return _finish(u, uz, scales, dtype, gptq=False)
 
 
+def modelopt_awq_to_signed(weight: torch.Tensor, weight_scale: torch.Tensor, pre_quant_scale: torch.Tensor,
+                           dtype=torch.float16):
+    """ModelOpt INT4-AWQ tensors of one layer -> (q int8 [K, N] in [-8, 7], scales [K/G, N] dtype, None,
+    pre_quant_scale [K] dtype) (functional.py:962-968, 919-937, 1023-1031 of the reference)."""
+    if weight.dtype not in (torch.uint8, torch.int8):
+        raise ValueError("ModelOpt-AWQ weight must be a byte tensor [N/2, K]")
+    u = unpack_int32_into_int8(weight.T)            # [K, N], nibbles as 0..15
+    q = torch.where(u >= 8, u - 16, u).to(torch.int8)  # two's-complement int4
+    k, n = q.shape
+    if weight_scale.numel() % n:
+        raise ValueError("weight_scale does not hold whole groups for every output feature")
+    scales = weight_scale.to(dtype).reshape(n, -1).T.contiguous()
+    if k % scales.shape[0]:
+        raise ValueError("K is not a multiple of the number of scale groups")
+    return q, scales, None, pre_quant_scale.to(dtype).reshape(-1)
+
+
+# Hugging Face Llama module -> TensorRT-LLM module, and how each is sharded
+LLAMA_LINEARS = (
+    ("attention.qkv", ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), "column"),
+    ("attention.dense", ("self_attn.o_proj",), "row"),
+    ("mlp.fc", ("mlp.gate_proj",), "column"),
+    ("mlp.gate", ("mlp.up_proj",), "column"),
+    ("mlp.proj", ("mlp.down_proj",), "row"),
+)
+
+
+def _layer_to_signed(fmt: str, state: Dict[str, torch.Tensor], name: str, dtype):
+    """(q, scales, zero, pre_quant_scale) of one Hugging Face linear in checkpoint format ``fmt``."""
+    if fmt == "gptq":
+        return gptq_to_signed(state[f"{name}.qweight"], state[f"{name}.qzeros"], state[f"{name}.scales"], dtype) + (None,)
+    if fmt == "awq":
+        return hf_awq_to_signed(state[f"{name}.qweight"], state[f"{name}.qzeros"], state[f"{name}.scales"], dtype) + (None,)
+    if fmt == "modelopt_awq":
+        return modelopt_awq_to_signed(state[f"{name}.weight"], state[f"{name}.weight_scale"],
+                                      state[f"{name}.input_quantizer._pre_quant_scale"], dtype)
+    raise ValueError("fmt must be 'gptq', 'awq' or 'modelopt_awq'")
+
+
+def convert_llama_layer(fmt: str, state: Dict[str, torch.Tensor], layer: int, *, mapping: Optional[Mapping] = None,
+                        group_size: int = 128, dtype=torch.float16, hf_prefix: str = "model.layers",
+                        tllm_prefix: str = "transformer.layers") -> Dict[str, torch.Tensor]:
+    """The TensorRT-LLM tensors of decoder layer ``layer`` for one tensor-parallel rank, from a Hugging
+    Face Llama state dict in GPTQ, AutoAWQ or ModelOpt-AWQ format. Column-parallel linears keep this
+    rank's chunk of the output features (q, k and v are chunked separately, then fused), row-parallel
+    ones this rank's chunk of the input features; features are padded to whole tiles / groups per rank
+    first, as the reference's layers do."""
+    mapping = mapping or Mapping(world_size=1, rank=0, tp_size=1)
+    tp_size, r = mapping.tp_size, mapping.tp_rank
+    out: Dict[str, torch.Tensor] = {}
+    for tllm_name, hf_names, kind in LLAMA_LINEARS:
+        shards = []
+        for hf in hf_names:
+            q, s, z, ps = _layer_to_signed(fmt, state, f"{hf_prefix}.{layer}.{hf}", dtype)
+            bias = state.get(f"{hf_prefix}.{layer}.{hf}.bias")
+            q, s, z, bias, ps, _, _ = tp.pad_quantized_for_tp(q, s, z, bias, ps, group_size, tp_size)
+            if kind == "column":
+                last = lambda t: None if t is None else tp.split(t, tp_size, r, dim=t.dim() - 1)  # noqa: E731
+                shards.append((tp.split(q, tp_size, r, dim=1), last(s), last(z), last(bias), ps))
+            else:
+                rows = lambda t: None if t is None else tp.split(t, tp_size, r, dim=0)  # noqa: E731
+                shards.append((tp.split(q, tp_size, r, dim=0), rows(s), rows(z), bias, rows(ps)))
+        cat = lambda i: None if shards[0][i] is None else torch.cat([x[i] for x in shards], dim=-1)  # noqa: E731
+        q, s, z, bias = cat(0), cat(1), cat(2), cat(3)
+        out.update(to_tllm_tensors(f"{tllm_prefix}.{layer}.{tllm_name}", q, s, z, dtype,
+                                   prequant_scale=shards[0][4], bias=bias))
+    return out
+
+
 def to_tllm_tensors(prefix: str, q: torch.Tensor, scales: torch.Tensor, zero: Optional[torch.Tensor],
                     dtype=torch.float16, prequant_scale: Optional[torch.Tensor] = None,
                     bias: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
@@ -107,13 +186,17 @@ def sharded_linear_from_checkpoint(fmt: str, qweight, qzeros, scales, *, mapping
                                    group_size: int = 128, dtype=torch.float16, device="cuda", bias=None, group=None):
     """GPTQ (``fmt="gptq"``) or AutoAWQ (``fmt="awq"``) tensors of one layer -> this rank's
     tensor-parallel layer (column: split N; row: split K, all-reduce after)."""
-    if fmt not in ("gptq", "awq"):
-        raise ValueError("fmt must be 'gptq' or 'awq'")
-    q, s, z = (gptq_to_signed if fmt == "gptq" else hf_awq_to_signed)(qweight, qzeros, scales, dtype)
+    if fmt not in ("gptq", "awq", "modelopt_awq"):
+        raise ValueError("fmt must be 'gptq', 'awq' or 'modelopt_awq'")
+    ps = None
+    if fmt == "modelopt_awq":  # (weight, pre_quant_scale, weight_scale) in place of (qweight, qzeros, scales)
+        q, s, z, ps = modelopt_awq_to_signed(qweight, scales, qzeros, dtype)
+    else:
+        q, s, z = (gptq_to_signed if fmt == "gptq" else hf_awq_to_signed)(qweight, qzeros, scales, dtype)
     if parallel == "column":
-        return tp.WeightOnlyColumnLinear.from_quantized(mapping, q, s, z, bias, bits=4, group_size=group_size,
+        return tp.WeightOnlyColumnLinear.from_quantized(mapping, q, s, z, bias, ps, bits=4, group_size=group_size,
                                                         dtype=dtype, device=device)
     if parallel == "row":
-        return tp.WeightOnlyRowLinear.from_quantized(mapping, q, s, z, bias, bits=4, group_size=group_size,
+        return tp.WeightOnlyRowLinear.from_quantized(mapping, q, s, z, bias, ps, bits=4, group_size=group_size,
                                                      dtype=dtype, device=device, group=group)
     raise ValueError("parallel must be 'column' or 'row'")

@@ -36,6 +36,48 @@ def split(v: torch.Tensor, tp_size: int, idx: int, dim: int = 0) -> torch.Tensor
     return torch.chunk(v, tp_size, dim=dim)[idx].contiguous()
 
 
+def padded_features(features: int, group_size: int, tp_size: int) -> int:
+    """Feature count the reference's quantised linears round in/out features up to before sharding:
+    a multiple of max(64, group_size) * tp_size (tensorrt_llm/quantization/layers.py:719-726 for
+    per-channel, :965-972 and :1091-1098 for groupwise layers), so that every shard keeps whole
+    64-wide tiles and whole scale groups."""
+    multiple = max(64, group_size) * tp_size
+    return -(-features // multiple) * multiple
+
+
+def pad_like(t: Optional[torch.Tensor], shape, value=0) -> Optional[torch.Tensor]:
+    """Pads ``t`` at the end of every dimension up to ``shape`` (functional.py:861-872 of the reference)."""
+    if t is None or tuple(t.shape) == tuple(shape):
+        return t
+    pad = []
+    for dim in range(len(shape)):
+        d = -1 - dim
+        pad += [0, max(0, shape[d] - t.shape[d])]
+    return torch.nn.functional.pad(t, pad, value=value)
+
+
+def pad_quantized_for_tp(q, scales, zeros, bias, pre_quant_scale, group_size: int, tp_size: int):
+    """Pads a whole (unsharded) layer's tensors to ``padded_features`` in both dimensions: integer
+    weights and zeros with 0, scales with 1, bias and pre-quant scale with 0. Padded input features
+    meet zero activations and padded output features are cut off by the caller, so the fill values
+    never reach a result (the reference fills with the same neutral values,
+    tensorrt_llm/quantization/functional.py:983-1009). Returns the padded tensors and (k, n) padded."""
+    k, n = q.shape
+    kp, np_ = padded_features(k, group_size, tp_size), padded_features(n, group_size, tp_size)
+    if (kp, np_) == (k, n):
+        return q, scales, zeros, bias, pre_quant_scale, k, n
+    q = pad_like(q, (kp, np_), 0)
+    if group_size == 0:
+        scales, zeros = pad_like(scales, (np_,), 1), pad_like(zeros, (np_,), 0)
+    else:
+        scales = pad_like(scales, (kp // group_size, np_), 1)
+        zeros = pad_like(zeros, (kp // group_size, np_), 0)
+    bias = pad_like(bias, (np_,), 0)
+    if pre_quant_scale is not None:
+        pre_quant_scale = pad_like(pre_quant_scale.reshape(-1), (kp,), 0)
+    return q, scales, zeros, bias, pre_quant_scale, kp, np_
+
+
 def _check_shard(k: int, n: int, bits: int, group_size: int):
     if k % 64 or (n * bits // 8) % 32:
         raise ValueError(f"shard [{k}, {n}] violates the layout's divisibility rules (k % 64, n*bits/8 % 32)")
@@ -81,9 +123,14 @@ class WeightOnlyColumnLinear(_ShardedLinear):
     @classmethod
     def from_quantized(cls, mapping, q, scales, zeros=None, bias=None, pre_quant_scale=None, *, bits=4,
                        group_size=128, dtype=torch.bfloat16, device="cpu"):
-        """q: signed int8 [K, N]; scales/zeros: [K/G, N] (or [N] for group_size 0); bias [N]."""
+        """q: signed int8 [K, N]; scales/zeros: [K/G, N] (or [N] for group_size 0); bias [N]. Features
+        that do not divide into whole tiles / groups per rank are padded first, as the reference does;
+        ``in_features`` / ``out_features`` keep the padded sizes, ``n_valid`` the real output width."""
         self = cls(mapping, bits, group_size, dtype, device)
         tp, r = mapping.tp_size, mapping.tp_rank
+        self.n_valid = q.shape[1]
+        q, scales, zeros, bias, pre_quant_scale, self.in_features, self.out_features = pad_quantized_for_tp(
+            q, scales, zeros, bias, pre_quant_scale, group_size, tp)
         last = lambda t: None if t is None else split(t, tp, r, dim=t.dim() - 1)
         self._load(split(q, tp, r, dim=1), last(scales), last(zeros), last(bias), pre_quant_scale)
         return self
@@ -114,8 +161,13 @@ class WeightOnlyRowLinear(_ShardedLinear):
     @classmethod
     def from_quantized(cls, mapping, q, scales, zeros=None, bias=None, pre_quant_scale=None, *, bits=4,
                        group_size=128, dtype=torch.bfloat16, device="cpu", group=None):
+        """As the column-parallel form; a padded K means this rank expects ``in_features / tp`` input
+        features per row (zeros in the padded tail, as the padded layer in front of it produces)."""
         self = cls(mapping, bits, group_size, dtype, device)
         tp, r = mapping.tp_size, mapping.tp_rank
+        self.n_valid = q.shape[1]
+        q, scales, zeros, bias, pre_quant_scale, self.in_features, self.out_features = pad_quantized_for_tp(
+            q, scales, zeros, bias, pre_quant_scale, group_size, tp)
         rows = lambda t: None if t is None else (t if group_size == 0 else split(t, tp, r, dim=0))
         ps = None if pre_quant_scale is None else split(pre_quant_scale.reshape(-1), tp, r, dim=0)
         self._load(split(q, tp, r, dim=0), rows(scales), rows(zeros), bias, ps)

@@ -74,6 +74,86 @@ def test_tllm_tensor_names_and_bytes():
     assert torch.equal(t[f"{p}.weight"].view(torch.int8), expect)
 
 
+def test_modelopt_awq_unpacking():
+    """ModelOpt INT4-AWQ: bytes [N/2, K] of two's-complement nibble pairs of adjacent output features,
+    scales [N, K/G], a pre-quant scale; no zeros."""
+    rng = np.random.default_rng(5)
+    k, n, group = 256, 64, 128
+    q = rng.integers(-8, 8, size=(k, n)).astype(np.int8)
+    u = (q.astype(np.int16) & 15).astype(np.uint8)          # two's-complement nibbles
+    weight = torch.from_numpy((u[:, 0::2] | (u[:, 1::2] << 4)).T.copy())  # [N/2, K]
+    wscale = torch.from_numpy(rng.uniform(0.001, 0.02, size=(n, k // group)).astype(np.float32))
+    ps = torch.from_numpy(rng.uniform(0.5, 1.5, size=(k,)).astype(np.float32))
+    q2, s2, z2, ps2 = ck.modelopt_awq_to_signed(weight, wscale, ps)
+    assert z2 is None and torch.equal(q2, torch.from_numpy(q))
+    assert tuple(s2.shape) == (k // group, n) and torch.equal(s2, wscale.half().T.contiguous())
+    assert torch.equal(ps2, ps.half())
+    with pytest.raises(ValueError):
+        ck.modelopt_awq_to_signed(weight.to(torch.int32), wscale, ps)
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq", "modelopt_awq"])
+@pytest.mark.parametrize("tp_size", [1, 2])
+def test_llama_layer_key_mapping_and_sharding(fmt, tp_size):
+    """One Hugging Face Llama decoder layer -> TensorRT-LLM names, q/k/v fused, sharded per rank; the
+    dequantised shards reassemble to the dequantised full matrices."""
+    rng = np.random.default_rng(11)
+    hidden, inter, kv, group = 256, 512, 256, 128
+    dims = {"self_attn.q_proj": (hidden, hidden), "self_attn.k_proj": (hidden, kv), "self_attn.v_proj": (hidden, kv),
+            "self_attn.o_proj": (hidden, hidden), "mlp.gate_proj": (hidden, inter), "mlp.up_proj": (hidden, inter),
+            "mlp.down_proj": (inter, hidden)}
+    state, dense = {}, {}
+    for name, (k, n) in dims.items():
+        u = rng.integers(0, 16, size=(k, n))
+        uz = rng.integers(0, 16, size=(k // group, n))
+        s = rng.uniform(0.001, 0.02, size=(k // group, n)).astype(np.float32)
+        pre = f"model.layers.3.{name}"
+        if fmt == "gptq":
+            state[f"{pre}.qweight"], state[f"{pre}.qzeros"] = _pack_words(u.T.copy()).T.contiguous(), _pack_words(uz)
+            state[f"{pre}.scales"] = torch.from_numpy(s).half()
+            w = (u - (np.repeat(uz, group, 0) + 1)) * np.repeat(torch.from_numpy(s).half().float().numpy(), group, 0)
+        elif fmt == "awq":
+            state[f"{pre}.qweight"], state[f"{pre}.qzeros"] = _pack_words(u, AWQ_ORDER), _pack_words(uz, AWQ_ORDER)
+            state[f"{pre}.scales"] = torch.from_numpy(s).half()
+            w = (u - np.repeat(uz, group, 0)) * np.repeat(torch.from_numpy(s).half().float().numpy(), group, 0)
+        else:
+            q = (u - 8).astype(np.int8)
+            nib = (q.astype(np.int16) & 15).astype(np.uint8)
+            state[f"{pre}.weight"] = torch.from_numpy((nib[:, 0::2] | (nib[:, 1::2] << 4)).T.copy())
+            state[f"{pre}.weight_scale"] = torch.from_numpy(s.T.copy())
+            state[f"{pre}.input_quantizer._pre_quant_scale"] = torch.ones(k)
+            w = q * np.repeat(torch.from_numpy(s).half().float().numpy(), group, 0)
+        dense[name] = w
+
+    from oracle import woq_oracle as oracle
+
+    def dequant(t, prefix):
+        wq = oracle.signed_weights(t[f"{prefix}.weight"].view(torch.int8), t[f"{prefix}.weight"].shape[0],
+                                   t[f"{prefix}.weight"].shape[1] * 4, 4).float()
+        s_ = t[f"{prefix}.weights_scaling_factor"].float().repeat_interleave(group, 0)
+        z_ = t.get(f"{prefix}.zero")
+        return wq * s_ + (0 if z_ is None else z_.float().repeat_interleave(group, 0))
+
+    shards = [ck.convert_llama_layer(fmt, state, 3, mapping=Mapping(tp_size, r, tp_size=tp_size), group_size=group)
+              for r in range(tp_size)]
+    p = "transformer.layers.3"
+    expect_keys = {f"{p}.{m}.{t}" for m in ("attention.qkv", "attention.dense", "mlp.fc", "mlp.gate", "mlp.proj")
+                   for t in (("weight", "weights_scaling_factor") + (("zero",) if fmt != "modelopt_awq" else
+                                                                     ("prequant_scaling_factor",)))}
+    assert set(shards[0]) == expect_keys
+    tol = 2 ** -9 * 0.4  # zero-point products are rounded to fp16 once
+    # row-parallel: K chunks stack; column-parallel: N chunks concatenate
+    for tllm, hf, dim in (("attention.dense", "self_attn.o_proj", 0), ("mlp.proj", "mlp.down_proj", 0),
+                          ("mlp.fc", "mlp.gate_proj", 1), ("mlp.gate", "mlp.up_proj", 1)):
+        whole = torch.cat([dequant(sh, f"{p}.{tllm}") for sh in shards], dim=dim)
+        assert float((whole - torch.from_numpy(dense[hf]).float()).abs().max()) <= tol
+    # fused qkv: every rank holds [q chunk | k chunk | v chunk]
+    for r, sh in enumerate(shards):
+        w = dequant(sh, f"{p}.attention.qkv")
+        parts = [torch.from_numpy(dense[f"self_attn.{x}_proj"]).float().chunk(tp_size, dim=1)[r] for x in "qkv"]
+        assert float((w - torch.cat(parts, dim=1)).abs().max()) <= tol
+
+
 def test_bad_inputs():
     u, uz, s = _make()
     with pytest.raises(ValueError):

@@ -40,9 +40,43 @@ def test_split_and_shard_rules():
     assert torch.equal(tp.split(x, 2, 1, dim=0), x[2:]) and torch.equal(tp.split(x, 3, 0, dim=1), x[:, :2])
     with pytest.raises(ValueError):
         tp.split(x, 4, 0, dim=1)
-    q = torch.zeros(192, 128, dtype=torch.int8)
-    with pytest.raises(ValueError):  # 96-row K shard is not a multiple of the 64-wide k tile
-        tp.WeightOnlyRowLinear.from_quantized(Mapping(2, 0, tp_size=2), q, torch.ones(3, 128), bits=4, group_size=64)
+
+
+def test_feature_padding_like_the_reference():
+    """Features that do not split into whole 64-wide tiles / scale groups per rank are rounded up to a
+    multiple of max(64, group) * tp first (quantization/layers.py:719-726, 965-972 of the reference);
+    the padded layer gives the same result on zero-extended activations."""
+    assert tp.padded_features(192, 64, 2) == 256 and tp.padded_features(4096, 128, 8) == 4096
+    assert tp.padded_features(11008, 128, 8) == 11264 and tp.padded_features(100, 0, 4) == 256
+    g = torch.Generator().manual_seed(4)
+    K, N, G, M, world = 192, 160, 64, 3, 2
+    q = torch.randint(-8, 8, (K, N), dtype=torch.int8, generator=g)
+    scales = (torch.rand(K // G, N, generator=g) * 0.02 + 0.001).half()
+    zeros = (torch.rand(K // G, N, generator=g) * 0.2 - 0.1).half()
+    bias = torch.randn(N, generator=g).half()
+    x = torch.randn(M, K, generator=g).half()
+    full = oracle.kernel_rounding_ref(x, q, scales, zeros=zeros, bias=bias, group_size=G)
+    xp = torch.nn.functional.pad(x, (0, 256 - K))
+    # row-parallel: K 192 -> 256, 128 per rank; partial sums add up to the unpadded result
+    acc = torch.zeros(M, 256, dtype=torch.float32)
+    for r in range(world):
+        layer = tp.WeightOnlyRowLinear.from_quantized(Mapping(world, r, tp_size=world), q, scales, zeros, bias, bits=4,
+                                                      group_size=G, dtype=torch.float16)
+        assert (layer.in_features, layer.out_features, layer.k_local, layer.n_local, layer.n_valid) == (256, 256, 128, 256, N)
+        layer.matmul = _oracle_matmul
+        acc += layer(tp.split(xp, world, r, dim=1), all_reduce=False).float() - (bias_pad := torch.nn.functional.pad(
+            bias, (0, 256 - N))).float()
+    got = (acc + bias_pad.float())[:, :N]
+    assert float((got - full.float()).abs().max()) <= 2e-3 * float(full.float().abs().max())
+    # column-parallel: N 160 -> 256, 128 per rank; the valid columns of the gathered output match
+    outs = []
+    for r in range(world):
+        layer = tp.WeightOnlyColumnLinear.from_quantized(Mapping(world, r, tp_size=world), q, scales, zeros, bias, bits=4,
+                                                         group_size=G, dtype=torch.float16)
+        layer.matmul = _oracle_matmul
+        outs.append(layer(xp))
+    got = torch.cat(outs, dim=1)[:, :N]
+    assert float((got.float() - full.float()).abs().max()) <= 2e-3 * float(full.float().abs().max())
 
 
 def _oracle_matmul(layer, x, bias):
