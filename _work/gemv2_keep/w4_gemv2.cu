@@ -96,96 +96,6 @@ struct Args
     int weights_static; // weights / scales / zeros / act_scale were complete before the preceding kernel started
 };
 
-// Slow path of a wait: bounded polling; once any wait in the CTA timed out every later one returns
-// at once.
-__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag)
-{
-    for (uint32_t i = 0; i < kMaxWaitPolls; ++i)
-    {
-        uint32_t ok;
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n"
-            "}\n"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok)
-            return true;
-        if ((i & 1023u) == 1023u && *abort_flag)
-            return false;
-    }
-    *abort_flag = 1;
-    atomicExch(&g_device_status, kDeviceTimeout);
-    return false;
-}
-
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag)
-{
-    return wait_slow(bar, parity, abort_flag);
-}
-
-// Progress counters in shared memory. An mbarrier instruction holds the issuing warp for several
-// hundred cycles even when the phase is long complete (measured: ~500 cycles for try_wait, ~200 for
-// arrive), which at one tile per ~700 cycles would be most of a consumer warp's time. So only the
-// watcher warp waits on the mbarriers the bulk copies complete; it publishes the number of tiles
-// that have landed in a plain word, the consumer warps publish the tiles they have finished in one
-// word each, and everybody else polls those words with ordinary acquire loads.
-__device__ __forceinline__ void publish(uint32_t addr, uint32_t v)
-{
-    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t observe(uint32_t addr)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-
-// Waits until the counter at `addr` has reached `needed`. Bounded; returns false after a timeout
-// anywhere in the CTA.
-__device__ __noinline__ bool wait_count_slow(uint32_t addr, uint32_t needed, volatile int* abort_flag)
-{
-    for (uint32_t i = 0; i < kMaxSpinPolls; ++i)
-    {
-        if (int32_t(observe(addr) - needed) >= 0)
-            return true;
-        if ((i & 4095u) == 4095u && *abort_flag)
-            return false;
-    }
-    *abort_flag = 1;
-    atomicExch(&g_device_status, kDeviceTimeout);
-    return false;
-}
-
-__device__ __forceinline__ bool wait_count(uint32_t addr, uint32_t needed, volatile int* abort_flag)
-{
-    if (int32_t(observe(addr) - needed) >= 0)
-        return true;
-    return wait_count_slow(addr, needed, abort_flag);
-}
-
-// All sixteen consumer warps have finished at least `needed` tiles (four 16-byte acquire loads).
-__device__ __forceinline__ bool all_done(uint32_t addr, uint32_t needed)
-{
-    bool ok = true;
-#pragma unroll
-    for (int q = 0; q < kWarps / 4; ++q)
-    {
-        uint32_t a, b, c, d;
-        asm volatile("ld.acquire.cta.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-                     : "r"(addr + 16 * q)
-                     : "memory");
-        ok = ok && int32_t(a - needed) >= 0 && int32_t(b - needed) >= 0 && int32_t(c - needed) >= 0
-            && int32_t(d - needed) >= 0;
-    }
-    return ok;
-}
-
 // Shared-memory loads through 32-bit addresses with immediate offsets.
 template <int OFF>
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
@@ -193,6 +103,49 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr)
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
     return v;
+}
+
+// The B-fragment vectors of one chunk, fetched only by the lanes whose activation row exists: a lane
+// that does not load costs no shared-memory cycle (a quarter-warp without active lanes is skipped),
+// its registers keep whatever they held and are zeroed by the caller with an integer multiply.
+template <int VECS>
+__device__ __forceinline__ void lds_b_fragments(uint4 (&v)[VECS], uint32_t addr, uint32_t active)
+{
+    static_assert(VECS == 2 || VECS == 4, "two or four 16-byte vectors per chunk");
+    if (VECS == 4)
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.u32 p, %17, 0;\n"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%16];\n"
+            "@p ld.shared.v4.u32 {%4,%5,%6,%7}, [%16+16];\n"
+            "@p ld.shared.v4.u32 {%8,%9,%10,%11}, [%16+32];\n"
+            "@p ld.shared.v4.u32 {%12,%13,%14,%15}, [%16+48];\n"
+            "}\n"
+            : "=r"(v[0].x), "=r"(v[0].y), "=r"(v[0].z), "=r"(v[0].w), "=r"(v[1].x), "=r"(v[1].y), "=r"(v[1].z),
+            "=r"(v[1].w), "=r"(v[VECS - 2].x), "=r"(v[VECS - 2].y), "=r"(v[VECS - 2].z), "=r"(v[VECS - 2].w),
+            "=r"(v[VECS - 1].x), "=r"(v[VECS - 1].y), "=r"(v[VECS - 1].z), "=r"(v[VECS - 1].w)
+            : "r"(addr), "r"(active));
+    else
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.u32 p, %9, 0;\n"
+            "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%8];\n"
+            "@p ld.shared.v4.u32 {%4,%5,%6,%7}, [%8+16];\n"
+            "}\n"
+            : "=r"(v[0].x), "=r"(v[0].y), "=r"(v[0].z), "=r"(v[0].w), "=r"(v[1].x), "=r"(v[1].y), "=r"(v[1].z),
+            "=r"(v[1].w)
+            : "r"(addr), "r"(active));
+#pragma unroll
+    for (int i = 0; i < VECS; ++i)
+    {
+        // integer multiply by 0 / 1: runs on the FMA pipe, which this kernel leaves idle
+        v[i].x *= active;
+        v[i].y *= active;
+        v[i].z *= active;
+        v[i].w *= active;
+    }
 }
 
 template <int OFF>
@@ -271,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     uint8_t* const ring = smem;
     uint8_t* const act_sm = smem + a.off_act;
-    // (f, P, Q) table: 32 bytes per (unit, row pair): {f0, f1, P0, P1, Q0, Q1, -, -}.
+    // (f, P, Q) table: 24 bytes per (unit, row pair): {f0, f1, P0, P1, Q0, Q1}.
     float* const tab = reinterpret_cast<float*>(smem + a.off_tab);
     float* const red = reinterpret_cast<float*>(smem + a.off_red);
     // Synchronisation area: done[16] (tiles finished per consumer warp), landed, abort flag, then
@@ -333,21 +286,8 @@ __global__ void __launch_bounds__(kThreads, 2)
                 if (j >= a.num_slots)
                 {
                     // every consumer warp has finished the tile that used this slot before
-                    uint32_t const needed = uint32_t(j - a.num_slots + 1);
-                    uint32_t polls = 0;
-                    bool free_now = all_done(done0, needed);
-                    while (!free_now)
-                    {
-                        if ((++polls & 4095u) == 0 && (*abort_flag || polls >= kMaxSpinPolls))
-                            break;
-                        free_now = all_done(done0, needed);
-                    }
-                    if (!free_now)
-                    {
-                        *abort_flag = 1;
-                        atomicExch(&g_device_status, kDeviceTimeout);
+                    if (!wait_all_counts(done0, uint32_t(j - a.num_slots + 1), abort_flag))
                         break;
-                    }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
                 if (j >= a.depth && !wait_count(landed_addr, uint32_t(j - a.depth + 1), abort_flag))
@@ -390,9 +330,9 @@ __global__ void __launch_bounds__(kThreads, 2)
             uint32_t parity = 0;
             for (int j = 0; j < num_tiles; ++j)
             {
-                if (!wait_bar(smem_u32(&full_bar[slot]), parity, abort_flag))
+                if (!mbar_wait_or_abort(&full_bar[slot], parity, abort_flag))
                     break;
-                publish(landed_addr, uint32_t(j + 1));
+                publish_count(landed_addr, uint32_t(j + 1));
                 if (++slot == a.num_slots)
                 {
                     slot = 0;
@@ -420,14 +360,14 @@ __global__ void __launch_bounds__(kThreads, 2)
     // Scale group of this warp's unit inside the panel's box, then this thread's column(s).
     int const sgrp = a.group_shift >= 31 ? 0 : (warp * C::UK) >> a.group_shift;
     uint32_t sc0 = ring32 + C::TILE_BYTES + (sgrp * kBoxCols + colA) * 2;
-    // B fragments: activation row g, chunk t of every unit; rows that do not exist read a block of
-    // zeros (and never advance).
+    // B fragments: activation row g, chunk t of every unit; lanes whose row does not exist load
+    // nothing and hold zeros.
     bool const row_ok = g < a.m;
-    uint32_t act0 = row_ok ? smem_u32(act_sm) + g * a.act_stride + t * C::BLOCK_STRIDE : smem_u32(smem + a.off_zero);
-    int ustride = row_ok ? C::UNIT_STRIDE : 0;
+    uint32_t act0 = smem_u32(act_sm) + (row_ok ? g : 0) * a.act_stride + t * C::BLOCK_STRIDE;
+    uint32_t active = row_ok ? 1u : 0u;
     // (f, P, Q) entries of the activation rows 2t, 2t+1 behind this thread's accumulator columns.
-    uint32_t tab0 = smem_u32(tab) + (t < MT ? t : MT - 1) * 32;
-    int const tstride = MT * 32;
+    uint32_t tab0 = smem_u32(tab) + (t < MT ? t : MT - 1) * 24;
+    int const tstride = MT * 24;
     uint32_t const my_done = done0 + 4 * warp;
     // These per-thread addresses are used once per tile; keep them in registers (the compiler would
     // otherwise recompute them from the thread index inside the loop, some thirty instructions per tile).
@@ -435,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     keep_in_register(wB0);
     keep_in_register(sc0);
     keep_in_register(act0);
-    keep_in_register(ustride);
+    keep_in_register(active);
     keep_in_register(tab0);
 
     // ---- stage the activations: act * pre-quant scale (rounded to T) -> fp16, per (row, unit).
@@ -549,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                 {
                     float const sum_stored = lo_sum + hi_sum;            // sum of a'
                     float const sum_true = f * (lo_sum + 16.f * hi_sum); // sum of the activations themselves
-                    float* e = tab + (u * MT + (row >> 1)) * 8 + (row & 1);
+                    float* e = tab + (u * MT + (row >> 1)) * 6 + (row & 1);
                     e[0] = f;
                     e[2] = f * 1024.f * sum_stored + C::BIAS * sum_true;
                     e[4] = sum_true;
@@ -603,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, 2)
             uint4 const wb = BITS == 4 ? lds128<32>(wA0 + so) : lds128<0>(wB0 + so);
             uint32_t const ra[4] = {wa.x, wa.y, wa.z, wa.w};
             uint32_t const rb[4] = {wb.x, wb.y, wb.z, wb.w};
-            uint32_t const au = act0 + u * ustride;
+            uint32_t const au = act0 + u * C::UNIT_STRIDE;
             // scale / zero words of the thread's two columns and the unit's (f, P, Q) entries: fetched
             // up front so that their latency hides behind the nibble extraction
             uint32_t s_word, z_word = 0;
@@ -620,14 +560,15 @@ __global__ void __launch_bounds__(kThreads, 2)
                     z_word = lds16<kZeroBoxOff>(sc0 + so) | (lds16<kZeroBoxOff + 16>(sc0 + so) << 16);
             }
             uint32_t const ta = tab0 + u * tstride;
-            uint4 const fp = lds128<0>(ta); // f0, f1, P0, P1
-            uint2 q2 = make_uint2(0u, 0u);  // Q0, Q1
+            uint2 const f2 = lds64<0>(ta), p2 = lds64<8>(ta); // (f0, f1), (P0, P1)
+            uint2 q2 = make_uint2(0u, 0u);                     // (Q0, Q1)
             if (HAS_ZERO)
                 q2 = lds64<16>(ta);
             float S[2][4];
             if (BITS == 4)
             {
-                uint4 const bv[4] = {lds128<0>(au), lds128<16>(au), lds128<32>(au), lds128<48>(au)};
+                uint4 bv[4];
+                lds_b_fragments<4>(bv, au, active);
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj)
                 {
@@ -656,7 +597,8 @@ __global__ void __launch_bounds__(kThreads, 2)
             else
             {
                 constexpr uint32_t kMagic8 = 0x64646464u; // prmt source: 0x64 high bytes -> 1024 + byte
-                uint4 const bv[2] = {lds128<0>(au), lds128<16>(au)};
+                uint4 bv[2];
+                lds_b_fragments<2>(bv, au, active);
 #pragma unroll
                 for (int v = 0; v < 2; ++v)
                 {
@@ -680,8 +622,8 @@ __global__ void __launch_bounds__(kThreads, 2)
             P::unpack2(s_word, sA, sB);
             if (HAS_ZERO)
                 P::unpack2(z_word, zA, zB);
-            float const f0 = __uint_as_float(fp.x), f1 = __uint_as_float(fp.y);
-            float const p0 = __uint_as_float(fp.z), p1 = __uint_as_float(fp.w);
+            float const f0 = __uint_as_float(f2.x), f1 = __uint_as_float(f2.y);
+            float const p0 = __uint_as_float(p2.x), p1 = __uint_as_float(p2.y);
             acc[0] = fmaf(sA, fmaf(S[0][0] + S[1][0], f0, -p0), acc[0]);
             acc[1] = fmaf(sA, fmaf(S[0][1] + S[1][1], f1, -p1), acc[1]);
             acc[2] = fmaf(sB, fmaf(S[0][2] + S[1][2], f0, -p0), acc[2]);
@@ -697,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         __syncwarp();
         if (lane == 0)
-            publish(my_done, uint32_t(tile + 1));
+            publish_count(my_done, uint32_t(tile + 1));
         if (++s == a.num_slots)
             s = 0;
         if (++panel < num_panels)
@@ -770,7 +712,7 @@ static bool plan(Args& a, DeviceInfo const& dev, int grid, size_t* smem_bytes)
         a.act_stride += 16;
     int const MT = (a.m + 1) / 2;
     int const act_bytes = round_up(a.m * a.act_stride, 128);
-    int const fpq_bytes = round_up(units * MT * 32, 128);
+    int const fpq_bytes = round_up(units * MT * 24, 128);
     // Partial sums: all column groups of a CTA in one reduction when that stays small.
     int const cgs = (a.num_cgs + grid - 1) / grid;
     int const per_cg = kWarps * 16 * a.m * 4;

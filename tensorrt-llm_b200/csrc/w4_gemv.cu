@@ -791,19 +791,13 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
     if (dev.num_sms <= 0)
         return W4_ERR_CUDA;
     size_t const elt = 2;
-    // Passes of at most 8 rows: the 16-row variant of the kernel (two B fragments per weight
-    // fragment) measured slower than two 8-row passes on every shape tried, so it is not used.
+    // Passes of at most 8 rows. The 16-row variant of the kernel (two B fragments per weight
+    // fragment, MB = 2) has to split K into two panels to hold its activation fragments and reloads
+    // them for every pair of column groups: measured again at 24.9 us for config 2 at m = 16, the
+    // same as two 8-row passes (24.4 us), so it is not instantiated.
     for (int m0 = 0; m0 < p.m; m0 += 8)
     {
         int const rows = p.m - m0 < 8 ? p.m - m0 : 8;
-        // Activations small enough to stay in shared memory: the second form of the kernel.
-        if (gemv2::supports(p, rows, dev))
-        {
-            int const rc = gemv2::launch(p, m0, rows, dev, stream);
-            if (rc != W4_OK)
-                return rc;
-            continue;
-        }
         gemv::Args a{};
         a.weight = static_cast<uint8_t const*>(p.weight);
         a.act = static_cast<char const*>(p.act) + size_t(m0) * p.k * elt;

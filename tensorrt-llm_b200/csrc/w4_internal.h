@@ -23,14 +23,6 @@ DeviceInfo const& current_device_info();
 // Streaming decode kernel: handles any m by passes of at most 8 rows. Returns a W4Status.
 int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
 
-// Second form of the decode kernel (activations resident in shared memory as fp16): whether it
-// covers one pass of `rows` rows of the problem, and the launch of that pass (rows m0 .. m0+rows).
-namespace gemv2
-{
-bool supports(W4GemmParams const& p, int rows, DeviceInfo const& dev);
-int launch(W4GemmParams const& p, int m0, int rows, DeviceInfo const& dev, cudaStream_t stream);
-} // namespace gemv2
-
 // tcgen05 tensor-core kernel. Returns a W4Status.
 int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream);
 // Workspace: the minimum the kernel needs (scaled activation copy), and what also allows split-k.

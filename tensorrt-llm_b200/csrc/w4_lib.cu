@@ -1,6 +1,5 @@
 // Single translation unit of the device library: the kernels share one device-side status word
 // and are compiled together for sm_100a only.
-#include "w4_gemv2.cu"
 #include "w4_gemv.cu"
 #include "w4_gemm_tc.cu"
 #include "w4_api.cu"
