@@ -434,8 +434,8 @@ def run_ours(args):
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": gbs_rank, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs_rank / peaks["hbm_gbs"], "frac_of_8TBs": gbs_rank / 8000.0,
-                     "peak_source": peaks["source"], "kernel": "w4::gemv2::gemv2_kernel<bf16, 4, zero>",
-                     "traffic": captured_traffic("gemv2_c2_m1")},
+                     "peak_source": peaks["source"], "kernel": "w4::gemv::gemv_kernel<bf16, int4, MB=1, zero, act_scale, folded>",
+                     "traffic": captured_traffic("gemv_c2_m1")},
         "clocks": clocks.summary(),
         "parity_err_frac_of_max": parity,
     }

@@ -165,12 +165,15 @@ extern "C"
         (void) group_size;
         if (m <= 8)
             return W4_REGIME_GEMV; // one pass over the weights
-        // Cost model fitted to measurements on B200 (microseconds): the decode kernel makes one
-        // pass over the packed weights per 8 rows at ~2.45 TB/s plus ~4.5 us; the tensor-core kernel's
-        // estimate comes from its own per-step costs (148 SMs assumed: no device is queried here).
+        // Cost model fitted to measurements on B200 (microseconds): the decode kernel makes one pass
+        // over the packed weights per 8 rows, 4.2 us plus the weight bytes at 3.4 TB/s (config 2:
+        // 12.3 us per pass; 4096 x 4096 int4: 6.6 us); the tensor-core kernel's estimate comes from its
+        // own per-step costs. The SM count is the current device's (148 when no device is present).
+        w4::DeviceInfo const& dev = w4::current_device_info();
+        int const sms = dev.num_sms > 0 ? dev.num_sms : 148;
         double const weight_mb = double(n) * double(k) * weight_bits / 8.0 / 1.0e6;
-        double const gemv_us = double((m + 7) / 8) * (weight_mb / 2.45 + 4.5);
-        double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, 148);
+        double const gemv_us = double((m + 7) / 8) * (weight_mb / 3.4 + 4.2);
+        double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, sms);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;
     }
 
