@@ -340,6 +340,9 @@ def run_ours(args):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
+        # NCCL_DEBUG=VERSION makes NCCL print its version on stdout, ahead of the one JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -398,16 +401,26 @@ def run_ours(args):
     gbs_rank = set_bytes / (ms_step * 1e-3) / 1e9
     del graph
 
-    # ---- end to end through the public torch op (C++ registration): every step copies the
-    # activations from pinned host memory, calls the op, reads the result back and synchronises.
+    # ---- end to end with host buffers: every step takes the activations from pinned host memory and
+    # leaves the result in pinned host memory, synchronised. Through the C ABI's host entry point
+    # (w4_gemm_run_host: copy in, GEMM, copy out, synchronise in one call) and, for comparison, through
+    # the torch op with the copies made by torch around it.
     h_act = prob.act[:m].cpu().contiguous().pin_memory()
     h_out = torch.empty((m, C2["n"]), dtype=torch.bfloat16).pin_memory()
     d_act = torch.empty((m, C2["k"]), dtype=torch.bfloat16, device=device)
+    d_out = torch.empty((m, C2["n"]), dtype=torch.bfloat16, device=device)
     algo = pkg.ZERO | pkg.PRE_QUANT_SCALE
     op = torch.ops.trtllm.weight_only_groupwise_quant_gemm
     cur = torch.cuda.current_stream()
+    prepared = [pkg.ops.PreparedGemm(d_act, w, s, d_out, n=C2["n"], k=C2["k"], weight_bits=4, group_size=128, zeros=z,
+                                     act_scale=prob.ps, regime=pkg.W4_REGIME_GEMV, weights_static=True)
+                for (w, s, z) in prob.sets]
+    cur_handle = cur.cuda_stream
 
     def e2e_step(i):
+        prepared[i % len(prepared)].run_host(h_act, h_out, cur_handle)
+
+    def e2e_torch_step(i):
         w, s, z = prob.sets[i % len(prob.sets)]
         d_act.copy_(h_act, non_blocking=True)
         y = op(d_act, prob.ps, w, s, z, None, 1.0, algo, 128, True)
@@ -415,8 +428,14 @@ def run_ours(args):
         cur.synchronize()
 
     e2e_steps = min(args.steps, 2000)
+    h_out.zero_()
+    e2e_step(0)
+    parity["e2e_host_m1"] = prob.parity(h_out, m)
+    if parity["e2e_host_m1"] > 1e-2:
+        raise SystemExit(f"parity FAILED for the host entry point: {parity['e2e_host_m1']} of max|ref| > 1e-2")
     e2e_ms = max_over_ranks(time_steps(e2e_step, e2e_steps, max(args.warmup, 3), sync, barrier)) / e2e_steps
     e2e_gbs = set_bytes / (e2e_ms * 1e-3) / 1e9
+    e2e_torch_ms = max_over_ranks(time_steps(e2e_torch_step, e2e_steps, max(args.warmup, 3), sync, barrier)) / e2e_steps
 
     line = {
         "metric": METRIC, "value": gbs_rank * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -430,7 +449,10 @@ def run_ours(args):
                    "algorithmic_bytes_per_step": set_bytes},
         "e2e": {"value": e2e_gbs * world, "unit": "GB/s", "h2d_bytes_per_step": m * C2["k"] * 2,
                 "d2h_bytes_per_step": m * C2["n"] * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "api": "torch.ops.trtllm.weight_only_groupwise_quant_gemm (C++ registration)"},
+                "api": "w4_gemm_run_host (C ABI: pinned host activations in, pinned host result out, synchronised)",
+                "torch_op_ms_per_step": e2e_torch_ms,
+                "torch_op_api": "torch.ops.trtllm.weight_only_groupwise_quant_gemm (C++ registration) with "
+                                "torch copies from / to pinned host memory around it"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": gbs_rank, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs_rank / peaks["hbm_gbs"], "frac_of_8TBs": gbs_rank / 8000.0,

@@ -159,6 +159,16 @@ extern "C"
     /* Enqueues the GEMM on `stream` (a cudaStream_t; NULL = default stream). m == 0 is a no-op. */
     int w4_gemm_launch(const W4GemmParams* p, void* stream);
 
+    /* w4_gemm_launch for a caller whose activations and result live in host memory (pinned, for the
+     * copies to be asynchronous): one call in place of copy-in, enqueue, copy-out and synchronise. No
+     * counterpart in the reference, whose plugins only ever see device tensors.
+     * Enqueues on `stream`: host_act [m, k] -> p->act, the GEMM, p->out -> host_out [m, n]; returns
+     * once the stream has drained, so host_out is valid on return. p->act and p->out are device buffers
+     * of the caller, used as staging (their contents afterwards are unspecified: blocks of up to 256 KiB
+     * in mapped pinned memory are read and written by kernels directly, without the copy engine);
+     * everything else in p as for w4_gemm_launch. Allocates nothing. */
+    int w4_gemm_run_host(const W4GemmParams* p, const void* host_act, void* host_out, void* stream);
+
     /* Bytes of scratch w4_gemm_launch needs for this problem in the regime it would pick. */
     size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
         int has_act_scale, int regime);
@@ -234,12 +244,13 @@ extern "C"
 #define W4_MAX_RANKS 8
 #define W4_ONESHOT_MAX_BYTES (1u << 20) /* largest message the one-shot form takes */
 #define W4_ALLREDUCE_MAX_CTAS 128       /* chunks a message (one-shot) or a slice (two-shot) is cut into */
+#define W4_ALLREDUCE_LL_MAX_BYTES (4u << 20) /* up to here data travels as flagged packets (no fences) */
 
     enum
     {
         W4_ALLREDUCE_AUTO = 0,     /* by message size, the reference's rule (allreducePlugin.cpp:258-283) */
         W4_ALLREDUCE_ONE_SHOT = 1, /* push the whole partial to every peer, reduce locally */
-        W4_ALLREDUCE_TWO_SHOT = 2  /* push slices to their owners, reduce, pull the reduced slices */
+        W4_ALLREDUCE_TWO_SHOT = 2  /* push slices to their owners, reduce, hand the reduced slices round */
     };
 
     /*

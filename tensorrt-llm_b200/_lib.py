@@ -25,7 +25,7 @@ EXPORTS = (
     "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
     "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce", "w4_allreduce_emulated",
     "w4_allreduce_workspace_bytes",
-    "w4_gemm_workspace_bytes_max",
+    "w4_gemm_workspace_bytes_max", "w4_gemm_run_host",
 )
 
 
@@ -46,6 +46,7 @@ W4_GEMM_WEIGHTS_STATIC = 1
 W4_MAX_RANKS = 8
 W4_ONESHOT_MAX_BYTES = 1 << 20
 W4_ALLREDUCE_MAX_CTAS = 128
+W4_ALLREDUCE_LL_MAX_BYTES = 4 << 20
 W4_ERR_DEVICE_TIMEOUT = -10
 W4_ALLREDUCE_AUTO, W4_ALLREDUCE_ONE_SHOT, W4_ALLREDUCE_TWO_SHOT = 0, 1, 2
 
@@ -81,6 +82,7 @@ def lib() -> ctypes.CDLL:
         l.w4_gemm_validate.argtypes = [ctypes.POINTER(W4GemmParams)]
         l.w4_gemm_launch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
         l.w4_gemm_launch_static_scratch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
+        l.w4_gemm_run_host.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         l.w4_gemm_static_scratch_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 8

@@ -6,28 +6,35 @@
 // allreducePlugin.cpp:258-283), which the reference never applies to this path. Plain peer loads
 // and stores only: no multicast objects, no cluster multicast.
 //
-// Every rank owns a workspace block that all ranks have mapped: a control area, two sets of arrival
-// flags, an inbox and (two-shot) a buffer of reduced values, each in two copies used by alternate
-// calls. One kernel per call and rank:
+// Every rank owns a workspace block that all ranks have mapped; every area below exists in two copies
+// used by alternate calls. One kernel per call and rank. Three protocols:
 //
-//   one-shot (latency-bound sizes): CTA c PUSHES chunk c of the local partial sums into the inbox of
-//     every peer (one NVLink traversal), then raises flag (sender, c) there; it waits for the same
-//     chunk from every peer in its own inbox (local polling, local loads) and adds the chunks in rank
-//     order in fp32, so all ranks hold bit-identical results.
-//   two-shot (bandwidth-bound sizes): the message is cut into one slice per rank. Phase 1: every rank
-//     pushes slice j of its partial sums to rank j. Phase 2: rank j adds the world copies of its slice
-//     (rank order, fp32, + bias), writes the rounded result to its `reduced` buffer and to its own
-//     output, and raises flag2 at every peer. Phase 3: every rank pulls the other slices from their
-//     owners. Each rank sends and receives about 2 * bytes instead of (world - 1) * bytes.
+//   Messages up to W4_ALLREDUCE_LL_MAX_BYTES travel as flagged packets: a 16-byte packet is
+//   {data, call number, data, call number}, so a receiver that polls the packet sees data and flag
+//   arrive together (each 8-byte half is written atomically). No fence, no separate flag, no barrier:
+//   the latency of a step is one NVLink traversal. Twice the bytes cross the link, which does not
+//   matter while latency dominates.
+//     one-shot: every thread pushes its vectors of the local partial sums into the inbox of every peer,
+//       then polls its own inbox for the same vectors of every peer and adds them in rank order in
+//       fp32, so all ranks hold bit-identical results.
+//     two-shot: the message is cut into one slice per rank. Rank j receives slice j from everybody,
+//       adds the world copies (rank order, fp32, + bias), writes its own output and pushes the rounded
+//       result to every peer's second inbox, where the peers poll for it. Each rank sends 2 * bytes
+//       instead of (world - 1) * bytes.
+//   Larger messages (bandwidth-bound) use the two-shot scheme with plain data and per-chunk arrival
+//   flags: push slices (system fence, release store of the call number into flag (sender, chunk) at
+//   the owner), reduce, publish in the owner's `reduced` buffer (second flag set), pull. These use
+//   areas of their own, so a packet poll can never meet plain data.
 //
 // Call numbers live in DEVICE memory (control word 0), not in a launch argument: every CTA reads the
 // number at start, the last CTA to finish advances it. A captured CUDA graph can therefore be replayed
-// any number of times, and the inbox / flag copy a call uses follows from the number's parity. Why two
-// copies are enough: a rank can only start call e + 2 after every peer has taken part in call e + 1,
-// which a peer does after its call e (and all its reads of copy e & 1) has finished.
+// any number of times, and the copy a call uses follows from the number's parity. Why two copies are
+// enough: a rank can only start call e + 2 after every peer has taken part in call e + 1, which a peer
+// does after its call e (and all its reads of copy e & 1) has finished. A packet left from an earlier
+// call carries an older number and is never taken for a new one (numbers repeat after 2^32 calls).
 //
-// Nobody waits before having pushed everything it owes, and a CTA only ever waits for peers, never for
-// another CTA of its own launch; grids are at most kMaxCtas <= SM count, so all CTAs are resident.
+// Nobody waits before having pushed everything it owes, and a thread only ever waits for peers, never
+// for another CTA of its own launch; grids are at most kMaxCtas <= SM count, so all CTAs are resident.
 // Waits are bounded in time: when one expires the kernel records W4_ERR_DEVICE_TIMEOUT in the device
 // status word, skips the rest and returns (a peer that never arrives must not hang this GPU); `out` is
 // then undefined and the workspace must be cleared on all ranks before it is used again.
@@ -41,16 +48,28 @@ namespace ar
 
 constexpr int kMaxRanks = W4_MAX_RANKS;
 constexpr int kThreads = 512;
-constexpr int kMaxCtas = W4_ALLREDUCE_MAX_CTAS; // chunks per message (one-shot) or per slice (two-shot)
+constexpr int kMaxCtas = W4_ALLREDUCE_MAX_CTAS; // chunks per message or slice
 constexpr size_t kCtrlBytes = 256;
 constexpr size_t kFlagBytes = size_t(2) * kMaxRanks * kMaxCtas * sizeof(uint32_t);
 constexpr size_t kHeaderBytes = kCtrlBytes + 2 * kFlagBytes; // control, flags, flags2
+constexpr size_t kOneShotMax = W4_ONESHOT_MAX_BYTES;
+constexpr size_t kPacketMax = W4_ALLREDUCE_LL_MAX_BYTES;
 
+enum
+{
+    kOneShotPackets = 0,
+    kTwoShotPackets = 1,
+    kTwoShotFlags = 2
+};
+
+// One copy of the data areas: [packets A: world slots][packets B: world slots][plain inbox: world
+// slots][reduced]. The last two are empty when no message can exceed W4_ALLREDUCE_LL_MAX_BYTES.
 struct Layout
 {
-    size_t inbox_bytes;   // one copy of the inbox: world sender slots
-    size_t slot_bytes;    // one sender's slot inside the inbox
-    size_t reduced_bytes; // one copy of the reduced-slice buffer
+    size_t pkt_slot;     // one sender's slot in either packet inbox
+    size_t plain_slot;   // one sender's slot in the plain inbox
+    size_t reduced;      // reduced-slice buffer
+    size_t copy_bytes;   // all areas of one copy
     size_t total;
 };
 
@@ -59,17 +78,19 @@ __host__ __device__ inline size_t align256(size_t v)
     return (v + 255) & ~size_t(255);
 }
 
-// Workspace for messages up to max_bytes: a sender slot holds a whole one-shot message (up to
-// W4_ONESHOT_MAX_BYTES) or one slice of a two-shot message, whichever is larger.
 __host__ __device__ inline Layout layout_for(size_t max_bytes, int world)
 {
     Layout l;
-    size_t const one = max_bytes < size_t(W4_ONESHOT_MAX_BYTES) ? max_bytes : size_t(W4_ONESHOT_MAX_BYTES);
+    size_t const one = max_bytes < kOneShotMax ? max_bytes : kOneShotMax;     // whole message per sender
+    size_t const pk = max_bytes < kPacketMax ? max_bytes : kPacketMax;
+    size_t const pk_slice = (pk + world - 1) / world + 16;                    // one slice per sender
+    l.pkt_slot = align256(2 * (one > pk_slice ? one : pk_slice));            // packets double the bytes
+    bool const plain = max_bytes > kPacketMax;
     size_t const slice = (max_bytes + world - 1) / world + 16;
-    l.slot_bytes = align256(one > slice ? one : slice);
-    l.inbox_bytes = l.slot_bytes * world;
-    l.reduced_bytes = align256(slice);
-    l.total = kHeaderBytes + 2 * l.inbox_bytes + 2 * l.reduced_bytes;
+    l.plain_slot = plain ? align256(slice) : 0;
+    l.reduced = plain ? align256(slice) : 0;
+    l.copy_bytes = 2 * world * l.pkt_slot + world * l.plain_slot + l.reduced;
+    l.total = kHeaderBytes + 2 * l.copy_bytes;
     return l;
 }
 
@@ -90,8 +111,8 @@ struct Batch
     int ranks_in_launch;
     int ctas_per_rank;
     int world;
-    int two_shot;
-    size_t slot_bytes, inbox_bytes, reduced_bytes;
+    int protocol;
+    size_t pkt_slot, plain_slot, copy_bytes;
     unsigned long long timeout_ns;
 };
 
@@ -114,7 +135,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(uint32_t const* p)
     return v;
 }
 
-// Data that another GPU writes (inbox) or owns (reduced) is accessed around L1.
+// Data that another GPU writes (inboxes) or owns (reduced) is accessed around L1.
 __device__ __forceinline__ uint4 ld_sys(void const* p)
 {
     uint4 v;
@@ -129,6 +150,90 @@ __device__ __forceinline__ void st_sys(void* p, uint4 v)
 {
     asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
+}
+
+// One 16-byte vector of data as two flagged packets at dst[0], dst[1].
+__device__ __forceinline__ void put_packets(uint4* dst, uint4 v, uint32_t epoch)
+{
+    st_sys(dst, make_uint4(v.x, epoch, v.y, epoch));
+    st_sys(dst + 1, make_uint4(v.z, epoch, v.w, epoch));
+}
+
+// Polls the packet pairs at inbox + r * slot + 32 * vec for every rank r in `mask` until all carry
+// `epoch`; v[r] receives the data. False when the time limit expired (here or in another thread).
+__device__ __forceinline__ bool get_packets(uint4 (&v)[kMaxRanks], uint8_t const* inbox, size_t slot, size_t vec,
+    uint32_t mask, uint32_t epoch, unsigned long long timeout_ns, volatile int* failed)
+{
+    unsigned long long t0 = 0;
+    for (uint32_t polls = 1;; ++polls)
+    {
+        uint4 p[kMaxRanks][2];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (mask >> r & 1u)
+            {
+                uint4 const* src = reinterpret_cast<uint4 const*>(inbox + size_t(r) * slot) + 2 * vec;
+                p[r][0] = ld_sys(src);
+                p[r][1] = ld_sys(src + 1);
+            }
+        bool ready = true;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (mask >> r & 1u)
+                ready = ready && p[r][0].y == epoch && p[r][0].w == epoch && p[r][1].y == epoch && p[r][1].w == epoch;
+        if (ready)
+        {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (mask >> r & 1u)
+                    v[r] = make_uint4(p[r][0].x, p[r][0].z, p[r][1].x, p[r][1].z);
+            return true;
+        }
+        if ((polls & 15u) == 0)
+        {
+            if (*failed)
+                return false;
+            unsigned long long const now = global_timer_ns();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > timeout_ns)
+            {
+                *failed = 1;
+                atomicExch(&g_device_status, kDeviceTimeout);
+                return false;
+            }
+        }
+    }
+}
+
+// dst[i] = src[i] for i in [v0, v1), four 16-byte vectors in flight per thread (NVLink needs about a
+// megabyte in flight per GPU to run at full rate). PEER_SRC: the source is another GPU's memory.
+template <bool PEER_SRC>
+__device__ __forceinline__ void copy_vectors(uint4* dst, uint4 const* src, size_t v0, size_t v1)
+{
+    size_t i = v0 + threadIdx.x;
+    for (; i + 3 * kThreads < v1; i += 4 * kThreads)
+    {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            v[u] = PEER_SRC ? ld_sys(src + i + u * kThreads) : src[i + u * kThreads];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+        {
+            if (PEER_SRC)
+                dst[i + u * kThreads] = v[u];
+            else
+                st_sys(dst + i + u * kThreads, v[u]);
+        }
+    }
+    for (; i < v1; i += kThreads)
+    {
+        if (PEER_SRC)
+            dst[i] = ld_sys(src + i);
+        else
+            st_sys(dst + i, src[i]);
+    }
 }
 
 template <typename T>
@@ -155,6 +260,20 @@ __device__ __forceinline__ uint4 pack8(float const (&acc)[8])
     o.z = uint32_t(P::from_float(acc[4])) | (uint32_t(P::from_float(acc[5])) << 16);
     o.w = uint32_t(P::from_float(acc[6])) | (uint32_t(P::from_float(acc[7])) << 16);
     return o;
+}
+
+// Sum of v[0..world) in rank order (+ bias vector), rounded to T.
+template <typename T>
+__device__ __forceinline__ uint4 sum_ranks(uint4 const (&v)[kMaxRanks], int world, uint4 const* bias_vec)
+{
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+        if (r < world)
+            add8<T>(acc, v[r]);
+    if (bias_vec)
+        add8<T>(acc, __ldg(bias_vec));
+    return pack8<T>(acc);
 }
 
 // Waits (threads 0..world-1, one flag word each) until every peer's flag for this chunk has reached
@@ -202,69 +321,107 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
 
     auto flags_of = [&](uint8_t* ws, int set) // set 0: arrival flags, set 1: "reduced slice published"
     { return reinterpret_cast<uint32_t*>(ws + kCtrlBytes + size_t(set) * kFlagBytes) + size_t(h) * kMaxRanks * kMaxCtas; };
-    auto inbox_of = [&](uint8_t* ws, int sender)
-    { return ws + kHeaderBytes + size_t(h) * b.inbox_bytes + size_t(sender) * b.slot_bytes; };
-    auto reduced_of = [&](uint8_t* ws) { return ws + kHeaderBytes + 2 * b.inbox_bytes + size_t(h) * b.reduced_bytes; };
+    auto copy_of = [&](uint8_t* ws) { return ws + kHeaderBytes + size_t(h) * b.copy_bytes; };
+    auto packets_of = [&](uint8_t* ws, int inbox) { return copy_of(ws) + size_t(inbox) * world * b.pkt_slot; };
+    auto plain_of = [&](uint8_t* ws, int sender)
+    { return copy_of(ws) + size_t(2) * world * b.pkt_slot + size_t(sender) * b.plain_slot; };
+    auto reduced_of = [&](uint8_t* ws) { return copy_of(ws) + size_t(2) * world * b.pkt_slot + size_t(world) * b.plain_slot; };
 
     size_t const V = a.count / 8; // 16-byte vectors in the message
     int const n_vec = a.n / 8;
     uint4 const* partial = static_cast<uint4 const*>(a.partial);
+    uint4 const* bias = static_cast<uint4 const*>(a.bias);
     uint4* out = static_cast<uint4*>(a.out);
-    bool ok = true;
+    uint32_t const peers = ((1u << world) - 1u) & ~(1u << rank);
+    // slice j = vectors [V j / world, V (j+1) / world)
+    auto slice_begin = [&](int j) { return V * size_t(j) / world; };
 
-    if (!b.two_shot)
+    if (b.protocol == kOneShotPackets)
     {
-        // ---- push chunk c to every peer's inbox, slot `rank`
         size_t const v0 = V * size_t(c) / C, v1 = V * size_t(c + 1) / C;
         for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
         {
             uint4 const v = partial[i];
 #pragma unroll
             for (int p = 0; p < kMaxRanks; ++p)
-                if (p < world && p != rank)
-                    st_sys(reinterpret_cast<uint4*>(inbox_of(a.ws[p], rank)) + i, v);
+                if (peers >> p & 1u)
+                    put_packets(reinterpret_cast<uint4*>(packets_of(a.ws[p], 0) + size_t(rank) * b.pkt_slot) + 2 * i, v, epoch);
         }
-        __syncthreads();
-        if (int(threadIdx.x) < world && int(threadIdx.x) != rank)
+        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
         {
-            __threadfence_system();
-            st_release_sys(flags_of(a.ws[threadIdx.x], 0) + size_t(rank) * kMaxCtas + c, epoch);
+            uint4 v[kMaxRanks];
+            if (!get_packets(v, packets_of(mine, 0), b.pkt_slot, i, peers, epoch, b.timeout_ns, &failed))
+                break;
+            v[rank] = partial[i];
+            out[i] = sum_ranks<T>(v, world, bias ? bias + (i % n_vec) : nullptr);
         }
-        // ---- wait for the peers' chunk c, add in rank order
-        ok = wait_peers(flags_of(mine, 0), world, rank, c, epoch, b.timeout_ns, &failed);
-        if (ok)
+    }
+    else if (b.protocol == kTwoShotPackets)
+    {
+        // Every slice is cut into the same C chunks of vector indices (slices differ by at most one
+        // vector in length; the index range is that of the longest).
+        size_t const max_len = (V + world - 1) / world;
+        size_t const v0 = max_len * size_t(c) / C, v1 = max_len * size_t(c + 1) / C;
+        size_t const s0 = slice_begin(rank), len = slice_begin(rank + 1) - s0;
+        // ---- vectors of slice j go to its owner j, inbox A, slot `rank`
+        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
         {
-            for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+#pragma unroll
+            for (int dj = 1; dj < kMaxRanks; ++dj)
             {
-                uint4 v[kMaxRanks];
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world)
-                        v[r] = r == rank ? partial[i] : ld_sys(reinterpret_cast<uint4 const*>(inbox_of(mine, r)) + i);
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world)
-                        add8<T>(acc, v[r]);
-                if (a.bias)
-                    add8<T>(acc, __ldg(static_cast<uint4 const*>(a.bias) + (i % n_vec)));
-                out[i] = pack8<T>(acc);
+                int const j = (rank + dj) % world; // start with the next rank: spreads the traffic
+                if (dj < world)
+                {
+                    size_t const t0 = slice_begin(j), tl = slice_begin(j + 1) - t0;
+                    if (i < tl)
+                        put_packets(reinterpret_cast<uint4*>(packets_of(a.ws[j], 0) + size_t(rank) * b.pkt_slot) + 2 * i,
+                            partial[t0 + i], epoch);
+                }
             }
+        }
+        // ---- reduce the own slice, write it out and send it to every peer's inbox B, slot `rank`
+        bool ok = true;
+        for (size_t i = v0 + threadIdx.x; i < v1 && i < len; i += kThreads)
+        {
+            uint4 v[kMaxRanks];
+            ok = get_packets(v, packets_of(mine, 0), b.pkt_slot, i, peers, epoch, b.timeout_ns, &failed);
+            if (!ok)
+                break;
+            v[rank] = partial[s0 + i];
+            uint4 const o = sum_ranks<T>(v, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
+            out[s0 + i] = o;
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; ++p)
+                if (peers >> p & 1u)
+                    put_packets(reinterpret_cast<uint4*>(packets_of(a.ws[p], 1) + size_t(rank) * b.pkt_slot) + 2 * i, o, epoch);
+        }
+        // ---- collect the other slices from inbox B
+        for (size_t i = v0 + threadIdx.x; ok && i < v1; i += kThreads)
+        {
+            uint32_t mask = 0;
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j)
+                if ((peers >> j & 1u) && i < slice_begin(j + 1) - slice_begin(j))
+                    mask |= 1u << j;
+            uint4 v[kMaxRanks];
+            if (!get_packets(v, packets_of(mine, 1), b.pkt_slot, i, mask, epoch, b.timeout_ns, &failed))
+                break;
+#pragma unroll
+            for (int j = 0; j < kMaxRanks; ++j)
+                if (mask >> j & 1u)
+                    out[slice_begin(j) + i] = v[j];
         }
     }
     else
     {
-        // slice j = vectors [V j / world, V (j+1) / world); chunk c of a slice likewise
-        auto slice_begin = [&](int j) { return V * size_t(j) / world; };
+        bool ok = true;
         // ---- phase 1: push chunk c of slice j to its owner j, slot `rank`, at the slice-relative offset
         for (int dj = 1; dj < world; ++dj)
         {
-            int const j = (rank + dj) % world; // start with the next rank: spreads the traffic
+            int const j = (rank + dj) % world;
             size_t const s0 = slice_begin(j), len = slice_begin(j + 1) - s0;
             size_t const v0 = len * size_t(c) / C, v1 = len * size_t(c + 1) / C;
-            uint4* dst = reinterpret_cast<uint4*>(inbox_of(a.ws[j], rank));
-            for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
-                st_sys(dst + i, partial[s0 + i]);
+            copy_vectors<false>(reinterpret_cast<uint4*>(plain_of(a.ws[j], rank)), partial + s0, v0, v1);
         }
         __syncthreads();
         if (int(threadIdx.x) < world && int(threadIdx.x) != rank)
@@ -285,15 +442,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
 #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r)
                     if (r < world)
-                        v[r] = r == rank ? partial[s0 + i] : ld_sys(reinterpret_cast<uint4 const*>(inbox_of(mine, r)) + i);
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world)
-                        add8<T>(acc, v[r]);
-                if (a.bias)
-                    add8<T>(acc, __ldg(static_cast<uint4 const*>(a.bias) + ((s0 + i) % n_vec)));
-                uint4 const o = pack8<T>(acc);
+                        v[r] = r == rank ? partial[s0 + i] : ld_sys(reinterpret_cast<uint4 const*>(plain_of(mine, r)) + i);
+                uint4 const o = sum_ranks<T>(v, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
                 st_sys(red + i, o);
                 out[s0 + i] = o;
             }
@@ -314,9 +464,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
                 int const j = (rank + dj) % world;
                 size_t const t0 = slice_begin(j), tl = slice_begin(j + 1) - t0;
                 size_t const w0 = tl * size_t(c) / C, w1 = tl * size_t(c + 1) / C;
-                uint4 const* src = reinterpret_cast<uint4 const*>(reduced_of(a.ws[j]));
-                for (size_t i = w0 + threadIdx.x; i < w1; i += kThreads)
-                    out[t0 + i] = ld_sys(src + i);
+                copy_vectors<true>(out + t0, reinterpret_cast<uint4 const*>(reduced_of(a.ws[j])), w0, w1);
             }
         }
     }
@@ -383,13 +531,13 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
     Batch b{};
     b.world = p0.world;
     b.ranks_in_launch = ranks_in_launch;
-    b.two_shot = pick_two_shot(p0.mode, bytes, p0.world);
-    if (!b.two_shot && bytes > size_t(W4_ONESHOT_MAX_BYTES))
+    bool const two_shot = pick_two_shot(p0.mode, bytes, p0.world) != 0;
+    if (!two_shot && bytes > kOneShotMax)
         return W4_ERR_UNSUPPORTED; // a one-shot message must fit one sender slot
+    b.protocol = bytes > kPacketMax ? kTwoShotFlags : (two_shot ? kTwoShotPackets : kOneShotPackets);
     // The workspace was sized for some largest message: recover the layout from its size.
     size_t const body = p0.workspace_bytes > kHeaderBytes ? p0.workspace_bytes - kHeaderBytes : 0;
-    // total - header = 2 * world * slot + 2 * reduced; the caller passes what
-    // w4_allreduce_workspace_bytes(max_bytes, world) returned, so invert by search over max_bytes' two regimes
+    // The caller passes what w4_allreduce_workspace_bytes(max_bytes, world) returned.
     Layout l{};
     {
         // capacity is monotone in max_bytes: find the largest max_bytes whose layout fits (binary search)
@@ -406,19 +554,20 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
             return W4_ERR_WORKSPACE;
         l = layout_for(lo, p0.world);
     }
-    b.slot_bytes = l.slot_bytes;
-    b.inbox_bytes = l.inbox_bytes;
-    b.reduced_bytes = l.reduced_bytes;
+    b.pkt_slot = l.pkt_slot;
+    b.plain_slot = l.plain_slot;
+    b.copy_bytes = l.copy_bytes;
     b.timeout_ns = p0.timeout_ms > 0 ? (unsigned long long) (p0.timeout_ms) * 1000000ull : 2000000000ull;
 
     w4::DeviceInfo const& dev = w4::current_device_info();
     if (dev.num_sms <= 0)
         return W4_ERR_CUDA;
-    // Chunks: at least 512 vectors (8 KB) each, at most kMaxCtas; all ranks derive the same number
-    // from the message size alone. Several ranks in one launch (single-GPU emulation) must all be
-    // resident at once, so the number is capped by the SMs available per rank.
-    size_t const unit = b.two_shot ? (p0.count / 8) / p0.world : p0.count / 8;
-    int ctas = int(unit / 512);
+    // Chunks: about 512 vectors (8 KB) each or more, at most kMaxCtas; all ranks derive the same
+    // number from the message size alone. Several ranks in one launch (single-GPU emulation) must all
+    // be resident at once, so the number is capped by the SMs available per rank.
+    size_t const vecs = p0.count / 8;
+    size_t const unit = b.protocol == kOneShotPackets ? vecs : (vecs + p0.world - 1) / p0.world;
+    int ctas = int(b.protocol == kTwoShotFlags ? unit / 512 : (unit + 511) / 512);
     ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
     if (ctas > dev.num_sms / ranks_in_launch)
         ctas = dev.num_sms / ranks_in_launch;

@@ -1,5 +1,5 @@
 // The C ABI declared in include/w4_gemm.h: argument validation, the M-based regime choice and
-// dispatch into the two kernel families. Nothing here allocates or synchronises.
+// dispatch into the two kernel families. Nothing here allocates; only w4_gemm_run_host synchronises.
 #include <mutex>
 
 #include "w4_common.cuh"
@@ -76,10 +76,36 @@ int launch_pre_quant_scale(void* out, void const* act, void const* scale, int m,
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
+// Stages a small activation block from mapped pinned host memory into device memory: the loads cross
+// PCIe, the kernel that follows on the stream may start at once (it waits for this one before it
+// touches the activations) and fetch its weights meanwhile. Takes the place of a copy-engine transfer,
+// whose fixed cost is several microseconds.
+__global__ void stage_in_kernel(uint4* dst, uint4 const* src, size_t vecs)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    size_t const stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs; i += stride)
+        dst[i] = src[i];
+}
+
 } // namespace w4
 
 namespace
 {
+
+// Device-visible address of a host pointer when it is pinned, mapped and 16-byte aligned, else null.
+void* mapped_device_pointer(void const* host)
+{
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, host) != cudaSuccess)
+    {
+        (void) cudaGetLastError();
+        return nullptr;
+    }
+    if (at.type != cudaMemoryTypeHost || !at.devicePointer || (reinterpret_cast<uintptr_t>(at.devicePointer) & 15u))
+        return nullptr;
+    return at.devicePointer;
+}
 
 bool aligned16(void const* p)
 {
@@ -222,6 +248,48 @@ extern "C"
         if (resolve_regime(*p) == W4_REGIME_GEMV)
             return w4::launch_gemv(*p, s);
         return w4::launch_gemm_tc(*p, s);
+    }
+
+    int w4_gemm_run_host(const W4GemmParams* p, const void* host_act, void* host_out, void* stream)
+    {
+        int const rc = w4_gemm_validate(p);
+        if (rc != W4_OK)
+            return rc;
+        if (p->m == 0)
+            return W4_OK;
+        if (!host_act || !host_out)
+            return W4_ERR_NULL_POINTER;
+        cudaStream_t const s = static_cast<cudaStream_t>(stream);
+        size_t const elt = 2;
+        size_t const in_bytes = size_t(p->m) * p->k * elt, out_bytes = size_t(p->m) * p->n * elt;
+        // Decode-sized blocks in mapped pinned memory skip the copy engine in both directions: a small
+        // kernel loads the activations across PCIe and the GEMM stores its result straight into the
+        // host buffer. Anything else (pageable or unaligned host memory, large blocks) is copied.
+        constexpr size_t kDirectMax = 256 * 1024;
+        void* const in_dev = in_bytes <= kDirectMax ? mapped_device_pointer(host_act) : nullptr;
+        void* const out_dev = out_bytes <= kDirectMax ? mapped_device_pointer(host_out) : nullptr;
+        if (in_dev)
+        {
+            size_t const vecs = in_bytes / 16; // k % 64 == 0: whole vectors
+            unsigned const blocks = unsigned((vecs + 255) / 256 < 64 ? (vecs + 255) / 256 : 64);
+            w4::stage_in_kernel<<<blocks, 256, 0, s>>>(
+                static_cast<uint4*>(const_cast<void*>(p->act)), static_cast<uint4 const*>(in_dev), vecs);
+            if (cudaGetLastError() != cudaSuccess)
+                return W4_ERR_CUDA;
+        }
+        else if (cudaMemcpyAsync(const_cast<void*>(p->act), host_act, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return W4_ERR_CUDA;
+        // The activations were just written by the work in front: an ordinary dependency, which the
+        // kernels honour; the weights keep whatever the caller declared in `flags`.
+        W4GemmParams q = *p;
+        if (out_dev)
+            q.out = out_dev;
+        int const lrc = resolve_regime(q) == W4_REGIME_GEMV ? w4::launch_gemv(q, s) : w4::launch_gemm_tc(q, s);
+        if (lrc != W4_OK)
+            return lrc;
+        if (!out_dev && cudaMemcpyAsync(host_out, p->out, out_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+            return W4_ERR_CUDA;
+        return cudaStreamSynchronize(s) == cudaSuccess ? W4_OK : W4_ERR_CUDA;
     }
 
     int w4_gemm_device_status(void)

@@ -75,7 +75,12 @@ struct Args
 
 struct __align__(16) Barriers
 {
-    uint64_t full[kMaxStages];    // TMA landed (tx bytes); watched by the conversion warps only
+    // TMA landed (tx bytes), one barrier per (conversion group, stage): the copy of a k step signals the
+    // barrier of the group that converts that step. A group therefore sees every phase of every
+    // barrier it waits on, whatever the number of stages and of k steps per tile (with one barrier
+    // per stage a group would meet a subset of the phases and could take a lagging copy of the other
+    // group's step for its own).
+    uint64_t full[kConvGroups][kMaxStages];
     uint64_t done[kMaxStages];    // the MMAs of the step completed: smem stage and TMEM stage are free
     uint64_t d_full;              // accumulator complete
     uint64_t d_empty;             // the epilogue warps drained the accumulator
@@ -274,7 +279,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
         for (int s = 0; s < a.num_stages; ++s)
         {
-            mbar_init(&bars->full[s], 1);
+            for (int g = 0; g < kConvGroups; ++g)
+                mbar_init(&bars->full[g][s], 1);
             mbar_init(&bars->done[s], 1);
         }
         mbar_init(&bars->d_full, 1);
@@ -312,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t ph = 0;
             bool ok = true;
             uint32_t const smem_base = smem_u32(smem);
-            uint32_t const full0 = smem_u32(&bars->full[0]), done0 = smem_u32(&bars->done[0]);
+            uint32_t const full0 = smem_u32(&bars->full[0][0]), done0 = smem_u32(&bars->done[0]);
             for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
             {
                 int const tile = SPLITK ? item / a.splits : item, split = SPLITK ? item - tile * a.splits : 0;
@@ -324,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (!ok)
                         break;
                     uint32_t const stage = smem_base + uint32_t(s) * STAGE_BYTES;
-                    uint32_t const full = full0 + 8 * s;
+                    uint32_t const full = full0 + 8 * ((uint32_t(ks) % kConvGroups) * kMaxStages + s);
                     elect_expect_tx(full, STAGE_BYTES);
                     elect_tma_load_2d(stage, &tm_act, ks * BK, tm * BM, full);
                     elect_tma_load_2d(stage + ACT_HALF, &tm_act, ks * BK + 64, tm * BM, full);
@@ -427,6 +433,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         int s = 0;
         uint32_t ph = 0, dph = 0;
         uint32_t my_steps = 0; // steps this warp has stored into TMEM (published by lane 0)
+        uint32_t full_seen = 0; // bit s: phases of full[cgroup][s] this group has consumed, mod 2
         bool ok = true;
         for (int item = blockIdx.x; item < num_tiles && ok; item += gridDim.x)
         {
@@ -486,22 +493,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                     s2h[h] = s2;
                     z2h[h] = z2;
                 }
-                // A group converts every kConvGroups-th k step. When the number of stages is not a multiple
-                // of the number of groups, a group that waited only for its own steps would meet a given
-                // stage's barrier in a subset of that barrier's phases and could ask for a parity that a late
-                // copy of a phase in between satisfies early; in that case every group observes every phase
-                // (a group that does not convert the step merely waits for its copy). With 4 stages and 2
-                // groups each group sees every second phase of "its" stages and all phases of none other,
-                // and the extra waits (measured: 6 % of the prefill time) are not needed.
-                bool const mine = (ks % kConvGroups) == cgroup;
-                if (mine || (a.num_stages % kConvGroups) != 0)
+                if ((ks % kConvGroups) == cgroup)
                 {
-                    ok = wait_flag_warp(&bars->full[s], ph, abort_flag, lane);
+                    // parity of this group's next phase on the stage's barrier: one bit per stage
+                    uint32_t const fph = (full_seen >> s) & 1u;
+                    full_seen ^= 1u << s;
+                    ok = wait_flag_warp(&bars->full[cgroup][s], fph, abort_flag, lane);
                     if (!ok)
                         break;
-                }
-                if (mine)
-                {
                     uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
                     constexpr int CHUNKS = SEG / 16; // 16-byte chunks per half: 2 (int4) or 4 (int8)
                     uint4 raw[kHalves][CHUNKS];

@@ -51,17 +51,16 @@ namespace w4
 namespace gemv
 {
 
-#ifndef W4_GEMV_WARPS
-#define W4_GEMV_WARPS 16
-#endif
-constexpr int kWarps = W4_GEMV_WARPS;           // consumer warps
+// Consumer warps. With 8 (half the registers and shared memory, so that CTAs of consecutive launches
+// share an SM) one CTA cannot keep up with the copies: 12.4 us against 10.4 us on a 4096 x 14336 int4
+// matrix, 93 us against 63 us on 8192 x 57344.
+constexpr int kWarps = 16;
 constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kThreads = kConsumerThreads + 128; // + one producer warp group (one lane of it works)
 // Registers: a fifth warp per scheduler would cap every thread at 96 registers; the producer group
 // gives its share back (setmaxnreg) and the consumer groups take it.
 constexpr int kProducerRegs = 24, kConsumerRegs = 112; // 128 * 24 + 512 * 112 <= 640 * 96 (the launch-time pool)
 constexpr int kRedBytes = 64 * 1024;            // shared memory for cross-warp partial sums
-constexpr int kCtasPerSm = kWarps <= 8 ? 2 : 1; // 8 warps: half an SM, so two launches can overlap
 constexpr int kScaleBoxCols = 24;               // columns per scale/zero box: 16 + slack to start on a 16-byte boundary
 
 template <int BITS, int MB>
@@ -167,7 +166,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 }
 
 template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreads, 1)
     gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros)
 {
     using C = Cfg<BITS, MB>;
@@ -680,9 +679,8 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     // remain; ~72 KB are in flight at a time anyway).
     args.red_bytes = kRedBytes;
     size_t const fixed = size_t(args.red_bytes) + 64;
-    // Shared memory per CTA: all a block may have, or half of the SM's 228 KB less the 1 KB the
-    // system reserves per block when two CTAs are to fit.
-    size_t const smem_budget = kCtasPerSm == 1 ? size_t(dev.max_smem_optin) : size_t(233472 / 2 - 1024);
+    // Shared memory per CTA: all a block may have.
+    size_t const smem_budget = size_t(dev.max_smem_optin);
     int slots = int((smem_budget - fixed) / (args.slot_bytes + 16));
     if (slots < 2)
         return W4_ERR_CUDA;

@@ -80,6 +80,51 @@ def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, grou
     _lib.check(rc, "w4_gemm_launch")
 
 
+class PreparedGemm:
+    """One GEMM whose buffers do not move between calls (a decode step: same weights, same staging
+    buffers every token): the parameter block is built once, a call costs one C-ABI call.
+
+    ``launch`` enqueues w4_gemm_launch; ``run_host`` is w4_gemm_run_host: activations come from and the
+    result goes to pinned host tensors, ``act`` / ``out`` are the device staging buffers, and the call
+    returns when the result has landed."""
+
+    def __init__(self, act, weight, scales, out, *, n: int, k: int, weight_bits: int, group_size: int, zeros=None,
+                 bias=None, act_scale=None, alpha: float = 1.0, regime: int = W4_REGIME_AUTO, workspace=None,
+                 weights_static: bool = False):
+        for name, t in (("act", act), ("weight", weight), ("scales", scales), ("out", out)):
+            _require_cuda(t, name)
+        self._keep = (act, weight, scales, out, zeros, bias, act_scale, workspace)
+        self.device = act.device
+        self.m = act.numel() // k if k else 0
+        self.n, self.k = n, k
+        self.params = W4GemmParams(
+            act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros),
+            bias=_p(bias), out=_p(out), alpha=float(alpha), m=self.m, n=n, k=k, group_size=group_size,
+            weight_bits=weight_bits, act_dtype=_DTYPES[act.dtype], regime=regime, workspace=_p(workspace),
+            workspace_bytes=workspace.numel() * workspace.element_size() if workspace is not None else 0,
+            flags=_lib.W4_GEMM_WEIGHTS_STATIC if weights_static else 0)
+        _lib.check(_lib.lib().w4_gemm_validate(ctypes.byref(self.params)), "w4_gemm_validate")
+        self._ref = ctypes.byref(self.params)
+        self._launch = _lib.lib().w4_gemm_launch
+        self._run_host = _lib.lib().w4_gemm_run_host
+
+    def launch(self, stream: int) -> None:
+        """Enqueue on the CUDA stream handle ``stream`` (the caller has made the device current)."""
+        rc = self._launch(self._ref, stream)
+        if rc:
+            _lib.check(rc, "w4_gemm_launch")
+
+    def run_host(self, host_act, host_out, stream: int) -> None:
+        if host_act.is_cuda or host_out.is_cuda:
+            raise RuntimeError("run_host takes host tensors")
+        if host_act.numel() != self.m * self.k or host_out.numel() != self.m * self.n \
+                or not host_act.is_contiguous() or not host_out.is_contiguous():
+            raise RuntimeError("host tensors must be contiguous [M, K] and [M, N]")
+        rc = self._run_host(self._ref, host_act.data_ptr(), host_out.data_ptr(), stream)
+        if rc:
+            _lib.check(rc, "w4_gemm_run_host")
+
+
 def _run(act, weight, scales, zeros, bias, act_scale, alpha, weight_bits, group_size, regime, out=None,
          weights_static=False):
     for name, t in (("act", act), ("weight", weight), ("scales", scales)):

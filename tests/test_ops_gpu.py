@@ -118,3 +118,32 @@ def test_per_channel_plugin_mirror_enqueue(dtype, wtype, m):
     assert plugin.enqueue([_d(p["act"]), _d(p["processed"]), _d(p["scales"])], [out], ws if nws else None) == 0
     _assert_close(out, p)
     assert plugin.enqueue([_d(p["act"])[:0], _d(p["processed"]), _d(p["scales"])], [out[:0]], None) == 0  # m == 0
+
+
+@pytest.mark.parametrize("m,regime", [(1, pkg.W4_REGIME_GEMV), (5, pkg.W4_REGIME_AUTO), (200, pkg.W4_REGIME_GEMM)])
+def test_host_entry_point(m, regime):
+    """w4_gemm_run_host: pinned host activations in, pinned host result out, valid on return; twice
+    with different activations through the same prepared parameter block."""
+    p = make_problem(m, 1024, 512, 4, 128, torch.bfloat16, zero=True, bias=True, prequant=True, seed=40 + m)
+    d_act = torch.empty_like(_d(p["act"]))
+    d_out = torch.empty((m, 1024), dtype=torch.bfloat16, device="cuda")
+    nb = ops.workspace_bytes(m, 1024, 512, 128, 4, torch.bfloat16, True, regime)
+    ws = torch.empty(max(nb, 16), dtype=torch.uint8, device="cuda")
+    g = ops.PreparedGemm(d_act, _d(p["processed"]), _d(p["scales"]), d_out, n=1024, k=512, weight_bits=4,
+                         group_size=128, zeros=_d(p["zeros"]), bias=_d(p["bias"]), act_scale=_d(p["ps"]),
+                         regime=regime, workspace=ws)
+    h_out = torch.zeros((m, 1024), dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    for scale in (1.0, -2.0):
+        q = dict(p)
+        q["act"] = (p["act"].float() * scale).to(torch.bfloat16)
+        g.run_host(q["act"].contiguous().pin_memory(), h_out, stream)
+        _assert_close(h_out, q)  # no synchronize here: the call returns with the result in place
+    # pageable host memory takes the copy path
+    pageable_out = torch.zeros((m, 1024), dtype=torch.bfloat16)
+    g.run_host(p["act"].contiguous(), pageable_out, stream)
+    _assert_close(pageable_out, p)
+    with pytest.raises(RuntimeError):
+        g.run_host(d_act, h_out, stream)
+    with pytest.raises(RuntimeError):
+        g.run_host(p["act"][:, :256].contiguous(), h_out, stream)
