@@ -323,7 +323,7 @@ def run_reference(args):
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_line(line)
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
@@ -340,9 +340,6 @@ def run_ours(args):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
-        # NCCL_DEBUG=VERSION makes NCCL print its version on stdout, ahead of the one JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -480,7 +477,7 @@ def run_ours(args):
     if world > 1:
         line["tp_llama70b"] = tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks)
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if use_dist:
         dist.destroy_process_group()
 
@@ -839,6 +836,18 @@ def tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2
     return out
 
 
+_REAL_STDOUT = None
+
+
+def emit_line(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -849,6 +858,12 @@ def main():
     args = ap.parse_args()
     args.steps = max(1, min(args.steps, 20000))
     args.warmup = max(0, args.warmup)
+    # Libraries print on stdout (NCCL its version line, for one): everything but the one JSON line goes
+    # to stderr. emit_line() writes to the real stdout.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:

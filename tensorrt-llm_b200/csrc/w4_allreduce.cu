@@ -47,7 +47,8 @@ namespace ar
 {
 
 constexpr int kMaxRanks = W4_MAX_RANKS;
-constexpr int kThreads = 512;
+constexpr int kThreads = 512;       // flag protocol
+constexpr int kPacketThreads = 128; // packet protocols
 constexpr int kMaxCtas = W4_ALLREDUCE_MAX_CTAS; // chunks per message or slice
 constexpr size_t kCtrlBytes = 256;
 constexpr size_t kFlagBytes = size_t(2) * kMaxRanks * kMaxCtas * sizeof(uint32_t);
@@ -167,28 +168,19 @@ __device__ __forceinline__ bool get_packets(uint4 (&v)[kMaxRanks], uint8_t const
     unsigned long long t0 = 0;
     for (uint32_t polls = 1;; ++polls)
     {
-        uint4 p[kMaxRanks][2];
+        // all loads are issued before the first flag is looked at
+        uint32_t bad = 0;
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r)
             if (mask >> r & 1u)
             {
                 uint4 const* src = reinterpret_cast<uint4 const*>(inbox + size_t(r) * slot) + 2 * vec;
-                p[r][0] = ld_sys(src);
-                p[r][1] = ld_sys(src + 1);
+                uint4 const p0 = ld_sys(src), p1 = ld_sys(src + 1);
+                v[r] = make_uint4(p0.x, p0.z, p1.x, p1.z);
+                bad |= (p0.y ^ epoch) | (p0.w ^ epoch) | (p1.y ^ epoch) | (p1.w ^ epoch);
             }
-        bool ready = true;
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (mask >> r & 1u)
-                ready = ready && p[r][0].y == epoch && p[r][0].w == epoch && p[r][1].y == epoch && p[r][1].w == epoch;
-        if (ready)
-        {
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (mask >> r & 1u)
-                    v[r] = make_uint4(p[r][0].x, p[r][0].z, p[r][1].x, p[r][1].z);
+        if (bad == 0)
             return true;
-        }
         if ((polls & 15u) == 0)
         {
             if (*failed)
@@ -262,15 +254,17 @@ __device__ __forceinline__ uint4 pack8(float const (&acc)[8])
     return o;
 }
 
-// Sum of v[0..world) in rank order (+ bias vector), rounded to T.
+// Sum over ranks 0..world-1 in rank order (+ bias vector), rounded to T: v[r] from the peers, `mine`
+// in this rank's place.
 template <typename T>
-__device__ __forceinline__ uint4 sum_ranks(uint4 const (&v)[kMaxRanks], int world, uint4 const* bias_vec)
+__device__ __forceinline__ uint4 sum_ranks(uint4 const (&v)[kMaxRanks], uint4 mine, int rank, int world,
+    uint4 const* bias_vec)
 {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r)
         if (r < world)
-            add8<T>(acc, v[r]);
+            add8<T>(acc, r == rank ? mine : v[r]);
     if (bias_vec)
         add8<T>(acc, __ldg(bias_vec));
     return pack8<T>(acc);
@@ -314,6 +308,12 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
 
     if (threadIdx.x == 0)
         failed = 0;
+    // Programmatic dependent launch: the kernel that follows on the stream may start its prologue now
+    // (the decode GEMM fetches its weights meanwhile); this kernel itself may have been started before
+    // the one in front has finished, and touches nothing (not even the call number, which the previous
+    // all-reduce call two kernels back may still be about to advance) before that one is complete.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Call number: read by every CTA before any CTA of this launch can advance it (see the end).
     uint32_t const epoch = *reinterpret_cast<volatile uint32_t*>(ctrl) + 1u;
     int const h = int(epoch & 1u);
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
     if (b.protocol == kOneShotPackets)
     {
         size_t const v0 = V * size_t(c) / C, v1 = V * size_t(c + 1) / C;
-        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+        for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x)
         {
             uint4 const v = partial[i];
 #pragma unroll
@@ -347,13 +347,12 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
                 if (peers >> p & 1u)
                     put_packets(reinterpret_cast<uint4*>(packets_of(a.ws[p], 0) + size_t(rank) * b.pkt_slot) + 2 * i, v, epoch);
         }
-        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+        for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x)
         {
             uint4 v[kMaxRanks];
             if (!get_packets(v, packets_of(mine, 0), b.pkt_slot, i, peers, epoch, b.timeout_ns, &failed))
                 break;
-            v[rank] = partial[i];
-            out[i] = sum_ranks<T>(v, world, bias ? bias + (i % n_vec) : nullptr);
+            out[i] = sum_ranks<T>(v, partial[i], rank, world, bias ? bias + (i % n_vec) : nullptr);
         }
     }
     else if (b.protocol == kTwoShotPackets)
@@ -364,7 +363,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
         size_t const v0 = max_len * size_t(c) / C, v1 = max_len * size_t(c + 1) / C;
         size_t const s0 = slice_begin(rank), len = slice_begin(rank + 1) - s0;
         // ---- vectors of slice j go to its owner j, inbox A, slot `rank`
-        for (size_t i = v0 + threadIdx.x; i < v1; i += kThreads)
+        for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x)
         {
 #pragma unroll
             for (int dj = 1; dj < kMaxRanks; ++dj)
@@ -381,14 +380,13 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
         }
         // ---- reduce the own slice, write it out and send it to every peer's inbox B, slot `rank`
         bool ok = true;
-        for (size_t i = v0 + threadIdx.x; i < v1 && i < len; i += kThreads)
+        for (size_t i = v0 + threadIdx.x; i < v1 && i < len; i += blockDim.x)
         {
             uint4 v[kMaxRanks];
             ok = get_packets(v, packets_of(mine, 0), b.pkt_slot, i, peers, epoch, b.timeout_ns, &failed);
             if (!ok)
                 break;
-            v[rank] = partial[s0 + i];
-            uint4 const o = sum_ranks<T>(v, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
+            uint4 const o = sum_ranks<T>(v, partial[s0 + i], rank, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
             out[s0 + i] = o;
 #pragma unroll
             for (int p = 0; p < kMaxRanks; ++p)
@@ -396,7 +394,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
                     put_packets(reinterpret_cast<uint4*>(packets_of(a.ws[p], 1) + size_t(rank) * b.pkt_slot) + 2 * i, o, epoch);
         }
         // ---- collect the other slices from inbox B
-        for (size_t i = v0 + threadIdx.x; ok && i < v1; i += kThreads)
+        for (size_t i = v0 + threadIdx.x; ok && i < v1; i += blockDim.x)
         {
             uint32_t mask = 0;
 #pragma unroll
@@ -441,9 +439,9 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
                 uint4 v[kMaxRanks];
 #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world)
-                        v[r] = r == rank ? partial[s0 + i] : ld_sys(reinterpret_cast<uint4 const*>(plain_of(mine, r)) + i);
-                uint4 const o = sum_ranks<T>(v, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
+                    if (peers >> r & 1u)
+                        v[r] = ld_sys(reinterpret_cast<uint4 const*>(plain_of(mine, r)) + i);
+                uint4 const o = sum_ranks<T>(v, partial[s0 + i], rank, world, bias ? bias + ((s0 + i) % n_vec) : nullptr);
                 st_sys(red + i, o);
                 out[s0 + i] = o;
             }
@@ -471,14 +469,14 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
 
     // ---- the last CTA of this rank's launch advances the call number
     __syncthreads();
+    // (No fences: every CTA has read the number before it takes its ticket, and the next call is a
+    // later kernel on the stream, which sees everything this one wrote.)
     if (threadIdx.x == 0)
     {
-        __threadfence();
         uint32_t const ticket = atomicAdd(ctrl + 1, 1u);
         if (ticket == uint32_t(C) - 1u)
         {
             ctrl[1] = 0u;
-            __threadfence();
             *reinterpret_cast<volatile uint32_t*>(ctrl) = epoch;
         }
     }
@@ -562,17 +560,30 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
     w4::DeviceInfo const& dev = w4::current_device_info();
     if (dev.num_sms <= 0)
         return W4_ERR_CUDA;
-    // Chunks: about 512 vectors (8 KB) each or more, at most kMaxCtas; all ranks derive the same
-    // number from the message size alone. Several ranks in one launch (single-GPU emulation) must all
-    // be resident at once, so the number is capped by the SMs available per rank.
+    // Chunks: at most kMaxCtas; all ranks derive the same number from the message size alone. The
+    // packet protocols are bound by how fast one SM issues stores towards the peers (2 * (world - 1)
+    // per vector: measured about 30 cycles per warp-wide store), so their work is spread thin: 128
+    // vectors per CTA of 128 threads. The flag protocol moves whole chunks: 512 threads, 8 KB or more
+    // each. Several ranks in one launch (single-GPU emulation) must all be resident at once, so the
+    // number is capped by the SMs available per rank.
     size_t const vecs = p0.count / 8;
     size_t const unit = b.protocol == kOneShotPackets ? vecs : (vecs + p0.world - 1) / p0.world;
-    int ctas = int(b.protocol == kTwoShotFlags ? unit / 512 : (unit + 511) / 512);
-    ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
-    if (ctas > dev.num_sms / ranks_in_launch)
-        ctas = dev.num_sms / ranks_in_launch;
-    if (ctas < 1)
+    int const cap = kMaxCtas < dev.num_sms / ranks_in_launch ? kMaxCtas : dev.num_sms / ranks_in_launch;
+    if (cap < 1)
         return W4_ERR_UNSUPPORTED;
+    int threads = kThreads;
+    int ctas = int(unit / kThreads);
+    if (b.protocol != kTwoShotFlags)
+    {
+        threads = kPacketThreads;
+        ctas = int((unit + kPacketThreads - 1) / kPacketThreads);
+        if (ctas > cap) // more work than thin CTAs can cover: full-size CTAs
+        {
+            threads = kThreads;
+            ctas = int((unit + kThreads - 1) / kThreads);
+        }
+    }
+    ctas = ctas < 1 ? 1 : (ctas > cap ? cap : ctas);
     b.ctas_per_rank = ctas;
     for (int i = 0; i < ranks_in_launch; ++i)
     {
@@ -587,7 +598,7 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
         a.n = p.n;
         a.rank = p.rank;
     }
-    dim3 const grid(unsigned(ctas * ranks_in_launch)), block(kThreads);
+    dim3 const grid(unsigned(ctas * ranks_in_launch)), block(threads);
     void* args[] = {&b};
     cudaError_t rc;
     if (ranks_in_launch > 1)
@@ -600,11 +611,20 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
     }
     else
     {
-        if (p0.act_dtype == W4_DTYPE_FP16)
-            allreduce_kernel<__half><<<grid, block, 0, stream>>>(b);
-        else
-            allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(b);
-        rc = cudaGetLastError();
+        // A programmatic dependent of whatever precedes it in the stream (see the kernel's first lines).
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        rc = p0.act_dtype == W4_DTYPE_FP16 ? cudaLaunchKernelEx(&cfg, allreduce_kernel<__half>, b)
+                                           : cudaLaunchKernelEx(&cfg, allreduce_kernel<__nv_bfloat16>, b);
+        if (rc == cudaSuccess)
+            rc = cudaGetLastError();
     }
     return rc == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
