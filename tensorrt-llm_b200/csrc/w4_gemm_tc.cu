@@ -266,8 +266,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         | (uint32_t(BM >> 3) << 17)                                         // MMA N = activation rows
         | (uint32_t(BN >> 4) << 24);                                        // MMA M = weight columns
 
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // The 128-byte swizzle of the TMA copies and of the MMA descriptors is a function of the
+    // shared-memory address: the ring starts on a 1024-byte boundary (declared, and checked below).
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) // never seen; nothing has been allocated or initialised yet
+    {
+        if (threadIdx.x == 0)
+            atomicExch(&g_device_status, kDeviceTimeout);
+        return;
+    }
     Barriers* bars = reinterpret_cast<Barriers*>(smem + size_t(a.num_stages) * STAGE_BYTES);
     volatile int* abort_flag = &bars->abort_flag;
 

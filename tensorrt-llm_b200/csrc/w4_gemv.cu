@@ -8,8 +8,9 @@
 // preprocessed weight (one interleaved row = IL adjacent output columns x all of K = 2K bytes, see
 // below), so every CTA streams one contiguous slab of HBM. One lane of a producer warp group moves
 // that slab into a shared-memory ring with bulk (TMA-engine) copies, one tile (16 columns x one k
-// panel, with its scale/zero boxes) at a time, a bounded number of tiles in flight so that they
-// land in order; 16 consumer warps split K, pull 16-byte chunks out of the ring with 128-bit shared
+// panel, with its scale/zero boxes) at a time (a flat copy when K fits one panel; with several
+// panels int4 rows come through a tensor map whose swizzle removes the bank conflicts of the
+// consumers' reads), a bounded number of tiles in flight so that they land in order; 16 consumer warps split K, pull 16-byte chunks out of the ring with 128-bit shared
 // loads and feed mma.sync (weights as the 16-row A operand, the m <= 8 activation rows as the
 // 8-column B operand, held in registers), accumulating in fp32. The producer group hands most of
 // its registers to the consumers (setmaxnreg). Partial sums of the 16 warps are combined through
@@ -125,6 +126,11 @@ struct Consts<__nv_bfloat16>
     static constexpr uint32_t ONE2 = 0x3f803f80u, SIXTEENTH2 = 0x3d803d80u;
 };
 
+__host__ __device__ inline int num_panels_of(int k, int kp)
+{
+    return (k + kp - 1) / kp;
+}
+
 struct Args
 {
     uint8_t const* weight;
@@ -167,14 +173,23 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 
 template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
 __global__ void __launch_bounds__(kThreads, 1)
-    gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros)
+    gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros,
+        __grid_constant__ CUtensorMap const tm_w)
 {
     using C = Cfg<BITS, MB>;
     using P = Pair<T>;
     using F = Fold<T, BITS>;
     constexpr int PLANES = FOLD ? F::PLANES : 1;
-    extern __shared__ __align__(128) uint8_t smem[];
+    // Slots start on 1024-byte boundaries: the swizzle of the int4 weight tiles is a function of the
+    // shared-memory address.
+    extern __shared__ __align__(1024) uint8_t smem[];
 
+    if (BITS == 4 && num_panels_of(a.k, C::KP) > 1 && (smem_u32(smem) & 1023u) != 0) // never seen; tiles would be read wrongly
+    {
+        if (threadIdx.x == 0)
+            atomicExch(&g_device_status, kDeviceTimeout);
+        return;
+    }
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + size_t(a.num_slots) * a.slot_bytes);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + size_t(a.num_slots) * a.slot_bytes + a.red_bytes);
@@ -221,14 +236,31 @@ __global__ void __launch_bounds__(kThreads, 1)
         int const kp_len = min(C::KP, a.k - panel * C::KP);
         uint32_t const bytes = 2u * kp_len;
         uint32_t const box_bytes = uint32_t(a.groups_per_panel) * kScaleBoxCols * 2;
-        mbar_expect_tx(&full_bar[slot], bytes * rows + box_bytes * (HAS_ZERO ? 2 : 1));
         uint8_t* dst = ring + size_t(slot) * a.slot_bytes;
-        uint8_t const* src = a.weight + size_t(row_first) * row_bytes + size_t(panel) * C::ROW_STRIDE;
-        if (num_panels == 1)
-            bulk_g2s(dst, src, bytes * rows, &full_bar[slot]);
-        else
+        if (BITS == 4 && num_panels > 1)
+        {
+            // int4 with several k panels: every row's panel is fetched as a box of 128-byte lines
+            // through a tensor map with the 32-byte-atom swizzle, which spreads the two lines a
+            // quarter-warp reads over all banks (+6 % on a 8192 x 57344 matrix; with a single panel
+            // the one flat copy below is as fast, so it stays). A box always arrives whole: lines
+            // past k hold the next row's weights (or zeros past the tensor's end) and only ever
+            // meet zero activations.
+            int const lpr = a.k >> 6; // lines per interleaved row
+            mbar_expect_tx(&full_bar[slot], uint32_t(rows) * C::ROW_STRIDE + box_bytes * (HAS_ZERO ? 2 : 1));
             for (int r = 0; r < rows; ++r)
-                bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
+                tma_load_2d(dst + r * C::ROW_STRIDE, &tm_w, 0, (row_first + r) * lpr + panel * (C::KP >> 6),
+                    &full_bar[slot]);
+        }
+        else
+        {
+            mbar_expect_tx(&full_bar[slot], bytes * rows + box_bytes * (HAS_ZERO ? 2 : 1));
+            uint8_t const* src = a.weight + size_t(row_first) * row_bytes + size_t(panel) * C::ROW_STRIDE;
+            if (num_panels == 1)
+                bulk_g2s(dst, src, bytes * rows, &full_bar[slot]);
+            else
+                for (int r = 0; r < rows; ++r)
+                    bulk_g2s(dst + r * C::ROW_STRIDE, src + r * row_bytes, bytes, &full_bar[slot]);
+        }
         // The scale / zero rows of this panel for the group's columns travel with the tile, from
         // the 8-column boundary at or below the group's first column.
         int const col_aligned = (row_first * C::IL) & ~7;
@@ -251,6 +283,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     else if (tid == 32)
     {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_scales) : "memory");
+        if (BITS == 4)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
         if (HAS_ZERO)
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_zeros) : "memory");
     }
@@ -312,6 +346,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const colB = BITS == 4 ? 2 * g + 1 : 8 + g;
     int const segA = (colA / C::IL) * row_stride + (colA % C::IL) * (128 / C::IL);
     int const segB = (colB / C::IL) * row_stride + (colB % C::IL) * (128 / C::IL);
+    // int4: byte offset of this thread's chunk of column A in a tile, per unit. In the swizzled tiles
+    // of the multi-panel case line L keeps its 32-byte column segment s at position s ^ (L & 3).
+    // Column B is the segment next to it: the offset with bit 5 flipped, swizzled or not.
+    uint32_t woff[C::UPW];
+#pragma unroll
+    for (int j = 0; j < C::UPW; ++j)
+    {
+        int const kk = (j * kWarps + warp) * C::UK + t * C::CK;
+        int const line = (colA / C::IL) * (row_stride >> 7) + (kk >> 6);
+        int const swz = num_panels > 1 ? (line & 3) : 0;
+        woff[j] = uint32_t(line * 128 + (((colA % C::IL) ^ swz) << 5) + ((kk & 63) / C::CK) * 16);
+    }
 
     T const* act = static_cast<T const*>(a.act);
     T const* act_scale = static_cast<T const*>(a.act_scale);
@@ -419,8 +465,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // slot (kk%64)/CK inside the column segment.
         int const kk = (j * kWarps + warp) * C::UK + t * C::CK;
         int const off = (kk >> 6) * 128 + ((kk & 63) / C::CK) * 16;
-        uint4 const wa = *reinterpret_cast<uint4 const*>(tile + segA + off);
-        uint4 const wb = *reinterpret_cast<uint4 const*>(tile + segB + off);
+        uint4 const wa = *reinterpret_cast<uint4 const*>(tile + (BITS == 4 ? woff[j] : uint32_t(segA + off)));
+        uint4 const wb = *reinterpret_cast<uint4 const*>(tile + (BITS == 4 ? woff[j] ^ 32u : uint32_t(segB + off)));
         uint32_t const ra[4] = {wa.x, wa.y, wa.z, wa.w};
         uint32_t const rb[4] = {wb.x, wb.y, wb.z, wb.w};
 
@@ -673,12 +719,12 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     Args args = a;
     args.groups_per_panel = a.group_shift >= 31 ? 1 : C::KP >> a.group_shift;
     args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
-    args.slot_bytes = C::TILE_BYTES + 2 * args.box_stride;
+    args.slot_bytes = (C::TILE_BYTES + 2 * args.box_stride + 1023) & ~1023;
     // 64 KB of partial sums (8 column groups at 8 rows, 32 at one): every reduction is a CTA-wide
     // barrier, and fewer of them measured faster than the two ring slots this costs (four slots
     // remain; ~72 KB are in flight at a time anyway).
     args.red_bytes = kRedBytes;
-    size_t const fixed = size_t(args.red_bytes) + 64;
+    size_t const fixed = size_t(args.red_bytes) + 64 + 1024; // + slack to start the ring on a 1024-byte boundary
     // Shared memory per CTA: all a block may have.
     size_t const smem_budget = size_t(dev.max_smem_optin);
     int slots = int((smem_budget - fixed) / (args.slot_bytes + 16));
@@ -705,6 +751,16 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
         && !make_tensor_map_2d(&tm_zeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, a.zeros, uint64_t(a.n), groups,
             uint64_t(a.n) * 2, kScaleBoxCols, uint32_t(args.groups_per_panel), CU_TENSOR_MAP_SWIZZLE_NONE))
         return W4_ERR_CUDA;
+    // int4 weights with several k panels as [lines, 128 bytes]; box = the lines of one row's panel.
+    CUtensorMap tm_w = tm_scales;
+    if (BITS == 4 && a.k > C::KP)
+    {
+        uint64_t const lpr = uint64_t(a.k) >> 6;
+        uint32_t const box_lines = uint32_t(C::KP >> 6); // used with several k panels only
+        if (!make_tensor_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.weight, 128, uint64_t(args.num_rows) * lpr, 128, 128,
+                box_lines, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+            return W4_ERR_CUDA;
+    }
 
     // The opt-in shared-memory limit is a per-function, per-device attribute: set it once.
     {
@@ -740,7 +796,7 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kernel, args, tm_scales, tm_zeros) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, kernel, args, tm_scales, tm_zeros, tm_w) != cudaSuccess)
         return W4_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
