@@ -1,4 +1,4 @@
-// Decode-regime kernel (m = 1..8 per pass): streams the packed int4/int8 weights exactly once.
+// Decode-regime kernel (m = 1..8 or 9..16 per pass): streams the packed int4/int8 weights exactly once.
 //
 // Replaces weight_only::kernel of the reference project
 // (cpp/tensorrt_llm/kernels/weightOnlyBatchedGemv/kernel.h:31-120) and, for m >= 5 / m >= 16, the
@@ -12,7 +12,8 @@
 // panels int4 rows come through a tensor map whose swizzle removes the bank conflicts of the
 // consumers' reads), a bounded number of tiles in flight so that they land in order; 16 consumer warps split K, pull 16-byte chunks out of the ring with 128-bit shared
 // loads and feed mma.sync (weights as the 16-row A operand, the m <= 8 activation rows as the
-// 8-column B operand, held in registers), accumulating in fp32. The producer group hands most of
+// 8-column B operand, held in registers; a 16-row pass feeds two B fragments per weight fragment
+// and covers half as much k per tile), accumulating in fp32. The producer group hands most of
 // its registers to the consumers (setmaxnreg). Partial sums of the 16 warps are combined through
 // shared memory in a fixed order (deterministic) once per batch of column groups, then alpha/bias
 // are applied and the result stored. The kernel is launched as a programmatic dependent: weight
@@ -62,6 +63,7 @@ constexpr int kThreads = kConsumerThreads + 128; // + one producer warp group (o
 // gives its share back (setmaxnreg) and the consumer groups take it.
 constexpr int kProducerRegs = 24, kConsumerRegs = 112; // 128 * 24 + 512 * 112 <= 640 * 96 (the launch-time pool)
 constexpr int kRedBytes = 64 * 1024;            // shared memory for cross-warp partial sums
+constexpr int kRedBytes16 = 112 * 1024;         // the same for 16-row passes (7 column groups)
 constexpr int kScaleBoxCols = 24;               // columns per scale/zero box: 16 + slack to start on a 16-byte boundary
 
 template <int BITS, int MB>
@@ -218,7 +220,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     int const red_cap = max(1, (a.red_bytes / 4) / per_cg); // column groups the reduction buffer holds
     // Column groups that share one activation load (only matters with several k panels); the
     // reduction batch is a whole number of such sub-batches.
-    int const cbe = min(CB, red_cap);
+    // CB == 0: no register sub-batches; the partial sums of a whole reduction batch accumulate in
+    // shared memory across the k panels, so one activation load per panel serves the whole batch.
+    constexpr bool RED_ACC = CB == 0;
+    constexpr int CBR = RED_ACC ? 1 : CB;
+    int const cbe = RED_ACC ? red_cap : min(CB, red_cap);
     int const batch = (red_cap / cbe) * cbe;
 
 
@@ -454,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     };
 
-    float acc[CB][MB][4]; // running sums of the column groups of the current sub-batch
+    float acc[CBR][MB][4]; // running sums of the column groups of the current sub-batch
 
     // One warp unit (16 columns x UK k) out of the tile in shared memory.
     auto process_unit = [&](int j, int cg, uint8_t const* tile, float(&acc)[MB][4])
@@ -614,7 +620,50 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int cg0 = 0; cg0 < num_cg; cg0 += batch)
     {
         int const nb = min(batch, num_cg - cg0);
-        for (int c0 = 0; c0 < nb; c0 += cbe)
+        if (RED_ACC)
+        {
+            for (int panel = 0; panel < num_panels; ++panel)
+            {
+                if (num_panels > 1 && !first_act)
+                    load_act(panel);
+                first_act = false;
+                for (int cb = 0; cb < nb; ++cb)
+                {
+                    if (ok)
+                        ok = wait_or_abort(&full_bar[slot], use & 1, abort_flag);
+                    uint8_t const* tile = ring + size_t(slot) * a.slot_bytes;
+#pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            acc[0][mb][c] = 0.f;
+#pragma unroll
+                    for (int j = 0; j < C::UPW; ++j)
+                        process_unit(j, cg0 + cb, tile, acc[0]);
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&empty_bar[slot]);
+                    if (++slot == a.num_slots)
+                    {
+                        slot = 0;
+                        ++use;
+                    }
+                    // every thread owns its entries of the buffer: plain read-modify-write
+                    if (t < MT)
+                    {
+#pragma unroll
+                        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                            {
+                                float* dst = red + (((cb * kWarps + warp) * MB + mb) * 4 + c) * (8 * MT) + g * MT + t;
+                                *dst = panel == 0 ? acc[0][mb][c] : *dst + acc[0][mb][c];
+                            }
+                    }
+                }
+            }
+        }
+        for (int c0 = 0; !RED_ACC && c0 < nb; c0 += cbe)
         {
             int const ncb = min(cbe, nb - c0);
 #pragma unroll
@@ -723,7 +772,7 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     // 64 KB of partial sums (8 column groups at 8 rows, 32 at one): every reduction is a CTA-wide
     // barrier, and fewer of them measured faster than the two ring slots this costs (four slots
     // remain; ~72 KB are in flight at a time anyway).
-    args.red_bytes = kRedBytes;
+    args.red_bytes = MB == 2 ? kRedBytes16 : kRedBytes;
     size_t const fixed = size_t(args.red_bytes) + 64 + 1024; // + slack to start the ring on a 1024-byte boundary
     // Shared memory per CTA: all a block may have.
     size_t const smem_budget = size_t(dev.max_smem_optin);
@@ -814,27 +863,46 @@ static int dispatch_flags(Args const& a, DeviceInfo const& dev, cudaStream_t str
     return launch_one<T, BITS, MB, false, false, FOLD, CB>(a, dev, stream);
 }
 
-// With more than one k panel the column groups are walked in sub-batches that share each
-// activation load (4 groups for m <= 8, 2 for m <= 16); with a single panel there is nothing to share.
+// 8-row passes: with more than one k panel the column groups are walked in sub-batches of 4 that
+// share each activation load and keep their sums in registers, or, when a CTA has more than 4 of
+// them, accumulate in shared memory like the 16-row passes; with a single panel there is nothing
+// to share. 16-row passes hold half as much k per panel (their activation fragments are twice as
+// large), so they always accumulate in shared memory and load the activations once per panel for all
+// the column groups of a reduction batch.
 template <typename T, int BITS, int MB, bool FOLD>
 static int dispatch_panels(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
-    if (a.k > Cfg<BITS, MB>::KP)
-        return dispatch_flags<T, BITS, MB, FOLD, (MB == 1 ? 4 : 2)>(a, dev, stream);
-    return dispatch_flags<T, BITS, MB, FOLD, 1>(a, dev, stream);
+    if constexpr (MB == 2)
+        return dispatch_flags<T, BITS, MB, FOLD, 0>(a, dev, stream);
+    else
+    {
+        if (a.k > Cfg<BITS, MB>::KP)
+        {
+            // more column groups per CTA than one register sub-batch holds: accumulate in shared
+            // memory instead, and load the activations once per panel for all of them (8192 x 57344
+            // int4, m = 1: 60.0 -> 54.1 us; with two groups per CTA the register form is the faster)
+            int const ctas = a.num_rows < dev.num_sms ? a.num_rows : dev.num_sms;
+            int const groups = (a.num_rows + Cfg<BITS, MB>::RPG - 1) / Cfg<BITS, MB>::RPG;
+            if (groups > 4 * ctas)
+                return dispatch_flags<T, BITS, MB, FOLD, 0>(a, dev, stream);
+            return dispatch_flags<T, BITS, MB, FOLD, 4>(a, dev, stream);
+        }
+        return dispatch_flags<T, BITS, MB, FOLD, 1>(a, dev, stream);
+    }
 }
 
 template <typename T>
 static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev, cudaStream_t stream)
 {
-    (void) mb; // only the 8-row variant (MB = 1) is instantiated
     if (bits == 4)
     {
         // A warp unit spans 128 k for int4: the folded arithmetic needs one scale group per unit.
         bool const fold = a.group_shift >= 7;
+        if (mb == 2)
+            return fold ? dispatch_panels<T, 4, 2, true>(a, dev, stream) : dispatch_panels<T, 4, 2, false>(a, dev, stream);
         return fold ? dispatch_panels<T, 4, 1, true>(a, dev, stream) : dispatch_panels<T, 4, 1, false>(a, dev, stream);
     }
-    return dispatch_panels<T, 8, 1, true>(a, dev, stream);
+    return mb == 2 ? dispatch_panels<T, 8, 2, true>(a, dev, stream) : dispatch_panels<T, 8, 1, true>(a, dev, stream);
 }
 
 } // namespace gemv
@@ -845,13 +913,13 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
     if (dev.num_sms <= 0)
         return W4_ERR_CUDA;
     size_t const elt = 2;
-    // Passes of at most 8 rows. The 16-row variant of the kernel (two B fragments per weight
-    // fragment, MB = 2) has to split K into two panels to hold its activation fragments and reloads
-    // them for every pair of column groups: measured again at 24.9 us for config 2 at m = 16, the
-    // same as two 8-row passes (24.4 us), so it is not instantiated.
-    for (int m0 = 0; m0 < p.m; m0 += 8)
+    // Passes over the weights: 16 rows at a time (two B fragments per weight fragment) while more
+    // than 8 rows are left, then one pass of up to 8.
+    for (int m0 = 0; m0 < p.m;)
     {
-        int const rows = p.m - m0 < 8 ? p.m - m0 : 8;
+        int const left = p.m - m0;
+        int const mb = left > 8 ? 2 : 1;
+        int const rows = left < 8 * mb ? left : 8 * mb;
         gemv::Args a{};
         a.weight = static_cast<uint8_t const*>(p.weight);
         a.act = static_cast<char const*>(p.act) + size_t(m0) * p.k * elt;
@@ -868,11 +936,11 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
         a.num_groups = p.group_size ? p.k / p.group_size : 1;
         a.num_rows = p.n / (p.weight_bits == 4 ? 4 : 2);
         a.weights_static = (p.flags & W4_GEMM_WEIGHTS_STATIC) ? 1 : 0;
-        int const mb = 1;
         int const rc = p.act_dtype == W4_DTYPE_FP16 ? gemv::dispatch_bits<__half>(a, p.weight_bits, mb, dev, stream)
                                                     : gemv::dispatch_bits<__nv_bfloat16>(a, p.weight_bits, mb, dev, stream);
         if (rc != W4_OK)
             return rc;
+        m0 += rows;
     }
     return W4_OK;
 }
