@@ -169,6 +169,21 @@ extern "C"
      * everything else in p as for w4_gemm_launch. Allocates nothing. */
     int w4_gemm_run_host(const W4GemmParams* p, const void* host_act, void* host_out, void* stream);
 
+    /*
+     * One GEMM per expert of a mixture-of-experts layer over 3-D weights, enqueued back to back on
+     * `stream`. p describes expert 0: weight is [E][K, N*bits/8], every expert's matrix laid out on its
+     * own - what preprocess_weights_for_mixed_gemm does with a 3-D tensor
+     * (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:136-147, force_interleave); scales / zeros are
+     * [E][K/G, N] (or [E][N]), bias [E][N]; act_scale [K] is shared. The rows of act and out are sorted
+     * by expert: expert e owns rows expert_first_row[e] .. expert_first_row[e + 1] - 1 (host array of
+     * num_experts + 1 non-decreasing ints starting at 0; the running totals the reference's MoE GEMM
+     * takes as total_tokens_including_expert,
+     * cpp/tensorrt_llm/kernels/internal_cutlass_kernels/include/moe_gemm_kernels.h:236, kept on the host). p->m is ignored; the
+     * workspace must cover the largest per-expert row count (w4_gemm_workspace_bytes_max) and is
+     * reused by every expert. Experts without rows are skipped. Returns the first error.
+     */
+    int w4_gemm_launch_experts(const W4GemmParams* p, int num_experts, const int* expert_first_row, void* stream);
+
     /* Bytes of scratch w4_gemm_launch needs for this problem in the regime it would pick. */
     size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
         int has_act_scale, int regime);

@@ -25,7 +25,7 @@ EXPORTS = (
     "w4_pack_int4", "w4_unpack_int4", "w4_gemm_launch_static_scratch", "w4_gemm_static_scratch_bytes",
     "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce", "w4_allreduce_emulated",
     "w4_allreduce_workspace_bytes",
-    "w4_gemm_workspace_bytes_max", "w4_gemm_run_host",
+    "w4_gemm_workspace_bytes_max", "w4_gemm_run_host", "w4_gemm_launch_experts",
 )
 
 
@@ -82,6 +82,8 @@ def lib() -> ctypes.CDLL:
         l.w4_gemm_validate.argtypes = [ctypes.POINTER(W4GemmParams)]
         l.w4_gemm_launch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
         l.w4_gemm_launch_static_scratch.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p]
+        l.w4_gemm_launch_experts.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                             ctypes.c_void_p]
         l.w4_gemm_run_host.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         l.w4_gemm_static_scratch_bytes.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes.restype = ctypes.c_size_t

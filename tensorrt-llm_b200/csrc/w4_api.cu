@@ -258,6 +258,40 @@ extern "C"
         return w4::launch_gemm_tc(*p, s);
     }
 
+    int w4_gemm_launch_experts(const W4GemmParams* p, int num_experts, const int* expert_first_row, void* stream)
+    {
+        if (!p || !expert_first_row)
+            return W4_ERR_NULL_POINTER;
+        if (num_experts < 1 || expert_first_row[0] != 0)
+            return W4_ERR_BAD_SHAPE;
+        for (int e = 0; e < num_experts; ++e)
+            if (expert_first_row[e + 1] < expert_first_row[e])
+                return W4_ERR_BAD_SHAPE;
+        size_t const elt = 2;
+        size_t const groups = p->group_size ? size_t(p->k) / size_t(p->group_size) : 1;
+        size_t const weight_bytes = size_t(p->k) * p->n * p->weight_bits / 8;
+        auto at = [](const void* base, size_t bytes) -> const void*
+        { return base ? static_cast<const char*>(base) + bytes : nullptr; };
+        for (int e = 0; e < num_experts; ++e)
+        {
+            int const row0 = expert_first_row[e], rows = expert_first_row[e + 1] - row0;
+            if (rows == 0)
+                continue;
+            W4GemmParams q = *p;
+            q.m = rows;
+            q.act = at(p->act, size_t(row0) * p->k * elt);
+            q.out = const_cast<void*>(at(p->out, size_t(row0) * p->n * elt));
+            q.weight = at(p->weight, size_t(e) * weight_bytes);
+            q.scales = at(p->scales, size_t(e) * groups * p->n * elt);
+            q.zeros = at(p->zeros, size_t(e) * groups * p->n * elt);
+            q.bias = at(p->bias, size_t(e) * p->n * elt);
+            int const rc = w4_gemm_launch(&q, stream);
+            if (rc != W4_OK)
+                return rc;
+        }
+        return W4_OK;
+    }
+
     int w4_gemm_run_host(const W4GemmParams* p, const void* host_act, void* host_out, void* stream)
     {
         int const rc = w4_gemm_validate(p);

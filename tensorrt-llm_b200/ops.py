@@ -80,6 +80,41 @@ def gemm_raw(act, weight, scales, out, *, n: int, k: int, weight_bits: int, grou
     _lib.check(rc, "w4_gemm_launch")
 
 
+def moe_gemm(act, weight, scales, expert_first_row: Sequence[int], *, weight_bits: int, group_size: int, zeros=None,
+             bias=None, act_scale=None, alpha: float = 1.0, out=None, weights_static: bool = False):
+    """w4_gemm_launch_experts: ``weight`` [E, K, N*bits/8] (laid out per expert), ``scales`` / ``zeros``
+    [E, K/G, N] or [E, N], ``bias`` [E, N]; rows of ``act`` sorted by expert, expert e owning rows
+    expert_first_row[e] .. expert_first_row[e+1]-1. Returns [M, N]."""
+    for name, t in (("act", act), ("weight", weight), ("scales", scales)):
+        _require_cuda(t, name)
+    if weight.dim() != 3:
+        raise RuntimeError("weight must be [experts, K, N*bits/8]")
+    e, k = weight.shape[0], weight.shape[1]
+    n = weight.shape[2] * weight.element_size() * 8 // weight_bits
+    m = act.numel() // k
+    first = [int(x) for x in expert_first_row]
+    if len(first) != e + 1 or first[0] != 0 or first[-1] != m:
+        raise RuntimeError("expert_first_row must hold experts + 1 offsets from 0 to M")
+    if out is None:
+        out = torch.empty((m, n), dtype=act.dtype, device=act.device)
+    if m == 0:
+        return out
+    biggest = max(b - a for a, b in zip(first[:-1], first[1:]))
+    nws = workspace_bytes_max(biggest, n, k, group_size, weight_bits, act.dtype, act_scale is not None)
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=act.device)
+    params = W4GemmParams(
+        act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros), bias=_p(bias),
+        out=_p(out), alpha=float(alpha), m=m, n=n, k=k, group_size=group_size, weight_bits=weight_bits,
+        act_dtype=_DTYPES[act.dtype], regime=W4_REGIME_AUTO, workspace=_p(ws), workspace_bytes=ws.numel(),
+        flags=_lib.W4_GEMM_WEIGHTS_STATIC if weights_static else 0)
+    offsets = (ctypes.c_int * (e + 1))(*first)
+    with torch.cuda.device(act.device):
+        rc = _lib.lib().w4_gemm_launch_experts(ctypes.byref(params), e, offsets,
+                                               ctypes.c_void_p(torch.cuda.current_stream(act.device).cuda_stream))
+    _lib.check(rc, "w4_gemm_launch_experts")
+    return out
+
+
 class PreparedGemm:
     """One GEMM whose buffers do not move between calls (a decode step: same weights, same staging
     buffers every token): the parameter block is built once, a call costs one C-ABI call.

@@ -43,7 +43,7 @@ def _expected(parts, b):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 5, 7, 8])
 @pytest.mark.parametrize("mode", [L.W4_ALLREDUCE_ONE_SHOT, L.W4_ALLREDUCE_TWO_SHOT])
 @pytest.mark.parametrize("m,n", [(1, 8192), (3, 1024), (64, 8192), (7, 4104)])
 def test_emulated_ranks_bit_exact(dtype, world, mode, m, n):
@@ -72,6 +72,24 @@ def test_large_and_auto_modes(mode, m):
     ref = _expected(parts, None)
     for r in range(world):
         assert torch.equal(outs[r], ref)
+
+
+@pytest.mark.parametrize("world", [3, 6])
+def test_flag_protocol_with_ragged_slices(world):
+    """Above 4 MiB the plain-data protocol with arrival flags runs; 271 625 vectors do not divide by the
+    rank count, so the slices and their chunks are ragged. Twice, for both copies of the buffers."""
+    m, n = 265, 8200
+    assert m * n * 2 > L.W4_ALLREDUCE_LL_MAX_BYTES
+    parts, wss, outs, b = _setup(world, m, n, torch.bfloat16, m * n * 2, world, bias=True)
+    for call in range(2):
+        for p in parts:
+            p.mul_(-0.75)
+        ops.allreduce_emulated(parts, wss, outs, n, biases=[b] * world)
+        torch.cuda.synchronize()
+        ref = _expected(parts, b)
+        for r in range(world):
+            assert torch.equal(outs[r], ref), f"call {call}, rank {r}"
+    assert L.lib().w4_gemm_device_status() == 0
 
 
 def test_graph_replay_needs_no_host_counter():

@@ -147,3 +147,39 @@ def test_host_entry_point(m, regime):
         g.run_host(d_act, h_out, stream)
     with pytest.raises(RuntimeError):
         g.run_host(p["act"][:, :256].contiguous(), h_out, stream)
+
+
+@pytest.mark.parametrize("bits,group", [(4, 128), (8, 0)])
+def test_experts_over_3d_weights(bits, group):
+    """w4_gemm_launch_experts: 3-D weights laid out per expert by the (3-D capable) layout op, rows
+    sorted by expert, one expert without rows, row counts on both sides of the regime switch."""
+    from tensorrt_llm_b200 import quantize
+    dtype, k, n = torch.float16, 512, 384
+    rows = [3, 0, 40, 1, 9]
+    first = [0]
+    for r in rows:
+        first.append(first[-1] + r)
+    probs = [make_problem(max(r, 1), n, k, bits, group, dtype, zero=group != 0, bias=group != 0, seed=70 + e)
+             for e, r in enumerate(rows)]
+    # the layout op on the stacked tensor must equal the per-expert layout (what the kernels consume)
+    stacked = torch.stack([p["packed"] for p in probs]).contiguous()
+    qt = torch.quint4x2 if bits == 4 else torch.int8
+    w3 = quantize.preprocess_weights_for_mixed_gemm(stacked, qt, torch.float16)
+    for e, p in enumerate(probs):
+        assert torch.equal(w3[e], p["processed"])
+    act = torch.cat([p["act"][:r] for p, r in zip(probs, rows)])
+    stack = lambda key: None if probs[0][key] is None else torch.stack([p[key] for p in probs]).cuda()
+    out = ops.moe_gemm(act.cuda(), w3.cuda(), stack("scales"), first, weight_bits=bits, group_size=group,
+                       zeros=stack("zeros"), bias=stack("bias")).cpu()
+    assert out.shape == (sum(rows), n)
+    for e, (p, r) in enumerate(zip(probs, rows)):
+        if r == 0:
+            continue
+        q = dict(p)
+        q["act"] = p["act"][:r]
+        ref = oracle_out(q)
+        got = out[first[e]:first[e + 1]]
+        assert max_err(got, ref) <= oracle.tolerance(ref), e
+    assert pkg._lib.lib().w4_gemm_device_status() == 0
+    with pytest.raises(RuntimeError):
+        ops.moe_gemm(act.cuda(), w3.cuda(), stack("scales"), first[:-1], weight_bits=bits, group_size=group)
