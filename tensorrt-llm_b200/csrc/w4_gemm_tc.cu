@@ -53,7 +53,6 @@ constexpr int kTmemCols = 512;
 constexpr int kConvGroups = 2;   // groups of 4 conversion warps; group g converts k steps with ks % 2 == g
 constexpr int kThreads = 64 + 128 * kConvGroups;
 constexpr int kMaxStages = kMaxAStages; // one ring index for the shared-memory stage and its TMEM stage
-constexpr int kScaleLookahead = 6; // scale groups fetched ahead of use by the conversion warps
 
 struct Args
 {
@@ -437,8 +436,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // Column segment of this thread inside the first of a stage's two weight lines.
         int const w_off = (n_local / IL) * (128 * kHalves) + (n_local % IL) * SEG;
 
-        int s = 0;
-        uint32_t ph = 0, dph = 0;
+        int s_item = 0;          // ring position of the current work item's first k step
+        uint32_t ph_item = 0, dph = 0;
         uint32_t my_steps = 0; // steps this warp has stored into TMEM (published by lane 0)
         uint32_t full_seen = 0; // bit s: phases of full[cgroup][s] this group has consumed, mod 2
         bool ok = true;
@@ -449,65 +448,60 @@ __global__ void __launch_bounds__(kThreads, 1)
             int const ks0 = SPLITK ? split * a.ksteps_split : 0, ks1 = SPLITK ? min(ksteps_all, ks0 + a.ksteps_split) : ksteps_all;
             int const n = tn * BN + n_local;
             bool const n_ok = n < a.n;
-            // Scale / zero of this thread's column, one pair per scale group. The loads come from
-            // global memory (L2 at best, ~1 us under load) while a k step lasts a quarter of that,
-            // so they are issued kScaleLookahead groups ahead into a small shift register.
-            uint32_t s2 = 0, z2 = 0;
-            uint32_t sq[kScaleLookahead], zq[kScaleLookahead];
+            // Scale / zero of this thread's column for the steps THIS group converts (every
+            // kConvGroups-th k step), one pair per 64-k half. They come from global memory (L2 at
+            // best, ~1 us under load, longer than a k step), so the pairs of a step are loaded two of
+            // the group's own steps ahead, into one of two register sets that the twice-unrolled loop
+            // below addresses statically. (A shift queue does not work here: shifting it reads the
+            // newest entry one scale group after its load was issued, and with 64-wide groups that
+            // is half a k step - the warp ends up waiting for every load.)
             int const num_groups = a.group_shift >= 31 ? 1 : (a.k >> a.group_shift);
-            int const g_first = SPLITK ? (ks0 * kHalves) >> gsh : 0; // scale group of this work item's first half
-#pragma unroll
-            for (int i = 0; i < kScaleLookahead; ++i)
+            auto load_pairs = [&](int ks, uint32_t(&sp)[kHalves], uint32_t(&zp)[kHalves])
             {
-                sq[i] = 0;
-                zq[i] = 0;
-                if (n_ok && g_first + i < num_groups)
-                {
-                    sq[i] = scales[size_t(g_first + i) * a.n + n];
-                    if (HAS_ZERO)
-                        zq[i] = zeros[size_t(g_first + i) * a.n + n];
-                }
-            }
-            for (int ks = ks0; ks < ks1; ++ks)
-            {
-                // (scale, zero) pairs of the step's two halves; a new scale group starts every
-                // 2^gsh halves: take the oldest prefetched pair, fetch the one furthest ahead.
-                uint32_t s2h[kHalves], z2h[kHalves];
 #pragma unroll
                 for (int h = 0; h < kHalves; ++h)
                 {
-                    int const u = ks * kHalves + h;
-                    if ((u & ((1 << gsh) - 1)) == 0 || (SPLITK && ks == ks0 && h == 0))
+                    int const g = (ks * kHalves + h) >> gsh;
+                    uint32_t sv = 0, zv = 0;
+                    if (n_ok && ks < ks1 && g < num_groups)
                     {
-                        s2 = sq[0] | (sq[0] << 16);
-                        z2 = zq[0] | (zq[0] << 16);
-#pragma unroll
-                        for (int i = 0; i + 1 < kScaleLookahead; ++i)
-                        {
-                            sq[i] = sq[i + 1];
-                            zq[i] = zq[i + 1];
-                        }
-                        int const gnext = (u >> gsh) + kScaleLookahead;
-                        sq[kScaleLookahead - 1] = 0;
-                        zq[kScaleLookahead - 1] = 0;
-                        if (n_ok && gnext < num_groups)
-                        {
-                            sq[kScaleLookahead - 1] = scales[size_t(gnext) * a.n + n];
-                            if (HAS_ZERO)
-                                zq[kScaleLookahead - 1] = zeros[size_t(gnext) * a.n + n];
-                        }
+                        sv = scales[size_t(g) * a.n + n];
+                        if (HAS_ZERO)
+                            zv = zeros[size_t(g) * a.n + n];
                     }
-                    s2h[h] = s2;
-                    z2h[h] = z2;
+                    sp[h] = sv | (sv << 16);
+                    zp[h] = zv | (zv << 16);
                 }
-                if ((ks % kConvGroups) == cgroup)
+            };
+            // position of the item's first step in the ring; own steps are reached from it
+            int const first_own = ks0 + ((cgroup - ks0 % kConvGroups + kConvGroups) % kConvGroups);
+            int s = s_item;
+            uint32_t ph = ph_item;
+            auto advance = [&](int steps)
+            {
+                s += steps;
+                while (s >= a.num_stages)
+                {
+                    s -= a.num_stages;
+                    ph ^= 1;
+                }
+            };
+            advance(first_own - ks0);
+            uint32_t sset[2][kHalves], zset[2][kHalves];
+            load_pairs(first_own, sset[0], zset[0]);
+            load_pairs(first_own + kConvGroups, sset[1], zset[1]);
+
+            // One own step: wait for its weights, convert, store into the TMEM stage, publish.
+            auto convert_step = [&](int ks, uint32_t const(&s2h)[kHalves], uint32_t const(&z2h)[kHalves]) -> bool
+            {
+                (void) ks;
                 {
                     // parity of this group's next phase on the stage's barrier: one bit per stage
                     uint32_t const fph = (full_seen >> s) & 1u;
                     full_seen ^= 1u << s;
                     ok = wait_flag_warp(&bars->full[cgroup][s], fph, abort_flag, lane);
                     if (!ok)
-                        break;
+                        return false;
                     uint8_t const* wsm = smem + size_t(s) * STAGE_BYTES + ACT_BYTES + w_off;
                     constexpr int CHUNKS = SEG / 16; // 16-byte chunks per half: 2 (int4) or 4 (int8)
                     uint4 raw[kHalves][CHUNKS];
@@ -564,7 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     ok = wait_flag_warp(&bars->done[s], ph ^ 1, abort_flag, lane);
                     if (!ok)
-                        break;
+                        return false;
                     tc_fence_after();
                     uint32_t const a_addr = lane_addr + kACol0 + s * (32 * kHalves); // warp-uniform column address
 #pragma unroll
@@ -581,12 +575,36 @@ __global__ void __launch_bounds__(kThreads, 1)
                                      : "memory");
                     }
                 }
-                if (++s == a.num_stages)
+                return true;
+            };
+
+            for (int ks = first_own; ks < ks1 && ok; ks += 2 * kConvGroups)
+            {
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
                 {
-                    s = 0;
-                    ph ^= 1;
+                    int const kk = ks + u * kConvGroups;
+                    if (kk < ks1 && ok)
+                    {
+                        uint32_t s2h[kHalves], z2h[kHalves];
+#pragma unroll
+                        for (int h = 0; h < kHalves; ++h)
+                        {
+                            s2h[h] = sset[u][h];
+                            z2h[h] = zset[u][h];
+                        }
+                        load_pairs(kk + 2 * kConvGroups, sset[u], zset[u]);
+                        if (convert_step(kk, s2h, z2h))
+                            advance(kConvGroups);
+                    }
                 }
             }
+            // the next item starts where this one's k range ends
+            s = s_item;
+            ph = ph_item;
+            advance(ks1 - ks0);
+            s_item = s;
+            ph_item = ph;
             if (!ok)
                 break;
 
@@ -851,7 +869,7 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 // tensor work; 256 rows leave shared memory for three stages only and the step turns latency-bound.
 static double step_us(int bm)
 {
-    return bm <= 128 ? 0.645 : (bm == 192 ? 0.70 : 1.06);
+    return bm <= 128 ? 0.57 : (bm == 192 ? 0.70 : 1.05);
 }
 
 // Split-k factor: used when the output tiles would occupy less than half of the SMs; every work
