@@ -13,7 +13,7 @@
 # treat the cross-check as optional.
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref="${1:-${WOQ_REFERENCE_ROOT:-/root/reference}}"
+ref="${1:-${WOQ_REFERENCE_ROOT:-$here/../../reference}}"
 out="$here/_ref"
 src="$ref/cpp/tensorrt_llm"
 
