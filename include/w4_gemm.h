@@ -237,6 +237,17 @@ extern "C"
     /* in: [k, n*bits/8] row-major two's-complement weights (int4: even column in the low nibble). */
     int w4_preprocess_weights(int8_t* out, const int8_t* in, size_t k, size_t n, int bits);
 
+    /* int4 weights in the layout the reference produces when the activation type is fp8 (W4A8-AWQ:
+     * preprocess_weights_for_mixed_gemm with QuantType::W4_AFP8, cutlass_preprocessors.cpp:114-116,
+     * 175-179: two interleaved columns, 128-row tiles, its own row permutation). in: [k, n/2] row-major
+     * two's-complement nibbles; k % 128 == 0, n % 64 == 0. Same bytes as the reference. */
+    int w4_preprocess_weights_w4a8(int8_t* out, const int8_t* in, size_t k, size_t n);
+
+    /* W4A8-layout bytes (above) -> the W4A16 layout the kernels of this library consume; done once
+     * when the weights are loaded. After it, a W4A8-AWQ layer is w4_gemm_launch with alpha set, the
+     * W4_GEMM_ACT_E4M3 flag and scales / zeros converted to the activation type. */
+    int w4_relayout_w4a8_to_w4a16(int8_t* out, const int8_t* in, size_t k, size_t n);
+
     int w4_pack_int4(int8_t* packed, const int8_t* unpacked, size_t num_packed_bytes);
     void w4_unpack_int4(int8_t* unpacked, const int8_t* packed, size_t num_packed_bytes);
 

@@ -106,6 +106,20 @@ extern "C"
         return 0;
     }
 
+    // int4 weights laid out for fp8 activations (W4A8).
+    int ref_preprocess_weights_w4a8(int8_t* out, int8_t const* in, size_t rows, size_t cols)
+    {
+        try
+        {
+            ck::preprocess_weights_for_mixed_gemm(out, in, {rows, cols}, ck::QuantType::W4_AFP8, false);
+        }
+        catch (std::exception const& e)
+        {
+            return report(e);
+        }
+        return 0;
+    }
+
     int ref_permute_B_rows(int8_t* out, int8_t const* in, size_t rows, size_t cols, int bits)
     {
         try

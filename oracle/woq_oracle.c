@@ -33,6 +33,9 @@
 static const int kPerm8[16] = {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15};
 static const int kPerm4[32] = {0, 1, 8, 9, 16, 17, 24, 25, 2, 3, 10, 11, 18, 19, 26, 27, 4, 5, 12, 13, 20, 21, 28, 29,
     6, 7, 14, 15, 22, 23, 30, 31};
+/* pre.cpp:175-179 - the permutation for int4 weights under fp8 activations (W4A8). */
+static const int kPerm4A8[32] = {0, 1, 2, 3, 16, 17, 18, 19, 4, 5, 6, 7, 20, 21, 22, 23, 8, 9, 10, 11, 24, 25, 26, 27,
+    12, 13, 14, 15, 28, 29, 30, 31};
 
 static int get_elt(const uint8_t* buf, size_t idx, int bits)
 {
@@ -115,6 +118,53 @@ int oracle_interleave_columns(uint8_t* out, const uint8_t* in, size_t K, size_t 
         }
     }
     return ORACLE_OK;
+}
+
+int oracle_add_bias_and_interleave(uint8_t* buf, size_t num_elts, int bits);
+
+/* The int4 layout for fp8 activations (W4A8), pre.cpp:114-116 with
+ * cutlass_extensions/.../mixed_gemm_B_layout.h:105-117 for an 8-bit A type: ThreadblockK = 128 and
+ * ColumnsInterleaved = 256 / 128 = 2; rows permuted by kPerm4A8; the nibble step is the W4A16 one
+ * (pre.cpp:498-505). */
+int oracle_preprocess_weights_w4a8(uint8_t* out, const uint8_t* in, size_t K, size_t N)
+{
+    const int bits = 4;
+    if (K % 128 || N % 8)
+        return ORACLE_BAD_SHAPE;
+    const size_t num_bytes = K * N / 2;
+    uint8_t* a = (uint8_t*) malloc(num_bytes ? num_bytes : 1);
+    uint8_t* b = (uint8_t*) malloc(num_bytes ? num_bytes : 1);
+    if (!a || !b)
+    {
+        free(a);
+        free(b);
+        return ORACLE_BAD_ARG;
+    }
+    const size_t row_bytes = N / 2;
+    for (size_t base = 0; base < K; base += 32)
+        for (int r = 0; r < 32; ++r)
+            memcpy(a + (base + r) * row_bytes, in + (base + kPerm4A8[r]) * row_bytes, row_bytes);
+    int rc = oracle_subbyte_transpose(b, a, K, N, bits);
+    if (rc == ORACLE_OK)
+    {
+        const size_t elts_per_word = 8, rows_per_tile = 128, interleave = 2;
+        const size_t words_per_col = K / elts_per_word, words_per_tile = rows_per_tile / elts_per_word;
+        const uint32_t* src = (const uint32_t*) b;
+        uint32_t* dst = (uint32_t*) a;
+        for (size_t n = 0; n < N; ++n)
+            for (size_t w = 0; w < words_per_col; ++w)
+            {
+                const size_t base = w - w % words_per_tile;
+                const size_t write_word = interleave * base + words_per_tile * (n % interleave) + w % words_per_tile;
+                dst[(n / interleave) * words_per_col * interleave + write_word] = src[n * words_per_col + w];
+            }
+        rc = oracle_add_bias_and_interleave(a, K * N, bits);
+    }
+    if (rc == ORACLE_OK)
+        memcpy(out, a, num_bytes);
+    free(a);
+    free(b);
+    return rc;
 }
 
 /* pre.cpp:412-433 (int8) and :435-489 (int4): make the values unsigned (+128 / +8) and shuffle

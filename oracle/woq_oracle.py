@@ -106,6 +106,18 @@ def preprocess_weights(q, bits: int) -> np.ndarray:
     return _step("oracle_preprocess_weights", q, K, N, bits)
 
 
+def preprocess_weights_w4a8(q) -> np.ndarray:
+    """[K, N/2] int8 row-major int4 weight -> the bytes the reference produces when the activation
+    type is fp8 (W4A8): a different row permutation and a 2-column, 128-row interleave."""
+    q = np.ascontiguousarray(q)
+    K, N = q.shape[0], q.shape[1] * 2
+    src = _as_u8(q).reshape(-1)
+    out = np.zeros_like(src)
+    _check(lib().oracle_preprocess_weights_w4a8(_ptr(out), _ptr(src), ctypes.c_size_t(K), ctypes.c_size_t(N)),
+           "preprocess_w4a8")
+    return out.view(np.int8).reshape(q.shape)
+
+
 def unpreprocess_to_int8(processed, K: int, N: int, bits: int) -> np.ndarray:
     """Inverse layout transform: signed integers [K, N] from preprocessed bytes."""
     src = _as_u8(processed).reshape(-1)
@@ -158,6 +170,18 @@ def ref_preprocess_weights(q, bits: int, sm=(10, 0)) -> np.ndarray:
     r.ref_set_sm(sm[0], sm[1])
     _check(r.ref_preprocess_weights_for_mixed_gemm(_ptr(out), _ptr(src), ctypes.c_size_t(K), ctypes.c_size_t(N), bits),
            "ref_preprocess")
+    return out.view(np.int8).reshape(q.shape)
+
+
+def ref_preprocess_weights_w4a8(q, sm=(10, 0)) -> np.ndarray:
+    r = ref_lib()
+    assert r is not None, "oracle/_ref was not built"
+    q = np.ascontiguousarray(q)
+    K, N = q.shape[0], q.shape[1] * 2
+    src = _as_u8(q).reshape(-1)
+    out = np.zeros_like(src)
+    r.ref_set_sm(sm[0], sm[1])
+    _check(r.ref_preprocess_weights_w4a8(_ptr(out), _ptr(src), ctypes.c_size_t(K), ctypes.c_size_t(N)), "ref_w4a8")
     return out.view(np.int8).reshape(q.shape)
 
 

@@ -97,7 +97,85 @@ void transform(uint8_t* out, uint8_t const* in, size_t K, size_t N, int bits)
         });
 }
 
+// int4 weights as the reference lays them out for fp8 activations (W4A8;
+// cutlass_preprocessors.cpp:114-116,175-179 with mixed_gemm_B_layout.h:105-117 for an 8-bit A type):
+// two columns interleaved, 128-row tiles, its own row permutation inside every block of 32 rows.
+// Register `reg` of the output holds, in nibble d, element e(d) of word j of tile t of column
+// 2 * irow + c, where reg = irow * (K / 4) + 32 * t + 16 * c + j. One routine walks that map in
+// either direction: FORWARD builds the W4A8 bytes from row-major two's-complement nibbles, the other
+// direction recovers the row-major nibbles from W4A8 bytes.
+constexpr int kPerm4A8[32] = {0, 1, 2, 3, 16, 17, 18, 19, 4, 5, 6, 7, 20, 21, 22, 23, 8, 9, 10, 11, 24, 25, 26, 27, 12, 13,
+    14, 15, 28, 29, 30, 31};
+
+template <bool FORWARD>
+void walk_w4a8(uint8_t* laid_out, uint8_t* row_major, size_t K, size_t N)
+{
+    size_t const regs_per_irow = K / 4; // two columns of K / 8 registers
+    size_t const num_irows = N / 2;
+    size_t const row_bytes = N / 2;
+    uint32_t* regs = reinterpret_cast<uint32_t*>(laid_out);
+    // parallel over interleaved rows: a pair of columns touches its own bytes of every source row
+    // (two nibbles of one byte), so the reverse direction has no write conflicts either
+    parallel_for(num_irows, 16,
+        [=](size_t lo, size_t hi)
+        {
+            for (size_t irow = lo; irow < hi; ++irow)
+                for (size_t vwr = 0; vwr < regs_per_irow; ++vwr)
+                {
+                    size_t const t = vwr / 32, c = (vwr % 32) / 16, j = vwr % 16;
+                    size_t const n = irow * 2 + c;
+                    uint32_t word = FORWARD ? 0u : regs[irow * regs_per_irow + vwr];
+                    for (size_t d = 0; d < 8; ++d)
+                    {
+                        size_t const e = d < 4 ? 2 * d : 2 * (d - 4) + 1;
+                        size_t const kp = 128 * t + 8 * j + e;
+                        size_t const k = (kp & ~size_t(31)) + size_t(kPerm4A8[kp & 31]);
+                        uint8_t& b = row_major[k * row_bytes + n / 2];
+                        if (FORWARD)
+                        {
+                            int const v = (n & 1) ? (int8_t(b) >> 4) : (int8_t(uint8_t(b << 4)) >> 4);
+                            word |= (uint32_t(v + 8) & 0xFu) << (4 * d);
+                        }
+                        else
+                        {
+                            uint32_t const q = (((word >> (4 * d)) & 0xFu) - 8u) & 0xFu; // two's complement nibble
+                            b = (n & 1) ? uint8_t((b & 0x0F) | (q << 4)) : uint8_t((b & 0xF0) | q);
+                        }
+                    }
+                    if (FORWARD)
+                        regs[irow * regs_per_irow + vwr] = word;
+                }
+        });
+}
+
+bool shape_ok_w4a8(size_t k, size_t n)
+{
+    return k > 0 && n > 0 && k % 128 == 0 && n % 64 == 0;
+}
+
 } // namespace
+
+extern "C" int w4_preprocess_weights_w4a8(int8_t* out, const int8_t* in, size_t k, size_t n)
+{
+    if (!out || !in)
+        return W4_ERR_NULL_POINTER;
+    if (!shape_ok_w4a8(k, n))
+        return W4_ERR_BAD_SHAPE;
+    walk_w4a8<true>(reinterpret_cast<uint8_t*>(out), const_cast<uint8_t*>(reinterpret_cast<uint8_t const*>(in)), k, n);
+    return W4_OK;
+}
+
+extern "C" int w4_relayout_w4a8_to_w4a16(int8_t* out, const int8_t* in, size_t k, size_t n)
+{
+    if (!out || !in)
+        return W4_ERR_NULL_POINTER;
+    if (!shape_ok_w4a8(k, n) || !shape_ok(k, n, 4))
+        return W4_ERR_BAD_SHAPE;
+    std::vector<uint8_t> row_major(k * n / 2);
+    walk_w4a8<false>(const_cast<uint8_t*>(reinterpret_cast<uint8_t const*>(in)), row_major.data(), k, n);
+    transform(reinterpret_cast<uint8_t*>(out), row_major.data(), k, n, 4);
+    return W4_OK;
+}
 
 extern "C" int w4_preprocess_weights(int8_t* out, const int8_t* in, size_t k, size_t n, int bits)
 {

@@ -74,7 +74,9 @@ def _symmetric_quantize_last_axis_of_batched_matrix(weight: torch.Tensor, quant_
 def preprocess_weights_for_mixed_gemm(row_major_quantized_weight: torch.Tensor, quant_type,
                                       activation_type=torch.float16) -> torch.Tensor:
     """[K, N*bits/8] int8 row-major two's-complement weights -> kernel layout
-    (weightOnlyQuantOp.cpp:123-151). activation_type float8_e4m3fn (W4A8) is not supported."""
+    (weightOnlyQuantOp.cpp:123-151). activation_type float8_e4m3fn selects the W4A8 layout whatever
+    quant_type says, as the reference's get_ft_quant_type does (weightOnlyQuantOp.cpp:40-46); the GEMM
+    kernels take that layout after relayout_w4a8_weights()."""
     t = row_major_quantized_weight
     _check_cpu_contiguous(t, "row_major_quantized_weight")
     if t.dtype != torch.int8:
@@ -82,14 +84,33 @@ def preprocess_weights_for_mixed_gemm(row_major_quantized_weight: torch.Tensor, 
     bits = _bits(quant_type)
     if t.dim() not in (2, 3):
         raise RuntimeError("Invalid dim. The dim of weight should be 2 or 3")
-    if activation_type == getattr(torch, "float8_e4m3fn", None):
-        raise RuntimeError("W4A8 (fp8 activation) layout is not supported by this library")
+    w4a8 = activation_type == getattr(torch, "float8_e4m3fn", None)
+    if w4a8:
+        bits = 4
     out = torch.zeros_like(t)
     mats = [(t, out)] if t.dim() == 2 else [(t[e], out[e]) for e in range(t.shape[0])]
     for src, dst in mats:
         k, n = src.shape[0], src.shape[1] * 8 // bits
-        rc = _lib.lib().w4_preprocess_weights(_ptr(dst), _ptr(src), k, n, bits)
+        if w4a8:
+            rc = _lib.lib().w4_preprocess_weights_w4a8(_ptr(dst), _ptr(src), k, n)
+        else:
+            rc = _lib.lib().w4_preprocess_weights(_ptr(dst), _ptr(src), k, n, bits)
         _lib.check(rc, "preprocess_weights_for_mixed_gemm")
+    return out
+
+
+def relayout_w4a8_weights(w4a8_weight: torch.Tensor) -> torch.Tensor:
+    """[K, N/2] (or [E, K, N/2]) int8 bytes in the reference's W4A8 layout -> the W4A16 layout this
+    library's kernels consume (w4_relayout_w4a8_to_w4a16). Done once at load time."""
+    t = w4a8_weight
+    _check_cpu_contiguous(t, "w4a8_weight")
+    if t.dtype != torch.int8 or t.dim() not in (2, 3):
+        raise RuntimeError("expected an int8 tensor [K, N/2] or [E, K, N/2]")
+    out = torch.zeros_like(t)
+    mats = [(t, out)] if t.dim() == 2 else [(t[e], out[e]) for e in range(t.shape[0])]
+    for src, dst in mats:
+        rc = _lib.lib().w4_relayout_w4a8_to_w4a16(_ptr(dst), _ptr(src), src.shape[0], src.shape[1] * 2)
+        _lib.check(rc, "relayout_w4a8_weights")
     return out
 
 

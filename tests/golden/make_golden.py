@@ -51,6 +51,14 @@ def main():
             out[f"raw_processed_int{bits}"] = o.ref_preprocess_weights(q, bits)
         np.savez_compressed(os.path.join(HERE, f"quant_{name}.npz"), dtype=str(dt), **out)
         print("wrote", name)
+    # int4 weights laid out for fp8 activations (W4A8): raw bytes through the reference's transform
+    out = {}
+    for K, N, seed in ((128, 64, 10), (256, 192, 11)):
+        q = np.random.default_rng(seed).integers(-128, 128, size=(K, N // 2), dtype=np.int8)
+        out[f"raw_{K}x{N}"] = q
+        out[f"w4a8_{K}x{N}"] = o.ref_preprocess_weights_w4a8(q)
+    np.savez_compressed(os.path.join(HERE, "layout_w4a8.npz"), **out)
+    print("wrote layout_w4a8")
 
 
 if __name__ == "__main__":

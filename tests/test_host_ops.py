@@ -56,6 +56,31 @@ def test_host_ops_match_oracle(bits, K, N):
     assert torch.equal(p2, exp[1]) and torch.equal(s2, exp[2])
 
 
+def test_w4a8_layout_and_relayout():
+    """preprocess_weights_for_mixed_gemm with an fp8 activation type gives the reference's W4A8 bytes
+    (golden vectors made by the reference's code); relayout_w4a8_weights turns them into the layout
+    the kernels consume, i.e. what the same integers give through the W4A16 transform."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "layout_w4a8.npz"))
+    for key in g.files:
+        if not key.startswith("raw_"):
+            continue
+        raw = torch.from_numpy(g[key])
+        a8 = quantize.preprocess_weights_for_mixed_gemm(raw, torch.quint4x2, torch.float8_e4m3fn)
+        assert np.array_equal(a8.numpy(), g["w4a8_" + key[4:]])
+        a16 = quantize.relayout_w4a8_weights(a8)
+        assert torch.equal(a16, quantize.preprocess_weights_for_mixed_gemm(raw, torch.quint4x2, torch.float16))
+    rng = np.random.default_rng(9)
+    q = torch.from_numpy(rng.integers(-128, 128, size=(2, 256, 64), dtype=np.int8))  # 3-D: per expert
+    a8 = quantize.preprocess_weights_for_mixed_gemm(q, torch.quint4x2, torch.float8_e4m3fn)
+    for e in range(2):
+        assert np.array_equal(a8[e].numpy(), o.preprocess_weights_w4a8(q[e].numpy()))
+    assert torch.equal(quantize.relayout_w4a8_weights(a8),
+                       quantize.preprocess_weights_for_mixed_gemm(q, torch.quint4x2, torch.float16))
+    with pytest.raises(pkg.W4Error):
+        quantize.preprocess_weights_for_mixed_gemm(torch.zeros(64, 32, dtype=torch.int8), torch.quint4x2,
+                                                   torch.float8_e4m3fn)
+
+
 def test_batched_weights():
     w = torch.randn(3, 64, 64, generator=torch.Generator().manual_seed(0))
     p, s = quantize.symmetric_quantize_last_axis_of_batched_matrix(w, torch.int8)

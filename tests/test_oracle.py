@@ -30,6 +30,22 @@ def test_oracle_matches_golden(path):
         assert np.array_equal(o.preprocess_weights(g[f"raw_int{bits}"], bits), g[f"raw_processed_int{bits}"])
 
 
+def test_w4a8_layout_matches_golden_and_reference():
+    """int4 weights laid out for fp8 activations: the oracle against vectors made by the reference's
+    own code, and against that code live when it is built."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "layout_w4a8.npz"))
+    for key in g.files:
+        if key.startswith("raw_"):
+            shape = key[4:]
+            assert np.array_equal(o.preprocess_weights_w4a8(g[key]), g[f"w4a8_{shape}"])
+            assert not np.array_equal(o.preprocess_weights(g[key], 4), g[f"w4a8_{shape}"])  # a different layout
+    if o.ref_lib() is not None:
+        q = np.random.default_rng(3).integers(-128, 128, size=(384, 64), dtype=np.int8)
+        assert np.array_equal(o.preprocess_weights_w4a8(q), o.ref_preprocess_weights_w4a8(q))
+    with pytest.raises(ValueError):
+        o.preprocess_weights_w4a8(np.zeros((64, 32), dtype=np.int8))  # K must be a multiple of 128
+
+
 @pytest.mark.parametrize("bits", [4, 8])
 def test_layout_round_trip(bits):
     rng = np.random.default_rng(5)
