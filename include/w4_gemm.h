@@ -244,8 +244,10 @@ extern "C"
     int w4_preprocess_weights_w4a8(int8_t* out, const int8_t* in, size_t k, size_t n);
 
     /* W4A8-layout bytes (above) -> the W4A16 layout the kernels of this library consume; done once
-     * when the weights are loaded. After it, a W4A8-AWQ layer is w4_gemm_launch with alpha set, the
-     * W4_GEMM_ACT_E4M3 flag and scales / zeros converted to the activation type. */
+     * when the weights are loaded. After it, a W4A8-AWQ layer (quant_algo & FP8_ALPHA,
+     * weightOnlyGroupwiseQuantMatmulPlugin.cpp:206-218) is w4_gemm_launch with alpha set and the
+     * float16 scales / zeros converted to the activation type; the activations stay 16-bit, as in the
+     * reference's own GEMV path for W4A8 (weightOnlyBatchedGemv/utility.h:136-147). */
     int w4_relayout_w4a8_to_w4a16(int8_t* out, const int8_t* in, size_t k, size_t n);
 
     int w4_pack_int4(int8_t* packed, const int8_t* unpacked, size_t num_packed_bytes);

@@ -226,14 +226,23 @@ Tensor weight_only_quant_gemm(Tensor act, Tensor weight, Tensor scales, int64_t 
 }
 
 // Groupwise (GPTQ / AWQ). quant_algo bits as in the plugin: 1 bias, 2 zero, 4 pre-quant scale,
-// 8 fp8 alpha (W4A8, not supported), 16 int8 weight
+// 8 fp8 alpha (W4A8-AWQ), 16 int8 weight
 // (weightOnlyGroupwiseQuantMatmulPlugin.cpp:33-37). Optional tensors must be present exactly when
-// their bit is set.
+// their bit is set. With the fp8-alpha bit (int4 only): alpha multiplies the product, scales / zeros
+// may be float16 whatever the activation type (cast here), the weight must already have been re-laid
+// with w4_relayout_w4a8_to_w4a16, and the activations stay 16-bit.
 Tensor weight_only_groupwise_quant_gemm(Tensor act, c10::optional<Tensor> pre_quant_scale, Tensor weight, Tensor scales,
     c10::optional<Tensor> zeros, c10::optional<Tensor> bias, double alpha, int64_t quant_algo, int64_t group_size,
     bool weights_static)
 {
-    TORCH_CHECK(!(quant_algo & W4_ALGO_FP8_ALPHA), "W4A8 (FP8_ALPHA) is not supported by this library");
+    if (quant_algo & W4_ALGO_FP8_ALPHA)
+    {
+        TORCH_CHECK(!(quant_algo & W4_ALGO_INT8_WEIGHT), "W4A(fp)8 requires INT4 weight");
+        if (scales.scalar_type() != act.scalar_type())
+            scales = scales.to(act.scalar_type());
+        if (zeros.has_value() && zeros->defined() && zeros->scalar_type() != act.scalar_type())
+            zeros = zeros->to(act.scalar_type());
+    }
     TORCH_CHECK(group_size == 64 || group_size == 128, "group_size must be 64 or 128");
     auto present = [](c10::optional<Tensor> const& t) { return t.has_value() && t->defined(); };
     TORCH_CHECK(bool(quant_algo & W4_ALGO_PRE_QUANT_SCALE) == present(pre_quant_scale),

@@ -208,10 +208,20 @@ def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zer
                                        regime: int = W4_REGIME_AUTO, out=None,
                                        weights_static: bool = False) -> torch.Tensor:
     """Groupwise W4A16 / W8A16 (GPTQ / AWQ). quant_algo bits: 1 bias, 2 zero, 4 pre-quant scale,
-    8 fp8 alpha (W4A8, not supported), 16 int8 weight. Optional tensors must be present exactly
-    when their bit is set. The weight may be viewed as the activation dtype, as the plugin takes it."""
+    8 fp8 alpha (W4A8-AWQ), 16 int8 weight. Optional tensors must be present exactly when their bit is
+    set. The weight may be viewed as the activation dtype, as the plugin takes it.
+
+    With the fp8-alpha bit (int4 only) the layer is a W4A8-AWQ one: ``alpha`` multiplies the product and
+    scales / zeros may arrive as float16 whatever the activation type (they are cast). The weight must
+    already be in this library's layout (``prepare_w4a8_layer``). Activations stay 16-bit: nothing is
+    rounded to e4m3, which keeps the result inside the reference test's tolerance of its own ground
+    truth (tests/quantization/test_weight_only_groupwise_quant_matmul.py:233-245) with room to spare."""
     if quant_algo & FP8_ALPHA:
-        raise RuntimeError("W4A8 (FP8_ALPHA) is not supported by this library")
+        if quant_algo & INT8_WEIGHT:
+            raise RuntimeError("W4A(fp)8 requires INT4 weight")
+        scales = scales if scales.dtype == act.dtype else scales.to(act.dtype)
+        if zeros is not None and zeros.dtype != act.dtype:
+            zeros = zeros.to(act.dtype)
     if group_size not in (64, 128):
         raise RuntimeError("group_size must be 64 or 128")
     for bit, t, name in ((PRE_QUANT_SCALE, pre_quant_scale, "pre_quant_scale"), (ZERO, zeros, "zeros"),
@@ -221,6 +231,19 @@ def weight_only_groupwise_quant_matmul(act, pre_quant_scale, weight, scales, zer
     bits = 8 if quant_algo & INT8_WEIGHT else 4
     return _run(act, weight, scales, zeros, bias, pre_quant_scale, alpha, bits, group_size, regime, out,
                 weights_static=weights_static)
+
+
+def prepare_w4a8_layer(weight_w4a8, scales, zeros, act_dtype, device):
+    """What a W4A8-AWQ layer's constants need once, at load time: the weight, laid out by the reference
+    for fp8 activations (preprocess_weights_for_mixed_gemm with activation type float8_e4m3fn), is
+    re-laid into the layout the kernels consume, and the float16 scales / zeros are cast to the
+    activation type. Returns (weight, scales, zeros) on ``device``."""
+    from . import quantize
+    w = weight_w4a8.detach().cpu().contiguous()
+    w = quantize.relayout_w4a8_weights(w.view(torch.int8)).to(device)
+    s = scales.to(device=device, dtype=act_dtype)
+    z = None if zeros is None else zeros.to(device=device, dtype=act_dtype)
+    return w, s, z
 
 
 class _PluginBase:
@@ -316,8 +339,9 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
 
     def __init__(self, type_id: int, quant_algo: int, group_size: int, alpha: float = 1.0):
         super().__init__(type_id)
-        if quant_algo & FP8_ALPHA:
-            raise RuntimeError("W4A8 (FP8_ALPHA) is not supported by this library")
+        if (quant_algo & FP8_ALPHA) and (quant_algo & INT8_WEIGHT):
+            raise RuntimeError("W4A(fp)8 kernel requires INT4 weight!")  # the reference's assert (.cpp:213)
+        self._w4a8_cache = {}  # W4A8: constants prepared on first use, keyed by the weight's address
         if group_size not in (64, 128):
             raise RuntimeError("group_size must be 64 or 128")
         self.quant_algo, self.group_size, self.alpha = quant_algo, group_size, float(alpha)
@@ -360,9 +384,17 @@ class WeightOnlyGroupwiseQuantMatmulPlugin(_PluginBase):
             weight = inputs[self.weight_idx]
             if act.numel() == 0:
                 return 0
-            gemm_raw(act, weight, inputs[self.scales_idx], outputs[0], n=self._real_n(weight), k=act.shape[-1],
+            scales = inputs[self.scales_idx]
+            zeros = inputs[self.zeros_idx] if self.quant_algo & ZERO else None
+            if self.quant_algo & FP8_ALPHA:
+                # the engine's constants are in the reference's W4A8 form: prepare them once
+                key = weight.data_ptr()
+                if key not in self._w4a8_cache:
+                    self._w4a8_cache[key] = prepare_w4a8_layer(weight, scales, zeros, act.dtype, act.device)
+                weight, scales, zeros = self._w4a8_cache[key]
+            gemm_raw(act, weight, scales, outputs[0], n=self._real_n(weight), k=act.shape[-1],
                      weight_bits=self.bits, group_size=self.group_size,
-                     zeros=inputs[self.zeros_idx] if self.quant_algo & ZERO else None,
+                     zeros=zeros,
                      bias=inputs[self.bias_idx] if self.quant_algo & BIAS else None,
                      act_scale=inputs[self.pre_quant_scale_idx] if self.quant_algo & PRE_QUANT_SCALE else None,
                      alpha=self.alpha, regime=regime, workspace=workspace, stream=stream,

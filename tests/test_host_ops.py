@@ -176,7 +176,9 @@ def test_plugin_mirror_fields_and_serialisation():
     p = pkg.WeightOnlyQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.ops.WEIGHT_TYPE_INT4)
     assert p.get_output_dimensions((2, 3, 64), (64, 32)) == (2, 3, 64)
     assert p.supports_format_combination(1, [torch.float16, torch.int8, torch.float16, torch.float16])
-    with pytest.raises(RuntimeError):
-        pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.FP8_ALPHA, 128)
+    w4a8 = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.FP8_ALPHA | pkg.PRE_QUANT_SCALE, 128, 0.5)
+    assert (w4a8.bits, w4a8.alpha, w4a8.weight_idx) == (4, 0.5, 2)
+    with pytest.raises(RuntimeError):  # W4A8 exists for int4 weights only (the reference asserts the same)
+        pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.FP8_ALPHA | pkg.INT8_WEIGHT, 128)
     with pytest.raises(RuntimeError):
         pkg.WeightOnlyQuantMatmulPlugin(0, 1)

@@ -64,8 +64,9 @@ def test_torch_op_errors():
     a, w, s, z = _d(p["act"]), _d(p["processed"]), _d(p["scales"]), _d(p["zeros"])
     with pytest.raises(RuntimeError, match="zeros must be given exactly"):
         torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, None, None, 1.0, pkg.ZERO, 128)
-    with pytest.raises(RuntimeError, match="FP8_ALPHA"):
-        torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, z, None, 1.0, pkg.ZERO | pkg.FP8_ALPHA, 128)
+    with pytest.raises(RuntimeError, match="INT4"):  # W4A8 exists for int4 weights only
+        torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, z, None, 1.0,
+                                                          pkg.ZERO | pkg.FP8_ALPHA | pkg.INT8_WEIGHT, 128)
     with pytest.raises(RuntimeError, match="group_size"):
         torch.ops.trtllm.weight_only_groupwise_quant_gemm(a, None, w, s, z, None, 1.0, pkg.ZERO, 32)
     with pytest.raises(RuntimeError, match="wTypeId"):
@@ -183,3 +184,41 @@ def test_experts_over_3d_weights(bits, group):
     assert pkg._lib.lib().w4_gemm_device_status() == 0
     with pytest.raises(RuntimeError):
         ops.moe_gemm(act.cuda(), w3.cuda(), stack("scales"), first[:-1], weight_bits=bits, group_size=group)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 12, 300])
+def test_w4a8_awq_layer(dtype, m):
+    """A W4A8-AWQ layer as the reference's test builds it (tests/quantization/
+    test_weight_only_groupwise_quant_matmul.py:150-245): int4 weights laid out for fp8 activations,
+    float16 scales and zeros whatever the activation type, a pre-quant scale and an fp8 alpha. The
+    constants are prepared once; result against the reference test's ground truth
+    (act * alpha * pre_quant_scale) @ (q * s + z) + bias through the three public routes."""
+    from tensorrt_llm_b200 import quantize
+    k, n, group, alpha = 512, 384, 128, 0.37
+    p = make_problem(m, n, k, 4, group, dtype, zero=True, bias=True, prequant=True, seed=90 + m)
+    s16, z16 = p["scales"].to(torch.float16), p["zeros"].to(torch.float16)
+    p["scales"], p["zeros"] = s16.to(dtype), z16.to(dtype)  # what the kernels see after the cast
+    w4a8 = quantize.preprocess_weights_for_mixed_gemm(p["packed"].contiguous(), torch.quint4x2, torch.float8_e4m3fn)
+    assert not torch.equal(w4a8, p["processed"])
+    algo = pkg.FP8_ALPHA | pkg.ZERO | pkg.BIAS | pkg.PRE_QUANT_SCALE
+    ref = oracle_out(p, alpha=alpha)
+    w, s, z = ops.prepare_w4a8_layer(w4a8, s16, z16, dtype, "cuda")
+    assert torch.equal(w.cpu(), p["processed"])
+    out = ops.weight_only_groupwise_quant_matmul(_d(p["act"]), _d(p["ps"]), w, _d(s16), _d(z16), _d(p["bias"]), alpha,
+                                                 algo, group)
+    assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)
+    out2 = torch.ops.trtllm.weight_only_groupwise_quant_gemm(_d(p["act"]), _d(p["ps"]), w, _d(s16), _d(z16),
+                                                             _d(p["bias"]), alpha, algo, group)
+    assert torch.equal(out2, out)
+    # the plugin mirror takes the engine's constants as the reference would hand them over
+    plug = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(ops.TRT_HALF if dtype == torch.float16 else ops.TRT_BF16, algo,
+                                                    group, alpha)
+    plug.configure_plugin(1, 512, n, k)
+    ws = torch.empty(max(plug.get_workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    out3 = torch.empty((m, n), dtype=dtype, device="cuda")
+    inputs = [_d(p["act"]), _d(p["ps"]), _d(w4a8), _d(s16), _d(z16), _d(p["bias"])]
+    for _ in range(2):  # the second call uses the cached constants
+        assert plug.enqueue(inputs, [out3], ws) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out3, out)
