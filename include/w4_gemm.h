@@ -61,7 +61,7 @@ extern "C"
         W4_ERR_BAD_GROUP = -3,      /* group_size not in {0, 64, 128} or does not divide k */
         W4_ERR_BAD_DTYPE = -4,      /* act_dtype / weight_bits not supported */
         W4_ERR_MISALIGNED = -5,     /* a pointer misses the alignment the kernels need */
-        W4_ERR_UNSUPPORTED = -6,    /* valid in the reference, not built here (e.g. W4A8 FP8 alpha) */
+        W4_ERR_UNSUPPORTED = -6,    /* valid in the reference, not built here (e.g. W4A8 in the C++ plugin classes) */
         W4_ERR_WORKSPACE = -7,      /* workspace missing or smaller than w4_gemm_workspace_bytes() */
         W4_ERR_CUDA = -8,           /* a CUDA runtime call failed; see cudaGetLastError() */
         W4_ERR_BAD_REGIME = -9,     /* regime not valid for this shape */
