@@ -17,8 +17,11 @@
  *
  * Differences from the reference, on purpose: no tactic profiling at engine-build time (the regime
  * choice is a pure function, w4_gemm_select_regime), so the serialised tactic map is always empty
- * (count = 0) and engines are not byte-compatible with the reference's; FP8_ALPHA (W4A8) is refused
- * at creation. enqueue never throws: it returns the negative W4Status on failure.
+ * (count = 0) and engines are not byte-compatible with the reference's. W4A8-AWQ (FP8_ALPHA) is taken
+ * for float16 plugins only, with int4 weights that the engine's emitter has re-laid
+ * (w4_relayout_w4a8_to_w4a16): the scales and zeros of a W4A8 layer are float16 whatever the activation
+ * type, and a plugin cannot convert engine constants in enqueue, so bfloat16 W4A8 is refused at
+ * creation. enqueue never throws: it returns the negative W4Status on failure.
  */
 #ifndef W4_TRT_PLUGIN_H
 #define W4_TRT_PLUGIN_H
@@ -187,7 +190,9 @@ struct GroupwiseState
 
     bool valid() const
     {
-        return act_dtype_of(type_id) >= 0 && (group_size == 64 || group_size == 128) && !(quant_algo & W4_ALGO_FP8_ALPHA);
+        if ((quant_algo & W4_ALGO_FP8_ALPHA) && (type_id != kTrtHalf || (quant_algo & W4_ALGO_INT8_WEIGHT)))
+            return false; // W4A8: float16 scales must match the activation type; int4 only
+        return act_dtype_of(type_id) >= 0 && (group_size == 64 || group_size == 128);
     }
 
     int bits() const

@@ -50,8 +50,8 @@ def test_header_compiles_without_tensorrt():
 def test_groupwise_input_indices_match_python_mirror(harness, algo):
     idx = (ctypes.c_int * 5)()
     nb = harness.harness_groupwise_indices(algo, idx)
-    if algo & pkg.FP8_ALPHA:
-        return  # the C++ plugin refuses W4A8 at creation (the Python mirror prepares the constants itself)
+    if (algo & pkg.FP8_ALPHA) and (algo & pkg.INT8_WEIGHT):
+        return  # W4A8 exists for int4 weights only: refused by both layers
     m = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(ops.TRT_HALF, algo, 128)
     assert list(idx) == [m.pre_quant_scale_idx, m.weight_idx, m.scales_idx, m.zeros_idx, m.bias_idx]
     assert nb == m.nb_inputs
@@ -69,7 +69,9 @@ def test_serialisation_layout(harness):
 
 
 def test_creators_refuse_what_the_library_cannot_run(harness):
-    assert harness.harness_create_fails(1, ops.TRT_HALF, pkg.FP8_ALPHA, 128) == 1   # W4A8
+    assert harness.harness_create_fails(1, ops.TRT_BF16, pkg.FP8_ALPHA, 128) == 1   # W4A8 with bf16: fp16 scales
+    assert harness.harness_create_fails(1, ops.TRT_HALF, pkg.FP8_ALPHA | pkg.INT8_WEIGHT, 128) == 1
+    assert harness.harness_create_fails(1, ops.TRT_HALF, pkg.FP8_ALPHA | pkg.PRE_QUANT_SCALE, 128) == 0
     assert harness.harness_create_fails(1, ops.TRT_HALF, 0, 32) == 1                # group size
     assert harness.harness_create_fails(1, 0, 0, 128) == 1                          # fp32 activations
     assert harness.harness_create_fails(0, ops.TRT_HALF, 3, 0) == 1                 # weight type
@@ -121,6 +123,29 @@ def test_groupwise_enqueue_every_input_layout(harness, dtype, m, bias, zero, pre
     ref = oracle_out(p)
     assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)  # 1e-2 * max|ref|
     assert pkg._lib.lib().w4_gemm_device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [2, 40])
+def test_groupwise_enqueue_w4a8_float16(harness, m):
+    """W4A8-AWQ through the C++ plugin: float16 activations, alpha, weights re-laid by the emitter."""
+    from tensorrt_llm_b200 import quantize
+    n, k, group, alpha = 512, 1024, 128, 0.41
+    p = make_problem(m, n, k, 4, group, torch.float16, zero=True, bias=False, prequant=True, seed=m + 3)
+    w4a8 = quantize.preprocess_weights_for_mixed_gemm(p["packed"].contiguous(), torch.quint4x2, torch.float8_e4m3fn)
+    relaid = quantize.relayout_w4a8_weights(w4a8)
+    algo = pkg.FP8_ALPHA | pkg.ZERO | pkg.PRE_QUANT_SCALE
+    dev = "cuda"
+    tensors = [p["act"].to(dev), p["ps"].to(dev), relaid.to(dev), p["scales"].to(dev), p["zeros"].to(dev)]
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    ws = torch.empty(ops.workspace_bytes_max(64, n, k, group, 4, torch.float16, True) + 16, dtype=torch.uint8, device=dev)
+    ptrs = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    rc = harness.harness_run(1, ops.TRT_HALF, algo, group, alpha, 64, m, n, k, ptrs, len(tensors), out.data_ptr(),
+                             ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ref = oracle_out(p, alpha=alpha)
+    assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)
 
 
 @pytest.mark.gpu
