@@ -207,7 +207,7 @@ extern "C"
             left -= left < 16 ? left : 16;
         }
         double const gemv_us = passes16 * (weight_mb / 2.7 + 6.3) + (left > 0 ? weight_mb / 3.4 + 4.2 : 0.0);
-        double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, sms);
+        double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, sms, weight_bits);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;
     }
 
@@ -222,7 +222,7 @@ extern "C"
             r = w4_gemm_select_regime(m, n, k, group_size, weight_bits);
         if (r == W4_REGIME_GEMV)
             return 0;
-        return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale);
+        return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale, weight_bits);
     }
 
     size_t w4_gemm_workspace_bytes_max(int max_m, int n, int k, int group_size, int weight_bits, int act_dtype,

@@ -823,10 +823,10 @@ static int launch_one(W4GemmParams const& p, void const* act, DeviceInfo const& 
 template <typename T, int BITS, bool HAS_ZERO>
 static int dispatch_bm(W4GemmParams const& p, void const* act, DeviceInfo const& dev, cudaStream_t stream)
 {
-    int const bm = gemm_tc_row_tile(p.m, p.n, dev.num_sms);
+    int const bm = gemm_tc_row_tile(p.m, p.n, dev.num_sms, p.weight_bits);
     // Split-k when the tiles alone would leave most SMs idle and the caller's workspace has room
     // for the partial tiles; the unsplit kernel is a separate instantiation without any of it.
-    int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms);
+    int splits = gemm_tc_splits(p.m, p.n, p.k, dev.num_sms, p.weight_bits);
     if (splits > 1)
     {
         size_t const act_copy = (act != p.act) ? split_align(size_t(p.m) * p.k * 2) : 0;
@@ -864,19 +864,23 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 } // namespace tc
 
 
-// Microseconds one CTA spends per 128-wide k step, by row tile (measured on B200, bf16 x int4,
-// group 128): up to 192 rows the step is bound by the conversion / hand-off pipeline, not by its
-// tensor work; 256 rows leave shared memory for three stages only and the step turns latency-bound.
-static double step_us(int bm)
+// Microseconds one CTA spends per 128-wide k step, by row tile (measured on B200, bf16, group 128).
+// int4: up to 192 rows the step is bound by the conversion / hand-off pipeline, not by its tensor
+// work; 256 rows leave shared memory for three stages only and the step turns latency-bound. int8
+// stages carry 16 KB of weights instead of 8: four of them fit up to 128 rows, three at 192 rows
+// (4096 x 14336 x 4096: 546 us with 128-row tiles against 623 us with 192), two at 256.
+static double step_us(int bm, int bits)
 {
+    if (bits == 8)
+        return bm <= 128 ? 0.70 : (bm == 192 ? 1.11 : 1.9);
     return bm <= 128 ? 0.57 : (bm == 192 ? 0.70 : 1.05);
 }
 
 // Split-k factor: used when the output tiles would occupy less than half of the SMs; every work
 // item keeps at least four k steps; only for m <= 256, where the fp32 partial tiles stay small.
-int gemm_tc_splits(int m, int n, int k, int num_sms)
+int gemm_tc_splits(int m, int n, int k, int num_sms, int bits)
 {
-    int const bm = gemm_tc_row_tile(m, n, num_sms);
+    int const bm = gemm_tc_row_tile(m, n, num_sms, bits);
     long const tiles = long((n + tc::BN - 1) / tc::BN) * long((m + bm - 1) / bm);
     int const ksteps = (k + tc::BK - 1) / tc::BK;
     if (tiles * 2 > num_sms || m > 256)
@@ -895,20 +899,20 @@ static double waves(int m, int n, int bm, int num_sms, int splits = 1)
     return double((tiles + num_sms - 1) / num_sms);
 }
 
-int gemm_tc_row_tile(int m, int n, int num_sms)
+int gemm_tc_row_tile(int m, int n, int num_sms, int bits)
 {
     if (m <= 64)
         return 64;
     if (m <= 128)
         return 128;
-    if (m <= 192)
+    if (m <= 192 && bits != 8) // int8 keeps only three stages at 192 rows: let the costs decide
         return 192;
     int const cand[3] = {128, 192, 256};
     int bm = 0;
     double best = 0;
     for (int i = 0; i < 3; ++i)
     {
-        double const cost = waves(m, n, cand[i], num_sms) * step_us(cand[i]);
+        double const cost = waves(m, n, cand[i], num_sms) * step_us(cand[i], bits);
         if (!bm || cost < best)
         {
             bm = cand[i];
@@ -918,13 +922,13 @@ int gemm_tc_row_tile(int m, int n, int num_sms)
     return bm;
 }
 
-double gemm_tc_estimate_us(int m, int n, int k, int num_sms)
+double gemm_tc_estimate_us(int m, int n, int k, int num_sms, int bits)
 {
-    int const bm = gemm_tc_row_tile(m, n, num_sms);
-    int const splits = gemm_tc_splits(m, n, k, num_sms);
+    int const bm = gemm_tc_row_tile(m, n, num_sms, bits);
+    int const splits = gemm_tc_splits(m, n, k, num_sms, bits);
     int const ksteps = (k + tc::BK - 1) / tc::BK;
     int const per = (ksteps + splits - 1) / splits;
-    return 7.0 + (splits > 1 ? 3.0 : 0.0) + waves(m, n, bm, num_sms, splits) * step_us(bm) * double(per);
+    return 7.0 + (splits > 1 ? 3.0 : 0.0) + waves(m, n, bm, num_sms, splits) * step_us(bm, bits) * double(per);
 }
 
 size_t gemm_tc_workspace_min(int m, int k, int has_act_scale)
@@ -934,12 +938,12 @@ size_t gemm_tc_workspace_min(int m, int k, int has_act_scale)
     return has_act_scale ? size_t(m) * k * 2 : 0;
 }
 
-size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale)
+size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale, int bits)
 {
     // what lets the kernel use split-k as well; with less (but at least the minimum) it runs unsplit
     DeviceInfo const& dev = current_device_info();
     int const sms = dev.num_sms > 0 ? dev.num_sms : 148;
-    int const splits = gemm_tc_splits(m, n, k, sms);
+    int const splits = gemm_tc_splits(m, n, k, sms, bits);
     size_t bytes = gemm_tc_workspace_min(m, k, has_act_scale);
     if (splits > 1)
         bytes = tc::split_align(bytes) + tc::split_bytes(m, n, splits);

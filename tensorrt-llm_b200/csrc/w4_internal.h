@@ -27,12 +27,12 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
 int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream);
 // Workspace: the minimum the kernel needs (scaled activation copy), and what also allows split-k.
 size_t gemm_tc_workspace_min(int m, int k, int has_act_scale);
-size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale);
-int gemm_tc_splits(int m, int n, int k, int num_sms);
+size_t gemm_tc_workspace_bytes(int m, int n, int k, int has_act_scale, int bits);
+int gemm_tc_splits(int m, int n, int k, int num_sms, int bits);
 // Activation-row tile the tensor-core kernel uses for this problem, and its estimated duration
 // (microseconds, measured per-step costs); shared by the launcher and the regime heuristic.
-int gemm_tc_row_tile(int m, int n, int num_sms);
-double gemm_tc_estimate_us(int m, int n, int k, int num_sms);
+int gemm_tc_row_tile(int m, int n, int num_sms, int bits);
+double gemm_tc_estimate_us(int m, int n, int k, int num_sms, int bits);
 
 // out[m, k] = act[m, k] * scale[k], rounded to the element type (the reference's
 // apply_per_channel_scale, cpp/tensorrt_llm/kernels/preQuantScaleKernel.cu:43-95).
