@@ -195,8 +195,9 @@ extern "C"
         // packed weights once per 16 rows while more than 8 rows are left, then once for up to 8:
         // an 8-row pass costs 4.2 us plus the weight bytes at 3.4 TB/s (config 2: 12.1 us; 4096 x 4096
         // int4: 6.6 us), a 16-row pass 6.3 us plus the bytes at 2.7 TB/s for int4 (config 2: 17.2 us;
-        // 4096 x 1024: 6.8 us) and 1.5 us plus the bytes at 1.9 TB/s for int8, whose tiles hold a
-        // quarter of the k (4096 x 4096: 10.2 us; 4096 x 14336: 32 us). The tensor-core kernel's
+        // 4096 x 1024: 6.8 us) and 3.5 us plus the bytes at 3.2 TB/s for int8, whose narrower units let
+        // a 16-row tile cover as much k as an 8-row one (4096 x 4096: 7.8 us; 4096 x 14336: 20-23 us).
+        // The tensor-core kernel's
         // estimate comes from its own per-step costs. The SM count is the current device's (148 when
         // no device is present).
         w4::DeviceInfo const& dev = w4::current_device_info();
@@ -208,7 +209,7 @@ extern "C"
             ++passes16;
             left -= left < 16 ? left : 16;
         }
-        double const pass16_us = weight_bits == 8 ? weight_mb / 1.9 + 1.5 : weight_mb / 2.7 + 6.3;
+        double const pass16_us = weight_bits == 8 ? weight_mb / 3.2 + 3.5 : weight_mb / 2.7 + 6.3;
         double const gemv_us = passes16 * pass16_us + (left > 0 ? weight_mb / 3.4 + 4.2 : 0.0);
         double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, sms, weight_bits);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;

@@ -73,7 +73,7 @@ struct Cfg
     static constexpr int RPG = 16 / IL;                 // interleaved rows per 16-column group
     static constexpr int CK = 128 / BITS;               // k values in one 16-byte chunk
     static constexpr int UK = 4 * CK;                   // k values per warp unit (4 chunks)
-    static constexpr int UPW = MB == 1 ? 2 : 1;         // units per warp per tile
+    static constexpr int UPW = (MB == 1 || BITS == 8) ? 2 : 1; // units per warp per tile (int8 units are half as wide)
     static constexpr int KP = kWarps * UPW * UK;        // k panel covered by one tile
     static constexpr int ROW_STRIDE = 2 * KP;           // bytes of one interleaved row inside a tile
     static constexpr int TILE_BYTES = RPG * ROW_STRIDE; // 32 KB (MB = 1) or 16 KB (MB = 2)
