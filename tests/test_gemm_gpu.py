@@ -102,11 +102,12 @@ def test_linearity_at_full_size():
 
 
 @pytest.mark.parametrize("m,n,k,bits", [(1024, 4096, 4096, 4), (2048, 4096, 2048, 4), (176, 2048, 4096, 8),
-                                        (192, 2048, 4096, 8)])
+                                        (192, 2048, 4096, 8), (192, 32768, 2048, 8), (384, 16384, 1152, 8)])
 def test_odd_stage_counts_over_a_long_ring(m, n, k, bits):
-    """Row tiles whose shared-memory ring has three stages (int4 with 256 rows, int8 with 192), with
-    16 to 32 k steps: each conversion group meets a stage's barrier in every second phase only, so it
-    has to observe the phases in between as well."""
+    """Row tiles whose shared-memory ring has three stages (int4 with 256 rows; int8 with 192 rows,
+    which the cost model picks when the column tiles fill several waves), with 9 to 32 k steps, one
+    case with an odd number of steps per tile: each conversion group meets a stage in every second
+    pass of the ring only, and with an odd step count the stages it meets change from tile to tile."""
     p = make_problem(m, n, k, bits, 128, torch.bfloat16, zero=True, seed=m + bits)
     rows = list(range(0, m, 37)) + [m - 1]
     out = run_gpu(p, regime=GEMM)
