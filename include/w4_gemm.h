@@ -278,7 +278,8 @@ extern "C"
     {
         W4_ALLREDUCE_AUTO = 0,     /* by message size, the reference's rule (allreducePlugin.cpp:258-283) */
         W4_ALLREDUCE_ONE_SHOT = 1, /* push the whole partial to every peer, reduce locally */
-        W4_ALLREDUCE_TWO_SHOT = 2  /* push slices to their owners, reduce, hand the reduced slices round */
+        W4_ALLREDUCE_TWO_SHOT = 2, /* push slices to their owners, reduce, hand the reduced slices round */
+        W4_ALLREDUCE_GATHER_ONLY = 3 /* one-shot whose pushes were already made by w4_gemm_launch_push */
     };
 
     /*
@@ -324,6 +325,24 @@ extern "C"
     size_t w4_allreduce_workspace_bytes(size_t max_message_bytes, int world);
 
     int w4_allreduce(const W4AllReduceParams* p, void* stream);
+
+    /*
+     * The row-parallel decode GEMM with the first half of its all-reduce fused into the epilogue: the
+     * kernel writes its partial sums to p->out (== r->partial) AND sends them, as the flagged packets
+     * of the one-shot protocol, straight into every peer's inbox, so the reduce that follows only has
+     * to gather: call w4_allreduce with mode W4_ALLREDUCE_GATHER_ONLY next on the same stream (same r
+     * otherwise). Saves the reduce kernel's own pass over the partial sums and lets the data cross
+     * NVLink while the GEMM is still finishing. Applies to int4 weights in the decode regime without a
+     * bias (the bias belongs to the reduce: r->bias) when the message would use the one-shot packet
+     * protocol; otherwise W4_ERR_UNSUPPORTED is returned and nothing has been launched.
+     * The second half of f1 of the reference's road map (gemmAllReducePlugin fuses a dense GEMM with
+     * its all-reduce on sm_90, cpp/tensorrt_llm/plugins/gemmAllReducePlugin; never for weight-only).
+     */
+    int w4_gemm_launch_push(const W4GemmParams* p, const W4AllReduceParams* r, void* stream);
+
+    /* GEMM followed by the all-reduce of its output: w4_gemm_launch_push + gather where that applies,
+     * w4_gemm_launch + w4_allreduce (r->mode) otherwise. p->out must be r->partial. */
+    int w4_gemm_allreduce(const W4GemmParams* p, const W4AllReduceParams* r, void* stream);
 
     /* The calls of all `world` ranks as ONE cooperative launch on the current GPU: ranks[r] describes
      * rank r, every workspace pointer is local memory. For machines with fewer GPUs than ranks (tests,

@@ -26,7 +26,7 @@ EXPORTS = (
     "w4_preprocess_weights_device", "w4_symmetric_quantize_device", "w4_allreduce", "w4_allreduce_emulated",
     "w4_allreduce_workspace_bytes",
     "w4_gemm_workspace_bytes_max", "w4_gemm_run_host", "w4_gemm_launch_experts",
-    "w4_preprocess_weights_w4a8", "w4_relayout_w4a8_to_w4a16",
+    "w4_preprocess_weights_w4a8", "w4_relayout_w4a8_to_w4a16", "w4_gemm_launch_push", "w4_gemm_allreduce",
 )
 
 
@@ -49,7 +49,7 @@ W4_ONESHOT_MAX_BYTES = 1 << 20
 W4_ALLREDUCE_MAX_CTAS = 128
 W4_ALLREDUCE_LL_MAX_BYTES = 4 << 20
 W4_ERR_DEVICE_TIMEOUT = -10
-W4_ALLREDUCE_AUTO, W4_ALLREDUCE_ONE_SHOT, W4_ALLREDUCE_TWO_SHOT = 0, 1, 2
+W4_ALLREDUCE_AUTO, W4_ALLREDUCE_ONE_SHOT, W4_ALLREDUCE_TWO_SHOT, W4_ALLREDUCE_GATHER_ONLY = 0, 1, 2, 3
 
 
 class W4AllReduceParams(ctypes.Structure):
@@ -104,6 +104,8 @@ def lib() -> ctypes.CDLL:
                                                    ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                                    ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         l.w4_allreduce.argtypes = [ctypes.POINTER(W4AllReduceParams), ctypes.c_void_p]
+        l.w4_gemm_launch_push.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.POINTER(W4AllReduceParams), ctypes.c_void_p]
+        l.w4_gemm_allreduce.argtypes = [ctypes.POINTER(W4GemmParams), ctypes.POINTER(W4AllReduceParams), ctypes.c_void_p]
         l.w4_allreduce_emulated.argtypes = [ctypes.POINTER(W4AllReduceParams), ctypes.c_int, ctypes.c_void_p]
         l.w4_allreduce_workspace_bytes.restype = ctypes.c_size_t
         l.w4_allreduce_workspace_bytes.argtypes = [ctypes.c_size_t, ctypes.c_int]

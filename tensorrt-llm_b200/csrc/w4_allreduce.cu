@@ -113,6 +113,7 @@ struct Batch
     int ctas_per_rank;
     int world;
     int protocol;
+    int skip_push; // one-shot packets only: the GEMM in front has already sent this rank's packets
     size_t pkt_slot, plain_slot, copy_bytes;
     unsigned long long timeout_ns;
 };
@@ -339,7 +340,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(Batch const b)
     if (b.protocol == kOneShotPackets)
     {
         size_t const v0 = V * size_t(c) / C, v1 = V * size_t(c + 1) / C;
-        for (size_t i = v0 + threadIdx.x; i < v1; i += blockDim.x)
+        for (size_t i = v0 + threadIdx.x; !b.skip_push && i < v1; i += blockDim.x)
         {
             uint4 const v = partial[i];
 #pragma unroll
@@ -490,7 +491,8 @@ static int check_one(W4AllReduceParams const& p)
         return W4_ERR_BAD_SHAPE;
     if (p.act_dtype != W4_DTYPE_FP16 && p.act_dtype != W4_DTYPE_BF16)
         return W4_ERR_BAD_DTYPE;
-    if (p.mode != W4_ALLREDUCE_AUTO && p.mode != W4_ALLREDUCE_ONE_SHOT && p.mode != W4_ALLREDUCE_TWO_SHOT)
+    if (p.mode != W4_ALLREDUCE_AUTO && p.mode != W4_ALLREDUCE_ONE_SHOT && p.mode != W4_ALLREDUCE_TWO_SHOT
+        && p.mode != W4_ALLREDUCE_GATHER_ONLY)
         return W4_ERR_BAD_REGIME;
     if (p.count % 8 != 0 || p.n <= 0 || p.n % 8 != 0 || p.count % size_t(p.n) != 0)
         return W4_ERR_BAD_SHAPE;
@@ -511,7 +513,7 @@ static int check_one(W4AllReduceParams const& p)
 // (allreducePlugin.cpp:258-283): always up to 2 ranks, below 1 MB up to 4, below 500 kB beyond.
 static int pick_two_shot(int mode, size_t bytes, int world)
 {
-    if (world == 1 || mode == W4_ALLREDUCE_ONE_SHOT)
+    if (world == 1 || mode == W4_ALLREDUCE_ONE_SHOT || mode == W4_ALLREDUCE_GATHER_ONLY)
         return 0;
     if (mode == W4_ALLREDUCE_TWO_SHOT)
         return 1;
@@ -520,6 +522,25 @@ static int pick_two_shot(int mode, size_t bytes, int world)
     if (world <= 2)
         return 0;
     return bytes < (world <= 4 ? size_t(1000000) : size_t(500000)) ? 0 : 1;
+}
+
+static bool layout_from_workspace(W4AllReduceParams const& p, size_t bytes, Layout* l)
+{
+    // The workspace was sized for some largest message: recover the layout from its size (capacity is
+    // monotone in the largest message, so search for the largest one whose layout fits).
+    size_t lo = 0, hi = size_t(1) << 34;
+    while (lo < hi)
+    {
+        size_t const mid = lo + (hi - lo + 1) / 2;
+        if (layout_for(mid, p.world).total <= p.workspace_bytes)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    if (lo < bytes || p.workspace_bytes <= kHeaderBytes)
+        return false;
+    *l = layout_for(lo, p.world);
+    return true;
 }
 
 static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStream_t stream)
@@ -533,25 +554,11 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
     if (!two_shot && bytes > kOneShotMax)
         return W4_ERR_UNSUPPORTED; // a one-shot message must fit one sender slot
     b.protocol = bytes > kPacketMax ? kTwoShotFlags : (two_shot ? kTwoShotPackets : kOneShotPackets);
-    // The workspace was sized for some largest message: recover the layout from its size.
-    size_t const body = p0.workspace_bytes > kHeaderBytes ? p0.workspace_bytes - kHeaderBytes : 0;
+    b.skip_push = p0.mode == W4_ALLREDUCE_GATHER_ONLY ? 1 : 0;
     // The caller passes what w4_allreduce_workspace_bytes(max_bytes, world) returned.
     Layout l{};
-    {
-        // capacity is monotone in max_bytes: find the largest max_bytes whose layout fits (binary search)
-        size_t lo = 0, hi = size_t(1) << 34;
-        while (lo < hi)
-        {
-            size_t const mid = lo + (hi - lo + 1) / 2;
-            if (layout_for(mid, p0.world).total <= p0.workspace_bytes)
-                lo = mid;
-            else
-                hi = mid - 1;
-        }
-        if (lo < bytes || body == 0)
-            return W4_ERR_WORKSPACE;
-        l = layout_for(lo, p0.world);
-    }
+    if (!layout_from_workspace(p0, bytes, &l))
+        return W4_ERR_WORKSPACE;
     b.pkt_slot = l.pkt_slot;
     b.plain_slot = l.plain_slot;
     b.copy_bytes = l.copy_bytes;
@@ -630,6 +637,27 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
 }
 
 } // namespace ar
+
+bool allreduce_push_target(W4AllReduceParams const& r, PushTarget* t)
+{
+    if (ar::check_one(r) != W4_OK || r.world < 2)
+        return false;
+    size_t const bytes = r.count * 2;
+    if (r.mode == W4_ALLREDUCE_TWO_SHOT || bytes > ar::kOneShotMax || ar::pick_two_shot(r.mode, bytes, r.world) != 0)
+        return false; // only the one-shot packet protocol takes packets from the GEMM
+    ar::Layout l{};
+    if (!ar::layout_from_workspace(r, bytes, &l))
+        return false;
+    for (int i = 0; i < W4_MAX_RANKS; ++i)
+        t->ws[i] = i < r.world ? static_cast<uint8_t*>(r.workspace[i]) : nullptr;
+    t->rank = r.rank;
+    t->world = r.world;
+    t->pkt_slot = l.pkt_slot;
+    t->copy_bytes = l.copy_bytes;
+    t->header_bytes = ar::kHeaderBytes;
+    return true;
+}
+
 } // namespace w4
 
 extern "C" size_t w4_allreduce_workspace_bytes(size_t max_message_bytes, int world)

@@ -262,6 +262,42 @@ extern "C"
         return w4::launch_gemm_tc(*p, s);
     }
 
+    int w4_gemm_launch_push(const W4GemmParams* p, const W4AllReduceParams* r, void* stream)
+    {
+        if (!p || !r)
+            return W4_ERR_NULL_POINTER;
+        // Only the decode kernel on int4 weights has the pushing epilogue, and only the one-shot packet
+        // protocol of the all-reduce takes packets from it; the bias belongs to the reduce. (Asked
+        // before the validation, which would demand the tensor-core kernel's workspace.)
+        if (p->m <= 0 || p->weight_bits != 4 || p->bias || resolve_regime(*p) != W4_REGIME_GEMV)
+            return W4_ERR_UNSUPPORTED;
+        int const rc = w4_gemm_validate(p);
+        if (rc != W4_OK)
+            return rc;
+        if (p->out != r->partial || r->count != size_t(p->m) * size_t(p->n) || r->n != p->n
+            || r->act_dtype != p->act_dtype)
+            return W4_ERR_BAD_SHAPE;
+        w4::PushTarget t{};
+        if (!w4::allreduce_push_target(*r, &t))
+            return W4_ERR_UNSUPPORTED;
+        return w4::launch_gemv(*p, static_cast<cudaStream_t>(stream), &t);
+    }
+
+    int w4_gemm_allreduce(const W4GemmParams* p, const W4AllReduceParams* r, void* stream)
+    {
+        if (!p || !r)
+            return W4_ERR_NULL_POINTER;
+        int rc = w4_gemm_launch_push(p, r, stream);
+        W4AllReduceParams q = *r;
+        if (rc == W4_OK)
+            q.mode = W4_ALLREDUCE_GATHER_ONLY;
+        else if (rc == W4_ERR_UNSUPPORTED)
+            rc = w4_gemm_launch(p, stream);
+        if (rc != W4_OK)
+            return rc;
+        return w4_allreduce(&q, stream);
+    }
+
     int w4_gemm_launch_experts(const W4GemmParams* p, int num_experts, const int* expert_first_row, void* stream)
     {
         if (!p || !expert_first_row)

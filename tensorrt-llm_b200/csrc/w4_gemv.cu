@@ -156,6 +156,8 @@ struct Args
     int depth;            // tiles kept in flight ahead of the one being consumed
     int red_bytes;        // shared memory for the cross-warp partial sums
     int weights_static;   // weights / scales / zeros were complete before the preceding kernel started
+    PushTarget push;      // world > 0: the epilogue also sends the results to the peers as flagged packets
+    int push_row0;        // row of the whole call that this pass's row 0 is
 };
 
 // Shared flag: once any wait in the CTA timed out, every later wait returns at once.
@@ -729,6 +731,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             int const lg = BITS == 4 ? col_in >> 1 : col_in & 7;
             int const chalf = BITS == 4 ? col_in & 1 : col_in >> 3;
             int const irow = r0 + (cg0 + cb) * C::RPG + col_in / C::IL;
+            int const col = (r0 + (cg0 + cb) * C::RPG) * C::IL + col_in;
+            uint32_t v16 = 0;
+            bool valid = false;
             if (row < a.m && irow < r1)
             {
                 int const mb = row >> 3, lt = (row & 7) >> 1, c = chalf * 2 + (row & 1);
@@ -737,11 +742,35 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                 for (int w = 0; w < kWarps; ++w)
                     sum += src[w * MB * 4 * 8 * MT];
-                int const col = (r0 + (cg0 + cb) * C::RPG) * C::IL + col_in;
                 float v = a.alpha * sum;
                 if (a.bias)
                     v += P::to_float(static_cast<uint16_t const*>(a.bias)[col]);
-                static_cast<uint16_t*>(a.out)[size_t(row) * a.n + col] = P::from_float(v);
+                v16 = P::from_float(v);
+                static_cast<uint16_t*>(a.out)[size_t(row) * a.n + col] = uint16_t(v16);
+                valid = true;
+            }
+            if (BITS == 4 && a.push.world > 0)
+            {
+                // Fused all-reduce, first half: four neighbouring lanes hold four neighbouring
+                // columns of one row (one interleaved row of this CTA, so all four are valid or none
+                // is); the first of them sends them as one flagged 16-byte packet
+                // {2 values, call number, 2 values, call number} into its slot of every peer's inbox.
+                // (All 32 lanes are here: the loop bound is a multiple of the warp size.)
+                uint32_t const pair = v16 | (__shfl_down_sync(0xffffffffu, v16, 1) << 16);
+                uint32_t const pair1 = __shfl_down_sync(0xffffffffu, pair, 2);
+                if (valid && (col_in & 3) == 0)
+                {
+                    uint32_t const epoch = *reinterpret_cast<volatile uint32_t const*>(a.push.ws[a.push.rank]) + 1u;
+                    size_t const pkt = (size_t(a.push_row0 + row) * a.n + size_t(col)) >> 2;
+                    size_t const off = a.push.header_bytes + size_t(epoch & 1u) * a.push.copy_bytes
+                        + size_t(a.push.rank) * a.push.pkt_slot + pkt * 16;
+#pragma unroll
+                    for (int r = 0; r < W4_MAX_RANKS; ++r)
+                        if (r < a.push.world && r != a.push.rank)
+                            asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(a.push.ws[r] + off),
+                                         "r"(pair), "r"(epoch), "r"(pair1), "r"(epoch)
+                                         : "memory");
+                }
             }
         }
         if (cg0 + batch < num_cg)
@@ -907,7 +936,7 @@ static int dispatch_bits(Args const& a, int bits, int mb, DeviceInfo const& dev,
 
 } // namespace gemv
 
-int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
+int launch_gemv(W4GemmParams const& p, cudaStream_t stream, PushTarget const* push)
 {
     DeviceInfo const& dev = current_device_info();
     if (dev.num_sms <= 0)
@@ -936,6 +965,13 @@ int launch_gemv(W4GemmParams const& p, cudaStream_t stream)
         a.num_groups = p.group_size ? p.k / p.group_size : 1;
         a.num_rows = p.n / (p.weight_bits == 4 ? 4 : 2);
         a.weights_static = (p.flags & W4_GEMM_WEIGHTS_STATIC) ? 1 : 0;
+        if (push && p.weight_bits == 4)
+        {
+            a.push = *push;
+            // rows of a later pass land further down in the peers' inboxes: packet index counts from
+            // the first row of the whole call
+            a.push_row0 = m0;
+        }
         int const rc = p.act_dtype == W4_DTYPE_FP16 ? gemv::dispatch_bits<__half>(a, p.weight_bits, mb, dev, stream)
                                                     : gemv::dispatch_bits<__nv_bfloat16>(a, p.weight_bits, mb, dev, stream);
         if (rc != W4_OK)

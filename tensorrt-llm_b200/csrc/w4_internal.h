@@ -21,7 +21,21 @@ struct DeviceInfo
 DeviceInfo const& current_device_info();
 
 // Streaming decode kernel: handles any m by passes of at most 8 rows. Returns a W4Status.
-int launch_gemv(W4GemmParams const& p, cudaStream_t stream);
+// Where the decode kernel's epilogue sends its results when the all-reduce is fused into it: the
+// packet inbox (slot `rank`) in every rank's all-reduce workspace. world == 0: no push.
+struct PushTarget
+{
+    uint8_t* ws[W4_MAX_RANKS];
+    int rank;
+    int world;
+    size_t pkt_slot;   // bytes of one sender's packet slot
+    size_t copy_bytes; // bytes of one copy of the workspace's data areas
+    size_t header_bytes;
+};
+int launch_gemv(W4GemmParams const& p, cudaStream_t stream, PushTarget const* push = nullptr);
+// Fills `t` for the one-shot packet protocol of this all-reduce call; false when the call would not
+// use that protocol (size, mode) or its arguments are not valid.
+bool allreduce_push_target(W4AllReduceParams const& r, PushTarget* t);
 
 // tcgen05 tensor-core kernel. Returns a W4Status.
 int launch_gemm_tc(W4GemmParams const& p, cudaStream_t stream);

@@ -450,6 +450,31 @@ def allreduce(partial: torch.Tensor, workspace_ptrs, workspace_bytes: int, out: 
     _lib.check(rc, "allreduce")
 
 
+def gemm_push(act, weight, scales, partial, workspace_ptrs, workspace_bytes: int, rank: int, *, n: int, k: int,
+              group_size: int, zeros=None, act_scale=None, alpha: float = 1.0, weights_static: bool = False,
+              regime: int = W4_REGIME_GEMV, stream=None) -> bool:
+    """w4_gemm_launch_push: the int4 decode GEMM writes ``partial`` and sends it, as the packets of the
+    one-shot all-reduce, into every peer's inbox. Follow it with ``allreduce(partial, ..., mode=
+    W4_ALLREDUCE_GATHER_ONLY)``. Returns False, having launched nothing, when the fused form does not
+    apply to this problem (the caller then runs ``gemm_raw`` and an ordinary ``allreduce``). ``regime``
+    defaults to the decode kernel, the only one with a pushing epilogue; W4_REGIME_AUTO lets the cost
+    model refuse row counts it would give to the tensor-core kernel."""
+    m = act.numel() // k if k else 0
+    g = W4GemmParams(
+        act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros), bias=None,
+        out=_p(partial), alpha=float(alpha), m=m, n=n, k=k, group_size=group_size, weight_bits=4,
+        act_dtype=_DTYPES[act.dtype], regime=regime, workspace=None, workspace_bytes=0,
+        flags=_lib.W4_GEMM_WEIGHTS_STATIC if weights_static else 0)
+    r = _allreduce_params(partial, workspace_ptrs, workspace_bytes, partial, n, rank, None, _lib.W4_ALLREDUCE_AUTO, 0)
+    s = stream if stream is not None else torch.cuda.current_stream(act.device)
+    with torch.cuda.device(act.device):
+        rc = _lib.lib().w4_gemm_launch_push(ctypes.byref(g), ctypes.byref(r), ctypes.c_void_p(s.cuda_stream))
+    if rc == _lib.W4_ERR_UNSUPPORTED:
+        return False
+    _lib.check(rc, "w4_gemm_launch_push")
+    return True
+
+
 def allreduce_emulated(partials, workspaces, outs, n: int, biases=None, mode: int = _lib.W4_ALLREDUCE_AUTO,
                        timeout_ms: int = 0, stream=None) -> None:
     """All ranks of an all-reduce as one cooperative launch on the current GPU (every buffer local):

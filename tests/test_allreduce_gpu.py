@@ -160,3 +160,74 @@ def test_real_gpus_against_nccl():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "PEER_ALLREDUCE_OK" in r.stdout
+
+
+@pytest.mark.parametrize("world,m", [(2, 1), (4, 5), (8, 1), (8, 12), (8, 20)])
+def test_gemm_epilogue_push_then_gather(world, m):
+    """The fused form of a row-parallel decode step on emulated ranks: every rank's int4 decode GEMM
+    writes its partial sums locally and pushes them as flagged packets into all inboxes
+    (w4_gemm_launch_push; the ranks' GEMMs are separate launches, they wait for nobody), then one
+    cooperative launch gathers on all ranks (W4_ALLREDUCE_GATHER_ONLY). Two rounds with fresh
+    activations (both copies of the inbox); 20 rows take a 16-row and a 4-row pass."""
+    from _cases import make_problem, oracle_out, max_err
+    from oracle import woq_oracle as oracle
+    n, k_local, group = 1024, 512, 128
+    dev = "cuda"
+    probs = [make_problem(m, n, k_local, 4, group, torch.bfloat16, zero=True, prequant=True, seed=300 + 10 * world + r)
+             for r in range(world)]
+    nws = ops.allreduce_workspace_bytes(1 << 20, world)
+    wss = [torch.zeros(nws, dtype=torch.uint8, device=dev) for _ in range(world)]
+    ptrs = [w.data_ptr() for w in wss]
+    partials = [torch.zeros(m, n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    outs = [torch.zeros(m, n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    bias = torch.randn(n, device=dev).to(torch.bfloat16)
+    d = lambda t: t.to(dev)
+    dev_t = [{key: d(p[key]) for key in ("processed", "scales", "zeros", "ps")} for p in probs]
+    for rnd in range(2):
+        acts = [d((p["act"].float() * (1.0 - 1.5 * rnd)).to(torch.bfloat16)) for p in probs]
+        for r in range(world):
+            t = dev_t[r]
+            pushed = ops.gemm_push(acts[r], t["processed"], t["scales"], partials[r], ptrs, nws, r, n=n, k=k_local,
+                                   group_size=group, zeros=t["zeros"], act_scale=t["ps"])
+            assert pushed
+        ops.allreduce_emulated(partials, wss, outs, n, biases=[bias] * world, mode=L.W4_ALLREDUCE_GATHER_ONLY)
+        torch.cuda.synchronize()
+        for r in range(world):  # every rank's GEMM against the oracle
+            ref = oracle_out(dict(probs[r], act=acts[r].cpu()))
+            assert max_err(partials[r].cpu(), ref) <= oracle.tolerance(ref)
+        ref = _expected(partials, bias)
+        for r in range(world):
+            assert torch.equal(outs[r], ref), f"round {rnd}, rank {r}"
+    assert [int(w[:4].view(torch.int32)[0]) for w in wss] == [2] * world
+    assert L.lib().w4_gemm_device_status() == 0
+    # an ordinary call afterwards continues the same sequence of call numbers
+    ops.allreduce_emulated(partials, wss, outs, n)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], _expected(partials, None))
+
+
+def pkg_regime_auto():
+    import tensorrt_llm_b200 as pkg
+    return pkg.W4_REGIME_AUTO
+
+
+def test_push_is_refused_where_it_does_not_apply():
+    from _cases import make_problem
+    dev = "cuda"
+    d = lambda t: t.to(dev)
+    nws = ops.allreduce_workspace_bytes(1 << 20, 2)
+    ws = torch.zeros(nws, dtype=torch.uint8, device=dev)
+    p8 = make_problem(1, 1024, 512, 8, 128, torch.bfloat16, zero=True, seed=1)  # int8: no pushing epilogue
+    out = torch.zeros(1, 1024, dtype=torch.bfloat16, device=dev)
+    from tensorrt_llm_b200._lib import W4GemmParams
+    import ctypes
+    par = W4GemmParams(act=d(p8["act"]).data_ptr(), weight=d(p8["processed"]).data_ptr(), scales=d(p8["scales"]).data_ptr(),
+                       zeros=d(p8["zeros"]).data_ptr(), out=out.data_ptr(), alpha=1.0, m=1, n=1024, k=512, group_size=128,
+                       weight_bits=8, act_dtype=1, regime=0)
+    r = ops._allreduce_params(out, [ws.data_ptr()] * 2, nws, out, 1024, 0, None, L.W4_ALLREDUCE_AUTO, 0)
+    rc = L.lib().w4_gemm_launch_push(ctypes.byref(par), ctypes.byref(r), None)
+    assert rc == L.W4_ERR_UNSUPPORTED
+    p4 = make_problem(64, 1024, 512, 4, 128, torch.bfloat16, zero=True, seed=2)  # 64 rows: tensor-core regime
+    big = torch.zeros(64, 1024, dtype=torch.bfloat16, device=dev)
+    assert not ops.gemm_push(d(p4["act"]), d(p4["processed"]), d(p4["scales"]), big, [ws.data_ptr()] * 2, nws, 0, n=1024,
+                             k=512, group_size=128, zeros=d(p4["zeros"]), regime=pkg_regime_auto())
