@@ -770,11 +770,23 @@ def tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2
                     peer.reduce(y_peer)
                     torch.cuda.synchronize()
                     entry["parity_peer_bit_exact"] = bool(max_over_ranks(0.0 if torch.equal(y_peer, expect) else 1.0) == 0.0)
+                    # the fused form (decode sizes): the GEMM's epilogue pushes, the reduce only gathers
+                    y_peer.zero_()
+                    fused = ops.gemm_push(x, w, s, peer.partial(m, n_loc), peer.ptrs, peer.ws_bytes, peer.rank,
+                                          n=n_loc, k=k_loc, group_size=group_size, zeros=z, weights_static=True,
+                                          regime=pkg.W4_REGIME_AUTO)
+                    if fused:
+                        peer.reduce(y_peer, mode=pkg._lib.W4_ALLREDUCE_GATHER_ONLY)
+                        torch.cuda.synchronize()
+                        entry["parity_fused_bit_exact"] = bool(
+                            max_over_ranks(0.0 if torch.equal(y_peer, expect) else 1.0) == 0.0)
+                    entry["fused_applies"] = bool(fused)
                     del y_peer
                 del y_nccl, expect
             entry["parity_ok"] = bool(entry["parity_gemm_err_frac_of_max"] <= 1e-2
                                       and entry.get("parity_nccl_err_frac_of_max", 0.0) <= 2e-2
-                                      and entry.get("parity_peer_bit_exact", True))
+                                      and entry.get("parity_peer_bit_exact", True)
+                                      and entry.get("parity_fused_bit_exact", True))
             # ---- eager timings with an L2 flush between repetitions
             t_gemm, t_ar = [], []
             for _ in range(reps):
@@ -812,8 +824,14 @@ def tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2
                     gemm(peer.partial(m, n_loc))
                     peer.reduce(y2)
 
+                def step_fused():
+                    ops.gemm_push(x, w, s, peer.partial(m, n_loc), peer.ptrs, peer.ws_bytes, peer.rank, n=n_loc, k=k_loc,
+                                  group_size=group_size, zeros=z, weights_static=True)
+                    peer.reduce(y2, mode=pkg._lib.W4_ALLREDUCE_GATHER_ONLY)
+
                 steps = (("gemm_only", gemm), ("gemm_plus_nccl", step_nccl)) + (
-                    (("gemm_plus_peer", step_peer),) if use_peer else ())
+                    (("gemm_plus_peer", step_peer),) if use_peer else ()) + (
+                    (("gemm_plus_peer_fused", step_fused),) if use_peer and entry.get("fused_applies") else ())
                 for label, fn in steps:
                     try:
                         st = torch.cuda.Stream(device=device)

@@ -192,11 +192,15 @@ class WeightOnlyRowLinear(_ShardedLinear):
         if (peer is not None and all_reduce and self.mapping.tp_size > 1 and peer.fits(nbytes)
                 and self.matmul is None and self.group_size != 0):
             part = peer.partial(m, self.n_local)
+            y = torch.empty(x_local.shape[:-1] + (self.n_local,), dtype=x_local.dtype, device=x_local.device)
+            # decode sizes on int4 weights: the GEMM's epilogue pushes its results to the peers itself
+            # and the reduce only gathers
+            if self.bits == 4 and m <= 16 and peer.gemm_push(x_local, self, part):
+                return peer.reduce(y, bias=self.bias, mode=_lib.W4_ALLREDUCE_GATHER_ONLY)
             algo = (_lib.INT8_WEIGHT if self.bits == 8 else 0) | (_lib.ZERO if self.zeros is not None else 0) \
                 | (_lib.PRE_QUANT_SCALE if self.pre_quant_scale is not None else 0)
             ops.weight_only_groupwise_quant_matmul(x_local, self.pre_quant_scale, self.weight, self.scales, self.zeros,
                                                    None, 1.0, algo, self.group_size, out=part)
-            y = torch.empty(x_local.shape[:-1] + (self.n_local,), dtype=x_local.dtype, device=x_local.device)
             return peer.reduce(y, bias=self.bias)
         y = self._gemm(x_local, with_bias=False)
         if all_reduce and self.mapping.tp_size > 1:
@@ -249,6 +253,13 @@ class PeerAllReduce:
         if nbytes > self.max_bytes:
             raise RuntimeError("message too large for this PeerAllReduce")
         return self._partial[:nbytes].view(self.dtype).view(m, n)
+
+    def gemm_push(self, x_local, layer, part, weights_static: bool = True) -> bool:
+        """The layer's int4 decode GEMM into ``part`` with its results pushed to the peers (see
+        ``ops.gemm_push``); False when the fused form does not apply and nothing was launched."""
+        return ops.gemm_push(x_local, layer.weight, layer.scales, part, self.ptrs, self.ws_bytes, self.rank,
+                             n=layer.n_local, k=x_local.shape[-1], group_size=layer.group_size, zeros=layer.zeros,
+                             act_scale=layer.pre_quant_scale, weights_static=weights_static)
 
     def reduce(self, out: torch.Tensor, bias=None, mode: int = _lib.W4_ALLREDUCE_AUTO, timeout_ms: int = 0,
                partial: Optional[torch.Tensor] = None) -> torch.Tensor:

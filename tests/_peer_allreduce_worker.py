@@ -1,7 +1,8 @@
 """Child process of tests/test_allreduce_gpu.py (one per GPU, started by torch.distributed.run):
 a row-parallel W4A16 layer whose partial sums are reduced by the library's peer-memory kernel,
 compared with the same layer reduced by NCCL over several calls and sizes (one-shot and two-shot
-forms), then a CUDA graph of GEMM + reduce steps replayed several times. Plain peer loads and
+forms; up to 16 rows through the fused form, whose GEMM pushes its results itself), then CUDA graphs
+of GEMM + reduce steps, unfused and fused, replayed several times. Plain peer loads and
 stores only; NVLS is off in the parent's environment."""
 import os
 import sys
@@ -82,6 +83,30 @@ def main():
             torch.cuda.synchronize()
             err = float((y.float() - ref.float()).abs().max())
             assert err <= 4 * 2.0 ** -8 * float(ref.float().abs().max()), (it, err)
+    # The same with the fused form: the GEMM's epilogue pushes its results to the peers, the reduce only
+    # gathers (what layer(x, peer=peer) does by itself for up to 16 rows).
+    def fused_step():
+        assert peer.gemm_push(x_loc, layer, peer.partial(m, n))
+        peer.reduce(y, bias=layer.bias, mode=pkg._lib.W4_ALLREDUCE_GATHER_ONLY)
+
+    with torch.cuda.stream(st):
+        fused_step()
+        st.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            fused_step()
+            fused_step()
+            fused_step()
+        for it in range(5):
+            x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+            x_loc.copy_(tp.split(x, world, rank, dim=1))
+            graph.replay()
+            st.synchronize()
+            ref = layer(x_loc)  # NCCL
+            torch.cuda.synchronize()
+            err = float((y.float() - ref.float()).abs().max())
+            assert err <= 4 * 2.0 ** -8 * float(ref.float().abs().max()), ("fused", it, err)
     assert pkg._lib.lib().w4_gemm_device_status() == 0
     dist.barrier()
     if rank == 0:
