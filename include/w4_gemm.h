@@ -2,7 +2,8 @@
  * C ABI of the B200 weight-only quantised GEMM (W4A16 / W8A16).
  *
  * Every entry point is plain C: pointers, sizes, ints. Nothing here allocates device memory,
- * keeps a caller's pointer after the call returns, synchronises the stream or throws; every
+ * keeps a caller's pointer after the call returns, synchronises the stream (w4_gemm_run_host apart,
+ * whose job that is) or throws; every
  * function that can fail returns a W4Status (0 = success, negative = error) and
  * w4_status_string() names it.
  *
@@ -38,6 +39,18 @@
  *                              (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:407), as a
  *                              peer-memory kernel in the manner of the reference's one-shot / two-shot
  *                              kernels (cpp/tensorrt_llm/kernels/customAllReduceKernels.cu:1307,1426).
+ *   w4_gemm_launch_push / w4_gemm_allreduce
+ *                            - the decode GEMM with the first half of that all-reduce in its epilogue;
+ *                              the reference fuses a GEMM with its all-reduce for dense layers on sm_90
+ *                              only (cpp/tensorrt_llm/plugins/gemmAllReducePlugin), never on this path.
+ *   w4_preprocess_weights_w4a8 / w4_relayout_w4a8_to_w4a16
+ *                            - preprocess_weights_for_mixed_gemm with QuantType::W4_AFP8
+ *                              (cutlass_preprocessors.cpp:114-116) and its conversion into the layout
+ *                              the kernels consume (W4A8-AWQ layers).
+ *   w4_gemm_launch_experts   - one GEMM per expert over 3-D weights
+ *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:136-147 lays them out).
+ *   w4_gemm_run_host, w4_gemm_launch_static_scratch
+ *                            - no counterpart: host buffers in and out; no workspace from the caller.
  *   w4_pack_int4 / w4_unpack_int4
  *                            - pack_int8_tensor_to_packed_int4 / unpack_int4_packed_tensor_to_int8
  *                              (cpp/tensorrt_llm/thop/weightOnlyQuantOp.cpp:284-353).
