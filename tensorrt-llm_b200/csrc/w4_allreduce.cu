@@ -21,6 +21,8 @@
 //       adds the world copies (rank order, fp32, + bias), writes its own output and pushes the rounded
 //       result to every peer's second inbox, where the peers poll for it. Each rank sends 2 * bytes
 //       instead of (world - 1) * bytes.
+//     In W4_ALLREDUCE_GATHER_ONLY mode the one-shot pushes are skipped: the decode GEMM in front has
+//     already sent this rank's results as packets from its epilogue (w4_gemm_launch_push).
 //   Larger messages (bandwidth-bound) use the two-shot scheme with plain data and per-chunk arrival
 //   flags: push slices (system fence, release store of the call number into flag (sender, chunk) at
 //   the owner), reduce, publish in the owner's `reduced` buffer (second flag set), pull. These use
