@@ -353,8 +353,15 @@ extern "C"
      */
     int w4_gemm_launch_push(const W4GemmParams* p, const W4AllReduceParams* r, void* stream);
 
-    /* GEMM followed by the all-reduce of its output: w4_gemm_launch_push + gather where that applies,
-     * w4_gemm_launch + w4_allreduce (r->mode) otherwise. p->out must be r->partial. */
+    /* GEMM followed by the all-reduce of its output, in the most fused form that applies:
+     *   - up to 16 rows, int4, decode regime, one-shot packet size: ONE kernel. The decode kernel's
+     *     epilogue pushes its results into every rank's inbox, collects the peers' packets for the
+     *     columns it owns (bounded wait, r->timeout_ms), adds them in rank order in fp32 (+ r->bias),
+     *     writes r->out and advances the workspace's call number. r->partial is not written.
+     *   - more rows in the decode regime: w4_gemm_launch_push, then the gather-only reduce;
+     *   - otherwise: w4_gemm_launch, then w4_allreduce (r->mode).
+     * p->out must be r->partial; p->bias must be NULL (the bias of a row-parallel layer is r->bias).
+     * All ranks must make the same call with the same shapes, as with any collective. */
     int w4_gemm_allreduce(const W4GemmParams* p, const W4AllReduceParams* r, void* stream);
 
     /* The calls of all `world` ranks as ONE cooperative launch on the current GPU: ranks[r] describes

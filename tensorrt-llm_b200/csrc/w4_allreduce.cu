@@ -642,7 +642,7 @@ static int launch(W4AllReduceParams const* ranks, int ranks_in_launch, cudaStrea
 
 bool allreduce_push_target(W4AllReduceParams const& r, PushTarget* t)
 {
-    if (ar::check_one(r) != W4_OK || r.world < 2)
+    if (ar::check_one(r) != W4_OK)
         return false;
     size_t const bytes = r.count * 2;
     if (r.mode == W4_ALLREDUCE_TWO_SHOT || bytes > ar::kOneShotMax || ar::pick_two_shot(r.mode, bytes, r.world) != 0)
@@ -657,6 +657,9 @@ bool allreduce_push_target(W4AllReduceParams const& r, PushTarget* t)
     t->pkt_slot = l.pkt_slot;
     t->copy_bytes = l.copy_bytes;
     t->header_bytes = ar::kHeaderBytes;
+    t->gather = 0;
+    t->bias = nullptr;
+    t->timeout_ns = r.timeout_ms > 0 ? (unsigned long long) (r.timeout_ms) * 1000000ull : 2000000000ull;
     return true;
 }
 

@@ -287,6 +287,25 @@ extern "C"
     {
         if (!p || !r)
             return W4_ERR_NULL_POINTER;
+        // Up to 16 rows are one launch of the decode kernel: it can do the whole call itself - push
+        // its results, collect the peers', add and write r->out - and advance the call number.
+        if (p->m > 0 && p->m <= 16 && p->weight_bits == 4 && !p->bias && resolve_regime(*p) == W4_REGIME_GEMV
+            && p->out == r->partial && r->count == size_t(p->m) * size_t(p->n) && r->n == p->n
+            && r->act_dtype == p->act_dtype && r->out)
+        {
+            w4::PushTarget t{};
+            if (w4::allreduce_push_target(*r, &t))
+            {
+                int const vrc = w4_gemm_validate(p);
+                if (vrc != W4_OK)
+                    return vrc;
+                t.gather = 1;
+                t.bias = r->bias;
+                W4GemmParams g = *p;
+                g.out = r->out;
+                return w4::launch_gemv(g, static_cast<cudaStream_t>(stream), &t);
+            }
+        }
         int rc = w4_gemm_launch_push(p, r, stream);
         W4AllReduceParams q = *r;
         if (rc == W4_OK)

@@ -175,7 +175,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 1)
     gemv_kernel(Args const a, __grid_constant__ CUtensorMap const tm_scales, __grid_constant__ CUtensorMap const tm_zeros,
         __grid_constant__ CUtensorMap const tm_w)
@@ -746,10 +746,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (a.bias)
                     v += P::to_float(static_cast<uint16_t const*>(a.bias)[col]);
                 v16 = P::from_float(v);
-                static_cast<uint16_t*>(a.out)[size_t(row) * a.n + col] = uint16_t(v16);
+                if (!(PUSH && a.push.gather)) // when gathering, `out` receives the reduced values below
+                    static_cast<uint16_t*>(a.out)[size_t(row) * a.n + col] = uint16_t(v16);
                 valid = true;
             }
-            if (BITS == 4 && a.push.world > 0)
+            if (PUSH)
             {
                 // Fused all-reduce, first half: four neighbouring lanes hold four neighbouring
                 // columns of one row (one interleaved row of this CTA, so all four are valid or none
@@ -764,17 +765,118 @@ __global__ void __launch_bounds__(kThreads, 1)
                     size_t const pkt = (size_t(a.push_row0 + row) * a.n + size_t(col)) >> 2;
                     size_t const off = a.push.header_bytes + size_t(epoch & 1u) * a.push.copy_bytes
                         + size_t(a.push.rank) * a.push.pkt_slot + pkt * 16;
+                    // (when gathering, the own slot gets a copy too, so that the sum below treats all
+                    // ranks alike)
 #pragma unroll
                     for (int r = 0; r < W4_MAX_RANKS; ++r)
-                        if (r < a.push.world && r != a.push.rank)
+                        if (r < a.push.world && (r != a.push.rank || a.push.gather))
                             asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(a.push.ws[r] + off),
                                          "r"(pair), "r"(epoch), "r"(pair1), "r"(epoch)
                                          : "memory");
                 }
             }
         }
+        if (PUSH && a.push.gather)
+        {
+            // Fused all-reduce, second half: the same lanes poll their packet in every rank's slot of
+            // the local inbox (bounded in time), add the values in rank order in fp32 (+ bias) and
+            // write the reduced row segment. Every CTA of every rank has pushed before it waits, and
+            // all CTAs of a launch are resident (one per SM), so nobody waits for a CTA that cannot run.
+            for (int o = tid; o < nb * 16 * MPAD; o += kConsumerThreads)
+            {
+                int const col_in = o & 15, row = (o >> 4) & (MPAD - 1), cb = o / (16 * MPAD);
+                int const irow = r0 + (cg0 + cb) * C::RPG + col_in / C::IL;
+                int const col = (r0 + (cg0 + cb) * C::RPG) * C::IL + col_in;
+                if (row >= a.m || irow >= r1 || (col_in & 3) != 0)
+                    continue;
+                uint32_t const epoch = *reinterpret_cast<volatile uint32_t const*>(a.push.ws[a.push.rank]) + 1u;
+                size_t const pkt = (size_t(a.push_row0 + row) * a.n + size_t(col)) >> 2;
+                uint8_t const* inbox = a.push.ws[a.push.rank] + a.push.header_bytes
+                    + size_t(epoch & 1u) * a.push.copy_bytes + pkt * 16;
+                uint4 pk[W4_MAX_RANKS];
+                unsigned long long t0 = 0;
+                bool got = false;
+                for (uint32_t polls = 1; !got; ++polls)
+                {
+                    uint32_t bad = 0;
+#pragma unroll
+                    for (int r = 0; r < W4_MAX_RANKS; ++r)
+                        if (r < a.push.world)
+                        {
+                            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(pk[r].x), "=r"(pk[r].y), "=r"(pk[r].z), "=r"(pk[r].w)
+                                         : "l"(inbox + size_t(r) * a.push.pkt_slot)
+                                         : "memory");
+                            bad |= (pk[r].y ^ epoch) | (pk[r].w ^ epoch);
+                        }
+                    got = bad == 0;
+                    if (!got && (polls & 15u) == 0)
+                    {
+                        if (*abort_flag)
+                            break;
+                        unsigned long long now;
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                        if (t0 == 0)
+                            t0 = now;
+                        else if (now - t0 > a.push.timeout_ns)
+                        {
+                            *abort_flag = 1;
+                            atomicExch(&g_device_status, kDeviceTimeout);
+                            break;
+                        }
+                    }
+                }
+                if (!got)
+                    continue;
+                float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < W4_MAX_RANKS; ++r)
+                    if (r < a.push.world)
+                    {
+                        float lo, hi;
+                        P::unpack2(pk[r].x, lo, hi);
+                        acc4[0] += lo;
+                        acc4[1] += hi;
+                        P::unpack2(pk[r].z, lo, hi);
+                        acc4[2] += lo;
+                        acc4[3] += hi;
+                    }
+                if (a.push.bias)
+                {
+                    uint2 const bv = *reinterpret_cast<uint2 const*>(static_cast<uint16_t const*>(a.push.bias) + col);
+                    float lo, hi;
+                    P::unpack2(bv.x, lo, hi);
+                    acc4[0] += lo;
+                    acc4[1] += hi;
+                    P::unpack2(bv.y, lo, hi);
+                    acc4[2] += lo;
+                    acc4[3] += hi;
+                }
+                uint2 o2;
+                o2.x = uint32_t(P::from_float(acc4[0])) | (uint32_t(P::from_float(acc4[1])) << 16);
+                o2.y = uint32_t(P::from_float(acc4[2])) | (uint32_t(P::from_float(acc4[3])) << 16);
+                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(a.out) + size_t(row) * a.n + col) = o2;
+            }
+        }
         if (cg0 + batch < num_cg)
             named_bar_sync(1, kConsumerThreads);
+    }
+    if (PUSH && a.push.gather)
+    {
+        // This launch was a whole all-reduce call: the last CTA to get here advances the workspace's
+        // call number (every CTA has read it before it takes its ticket; the next call is a later
+        // kernel on the stream).
+        named_bar_sync(1, kConsumerThreads);
+        if (tid == 0)
+        {
+            uint32_t* ctrl = reinterpret_cast<uint32_t*>(a.push.ws[a.push.rank]);
+            uint32_t const epoch = *reinterpret_cast<volatile uint32_t*>(ctrl) + 1u;
+            if (atomicAdd(ctrl + 1, 1u) == gridDim.x - 1u)
+            {
+                ctrl[1] = 0u;
+                *reinterpret_cast<volatile uint32_t*>(ctrl) = epoch;
+            }
+        }
     }
 }
 
@@ -789,11 +891,11 @@ namespace w4
 namespace gemv
 {
 
-template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB>
+template <typename T, int BITS, int MB, bool HAS_ZERO, bool HAS_ACT_SCALE, bool FOLD, int CB, bool PUSH>
 static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     using C = Cfg<BITS, MB>;
-    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE, FOLD, CB>;
+    auto kernel = gemv_kernel<T, BITS, MB, HAS_ZERO, HAS_ACT_SCALE, FOLD, CB, PUSH>;
     Args args = a;
     args.groups_per_panel = a.group_shift >= 31 ? 1 : C::KP >> a.group_shift;
     args.box_stride = (args.groups_per_panel * kScaleBoxCols * 2 + 127) & ~127;
@@ -879,17 +981,31 @@ static int launch_one(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
 }
 
-template <typename T, int BITS, int MB, bool FOLD, int CB>
-static int dispatch_flags(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
+template <typename T, int BITS, int MB, bool FOLD, int CB, bool PUSH>
+static int dispatch_inputs(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
 {
     bool const z = a.zeros != nullptr, s = a.act_scale != nullptr;
     if (z && s)
-        return launch_one<T, BITS, MB, true, true, FOLD, CB>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, true, FOLD, CB, PUSH>(a, dev, stream);
     if (z)
-        return launch_one<T, BITS, MB, true, false, FOLD, CB>(a, dev, stream);
+        return launch_one<T, BITS, MB, true, false, FOLD, CB, PUSH>(a, dev, stream);
     if (s)
-        return launch_one<T, BITS, MB, false, true, FOLD, CB>(a, dev, stream);
-    return launch_one<T, BITS, MB, false, false, FOLD, CB>(a, dev, stream);
+        return launch_one<T, BITS, MB, false, true, FOLD, CB, PUSH>(a, dev, stream);
+    return launch_one<T, BITS, MB, false, false, FOLD, CB, PUSH>(a, dev, stream);
+}
+
+// The epilogue that sends the results to the peers (and may collect theirs) is an instantiation of
+// its own, int4 only: compiled into the ordinary kernel it cost that kernel 10 % (11.2 against
+// 10.0 us on a 4096 x 14336 matrix) although it never ran.
+template <typename T, int BITS, int MB, bool FOLD, int CB>
+static int dispatch_flags(Args const& a, DeviceInfo const& dev, cudaStream_t stream)
+{
+    if constexpr (BITS == 4)
+    {
+        if (a.push.world > 0)
+            return dispatch_inputs<T, BITS, MB, FOLD, CB, true>(a, dev, stream);
+    }
+    return dispatch_inputs<T, BITS, MB, FOLD, CB, false>(a, dev, stream);
 }
 
 // 8-row passes: with more than one k panel the column groups are walked in sub-batches of 4 that

@@ -31,6 +31,11 @@ struct PushTarget
     size_t pkt_slot;   // bytes of one sender's packet slot
     size_t copy_bytes; // bytes of one copy of the workspace's data areas
     size_t header_bytes;
+    // gather != 0: the kernel also collects the peers' packets and writes the reduced result (one
+    // kernel for GEMM and all-reduce); it then advances the workspace's call number itself.
+    int gather;
+    void const* bias;            // added after the sum when gathering
+    unsigned long long timeout_ns;
 };
 int launch_gemv(W4GemmParams const& p, cudaStream_t stream, PushTarget const* push = nullptr);
 // Fills `t` for the one-shot packet protocol of this all-reduce call; false when the call would not

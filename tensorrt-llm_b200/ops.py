@@ -475,6 +475,30 @@ def gemm_push(act, weight, scales, partial, workspace_ptrs, workspace_bytes: int
     return True
 
 
+def gemm_allreduce(act, weight, scales, partial, out, workspace_ptrs, workspace_bytes: int, rank: int, *, n: int,
+                   k: int, weight_bits: int, group_size: int, zeros=None, act_scale=None, bias=None, alpha: float = 1.0,
+                   weights_static: bool = False, regime: int = W4_REGIME_AUTO, timeout_ms: int = 0,
+                   stream=None) -> None:
+    """w4_gemm_allreduce: the row-parallel GEMM and the all-reduce of its output in the most fused form
+    that applies (one kernel up to 16 rows on int4 weights; GEMM with pushing epilogue + gather; or two
+    ordinary launches). ``partial`` [M, N] is scratch for the forms that need it, ``out`` receives the
+    reduced result (+ ``bias``) on every rank."""
+    m = act.numel() // k if k else 0
+    nws = workspace_bytes_max(max(m, 1), n, k, group_size, weight_bits, act.dtype, act_scale is not None)
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=act.device)
+    g = W4GemmParams(
+        act=_p(act), act_scale=_p(act_scale), weight=_p(weight), scales=_p(scales), zeros=_p(zeros), bias=None,
+        out=_p(partial), alpha=float(alpha), m=m, n=n, k=k, group_size=group_size, weight_bits=weight_bits,
+        act_dtype=_DTYPES[act.dtype], regime=regime, workspace=_p(ws), workspace_bytes=ws.numel(),
+        flags=_lib.W4_GEMM_WEIGHTS_STATIC if weights_static else 0)
+    r = _allreduce_params(partial, workspace_ptrs, workspace_bytes, out, n, rank, bias, _lib.W4_ALLREDUCE_AUTO,
+                          timeout_ms)
+    s = stream if stream is not None else torch.cuda.current_stream(act.device)
+    with torch.cuda.device(act.device):
+        rc = _lib.lib().w4_gemm_allreduce(ctypes.byref(g), ctypes.byref(r), ctypes.c_void_p(s.cuda_stream))
+    _lib.check(rc, "w4_gemm_allreduce")
+
+
 def allreduce_emulated(partials, workspaces, outs, n: int, biases=None, mode: int = _lib.W4_ALLREDUCE_AUTO,
                        timeout_ms: int = 0, stream=None) -> None:
     """All ranks of an all-reduce as one cooperative launch on the current GPU (every buffer local):

@@ -193,10 +193,10 @@ class WeightOnlyRowLinear(_ShardedLinear):
                 and self.matmul is None and self.group_size != 0):
             part = peer.partial(m, self.n_local)
             y = torch.empty(x_local.shape[:-1] + (self.n_local,), dtype=x_local.dtype, device=x_local.device)
-            # decode sizes on int4 weights: the GEMM's epilogue pushes its results to the peers itself
-            # and the reduce only gathers
-            if self.bits == 4 and m <= 16 and peer.gemm_push(x_local, self, part):
-                return peer.reduce(y, bias=self.bias, mode=_lib.W4_ALLREDUCE_GATHER_ONLY)
+            # decode sizes on int4 weights: one kernel computes, pushes its results to the peers,
+            # collects theirs and writes the reduced output
+            if self.bits == 4 and m <= 16:
+                return peer.gemm_allreduce(x_local, self, part, y)
             algo = (_lib.INT8_WEIGHT if self.bits == 8 else 0) | (_lib.ZERO if self.zeros is not None else 0) \
                 | (_lib.PRE_QUANT_SCALE if self.pre_quant_scale is not None else 0)
             ops.weight_only_groupwise_quant_matmul(x_local, self.pre_quant_scale, self.weight, self.scales, self.zeros,
@@ -260,6 +260,16 @@ class PeerAllReduce:
         return ops.gemm_push(x_local, layer.weight, layer.scales, part, self.ptrs, self.ws_bytes, self.rank,
                              n=layer.n_local, k=x_local.shape[-1], group_size=layer.group_size, zeros=layer.zeros,
                              act_scale=layer.pre_quant_scale, weights_static=weights_static)
+
+    def gemm_allreduce(self, x_local, layer, part, out, weights_static: bool = True):
+        """The layer's GEMM and the all-reduce of its output, fused as far as the sizes allow
+        (``ops.gemm_allreduce``). Counts as one call of the collective."""
+        self.calls += 1
+        ops.gemm_allreduce(x_local, layer.weight, layer.scales, part, out, self.ptrs, self.ws_bytes, self.rank,
+                           n=layer.n_local, k=x_local.shape[-1], weight_bits=layer.bits, group_size=layer.group_size,
+                           zeros=layer.zeros, act_scale=layer.pre_quant_scale, bias=layer.bias,
+                           weights_static=weights_static)
+        return out
 
     def reduce(self, out: torch.Tensor, bias=None, mode: int = _lib.W4_ALLREDUCE_AUTO, timeout_ms: int = 0,
                partial: Optional[torch.Tensor] = None) -> torch.Tensor:

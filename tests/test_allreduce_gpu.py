@@ -231,3 +231,38 @@ def test_push_is_refused_where_it_does_not_apply():
     big = torch.zeros(64, 1024, dtype=torch.bfloat16, device=dev)
     assert not ops.gemm_push(d(p4["act"]), d(p4["processed"]), d(p4["scales"]), big, [ws.data_ptr()] * 2, nws, 0, n=1024,
                              k=512, group_size=128, zeros=d(p4["zeros"]), regime=pkg_regime_auto())
+
+
+@pytest.mark.parametrize("m", [1, 7, 16])
+def test_single_kernel_gemm_allreduce_one_rank(m):
+    """w4_gemm_allreduce with a group of one rank: the decode kernel pushes into its own inbox slot,
+    collects it again, adds the bias, writes the output and advances the call number - the whole
+    single-kernel path without a peer to wait for (with peers it runs in the multi-GPU worker test).
+    Three calls in a row (both buffer copies), then an ordinary all-reduce continues the numbering."""
+    from _cases import make_problem, oracle_out, max_err
+    from oracle import woq_oracle as oracle
+    n, k, group = 1024, 512, 128
+    dev = "cuda"
+    p = make_problem(m, n, k, 4, group, torch.bfloat16, zero=True, prequant=True, seed=500 + m)
+    d = lambda t: t.to(dev)
+    nws = ops.allreduce_workspace_bytes(1 << 20, 1)
+    ws = torch.zeros(nws, dtype=torch.uint8, device=dev)
+    part = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+    bias = torch.randn(n, device=dev).to(torch.bfloat16)
+    w, s, z, ps = d(p["processed"]), d(p["scales"]), d(p["zeros"]), d(p["ps"])
+    for call in range(3):
+        act = d((p["act"].float() * (1.0 + call)).to(torch.bfloat16))
+        out.zero_()
+        ops.gemm_allreduce(act, w, s, part, out, [ws.data_ptr()], nws, 0, n=n, k=k, weight_bits=4, group_size=group,
+                           zeros=z, act_scale=ps, bias=bias, timeout_ms=50)
+        torch.cuda.synchronize()
+        assert L.lib().w4_gemm_device_status() == 0
+        ref_part = oracle.kernel_rounding_ref(act.cpu(), p["q"], p["scales"], zeros=p["zeros"], pre_quant_scale=p["ps"],
+                                              group_size=group)
+        ref = (ref_part.float() + bias.cpu().float()).to(torch.bfloat16)
+        assert max_err(out.cpu(), ref) <= oracle.tolerance(ref)
+        assert int(ws[:4].view(torch.int32)[0]) == call + 1 and int(ws[4:8].view(torch.int32)[0]) == 0
+    ops.allreduce(out, [ws.data_ptr()], nws, part, n, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(part, out) and int(ws[:4].view(torch.int32)[0]) == 4
