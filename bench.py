@@ -781,12 +781,22 @@ def tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2
                         entry["parity_fused_bit_exact"] = bool(
                             max_over_ranks(0.0 if torch.equal(y_peer, expect) else 1.0) == 0.0)
                     entry["fused_applies"] = bool(fused)
+                    if fused and m <= 16:
+                        # the whole step as ONE kernel (GEMM, push, collect, add, write)
+                        y_peer.zero_()
+                        ops.gemm_allreduce(x, w, s, peer.partial(m, n_loc), y_peer, peer.ptrs, peer.ws_bytes, peer.rank,
+                                           n=n_loc, k=k_loc, weight_bits=4, group_size=group_size, zeros=z,
+                                           weights_static=True)
+                        torch.cuda.synchronize()
+                        entry["parity_one_kernel_bit_exact"] = bool(
+                            max_over_ranks(0.0 if torch.equal(y_peer, expect) else 1.0) == 0.0)
                     del y_peer
                 del y_nccl, expect
             entry["parity_ok"] = bool(entry["parity_gemm_err_frac_of_max"] <= 1e-2
                                       and entry.get("parity_nccl_err_frac_of_max", 0.0) <= 2e-2
                                       and entry.get("parity_peer_bit_exact", True)
-                                      and entry.get("parity_fused_bit_exact", True))
+                                      and entry.get("parity_fused_bit_exact", True)
+                                      and entry.get("parity_one_kernel_bit_exact", True))
             # ---- eager timings with an L2 flush between repetitions
             t_gemm, t_ar = [], []
             for _ in range(reps):
@@ -829,9 +839,15 @@ def tp_layer_set(pkg, device, rank, world, barrier, max_over_ranks, ms=(1, 64, 2
                                   group_size=group_size, zeros=z, weights_static=True)
                     peer.reduce(y2, mode=pkg._lib.W4_ALLREDUCE_GATHER_ONLY)
 
+                def step_one_kernel():
+                    ops.gemm_allreduce(x, w, s, peer.partial(m, n_loc), y2, peer.ptrs, peer.ws_bytes, peer.rank, n=n_loc,
+                                       k=k_loc, weight_bits=4, group_size=group_size, zeros=z, weights_static=True)
+
                 steps = (("gemm_only", gemm), ("gemm_plus_nccl", step_nccl)) + (
                     (("gemm_plus_peer", step_peer),) if use_peer else ()) + (
-                    (("gemm_plus_peer_fused", step_fused),) if use_peer and entry.get("fused_applies") else ())
+                    (("gemm_plus_peer_fused", step_fused),) if use_peer and entry.get("fused_applies") else ()) + (
+                    (("gemm_allreduce_one_kernel", step_one_kernel),)
+                    if use_peer and "parity_one_kernel_bit_exact" in entry else ())
                 for label, fn in steps:
                     try:
                         st = torch.cuda.Stream(device=device)

@@ -107,6 +107,32 @@ def main():
             torch.cuda.synchronize()
             err = float((y.float() - ref.float()).abs().max())
             assert err <= 4 * 2.0 ** -8 * float(ref.float().abs().max()), ("fused", it, err)
+    # And as ONE kernel per step (w4_gemm_allreduce: compute, push, collect, add, write).
+    def one_kernel_step():
+        peer.gemm_allreduce(x_loc, layer, peer.partial(m, n), y)
+
+    with torch.cuda.stream(st):
+        one_kernel_step()
+        st.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            one_kernel_step()
+            one_kernel_step()
+            one_kernel_step()
+        for it in range(5):
+            x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+            x_loc.copy_(tp.split(x, world, rank, dim=1))
+            graph.replay()
+            st.synchronize()
+            ref = layer(x_loc)  # NCCL
+            torch.cuda.synchronize()
+            err = float((y.float() - ref.float()).abs().max())
+            assert err <= 4 * 2.0 ** -8 * float(ref.float().abs().max()), ("one kernel", it, err)
+            gathered = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(gathered, y)
+            for other in gathered:
+                assert torch.equal(other, gathered[0]), "ranks disagree"
     assert pkg._lib.lib().w4_gemm_device_status() == 0
     dist.barrier()
     if rank == 0:
