@@ -43,7 +43,7 @@
  *                            - the decode GEMM with the first half of that all-reduce in its epilogue;
  *                              the reference fuses a GEMM with its all-reduce for dense layers on sm_90
  *                              only (cpp/tensorrt_llm/plugins/gemmAllReducePlugin), never on this path.
- *   w4_preprocess_weights_w4a8 / w4_relayout_w4a8_to_w4a16
+ *   w4_preprocess_weights_w4a8 / w4_relayout_w4a8_to_w4a16 / w4_relayout_w4a8_to_w4a16_device
  *                            - preprocess_weights_for_mixed_gemm with QuantType::W4_AFP8
  *                              (cutlass_preprocessors.cpp:114-116) and its conversion into the layout
  *                              the kernels consume (W4A8-AWQ layers).
@@ -271,6 +271,10 @@ extern "C"
     /* in / out: [k, n*bits/8] bytes on the device, 16-byte aligned, out != in. Same bytes as
      * w4_preprocess_weights. */
     int w4_preprocess_weights_device(void* out, const void* in, size_t k, size_t n, int bits, void* stream);
+
+    /* w4_relayout_w4a8_to_w4a16 on device buffers: in / out [k, n/2] bytes, 16-byte aligned, out != in;
+     * k % 128 == 0, n % 64 == 0. Same bytes as the host function. */
+    int w4_relayout_w4a8_to_w4a16_device(void* out, const void* in, size_t k, size_t n, void* stream);
 
     /* weight: [k, n] row-major on the device, weight_dtype = W4_DTYPE_FP32 / FP16 / BF16 (the
      * reference's ComputeType). processed (mandatory) and unprocessed (optional) as in

@@ -27,6 +27,7 @@ EXPORTS = (
     "w4_allreduce_workspace_bytes",
     "w4_gemm_workspace_bytes_max", "w4_gemm_run_host", "w4_gemm_launch_experts",
     "w4_preprocess_weights_w4a8", "w4_relayout_w4a8_to_w4a16", "w4_gemm_launch_push", "w4_gemm_allreduce",
+    "w4_relayout_w4a8_to_w4a16_device",
 )
 
 
@@ -98,6 +99,8 @@ def lib() -> ctypes.CDLL:
                                             ctypes.c_int]
         l.w4_preprocess_weights_w4a8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
         l.w4_relayout_w4a8_to_w4a16.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
+        l.w4_relayout_w4a8_to_w4a16_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                                       ctypes.c_size_t, ctypes.c_void_p]
         l.w4_preprocess_weights_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
                                                    ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         l.w4_symmetric_quantize_device.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

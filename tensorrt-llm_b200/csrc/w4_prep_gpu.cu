@@ -10,6 +10,8 @@
 // reference passes (row permutation inside 16/32-row blocks, sub-byte transpose, column
 // interleave in 64-k tiles, bias + in-register shuffle) and a warp writes one whole output line
 // per store instruction.
+#include <algorithm>
+
 #include "w4_common.cuh"
 #include "w4_internal.h"
 
@@ -83,6 +85,43 @@ __global__ void __launch_bounds__(kThreads) preprocess_kernel(uint32_t* out, uin
     }
     __syncthreads();
     emit_tile<BITS>(out, tile, k_tile, b0 * 8 / BITS, nbytes * 8 / BITS, K);
+}
+
+// W4A8-layout registers (the reference's layout for fp8 activations, cutlass_preprocessors.cpp:114-116,
+// 175-179 of the TensorRT-LLM tree: two interleaved columns, 128-row tiles, rows of a 32-block in the
+// order {0..3, 16..19, 4..7, 20..23, ...}) -> the W4A16 registers the GEMM kernels consume. Both hold
+// biased nibbles, so this is a pure permutation: one thread per output register gathers its eight
+// nibbles from the two source registers that hold them (same column, same 32-row block) and a warp
+// writes one whole 128-byte line.
+__global__ void __launch_bounds__(kThreads) relayout_w4a8_kernel(uint32_t* out, uint32_t const* in, int K, int N)
+{
+    size_t const total = size_t(K) * size_t(N) / 8;
+    size_t const regs_per_irow16 = size_t(K) / 2; // four columns of K / 8 registers
+    size_t const regs_per_irow8 = size_t(K) / 4;  // two columns
+    for (size_t reg = size_t(blockIdx.x) * kThreads + threadIdx.x; reg < total; reg += size_t(gridDim.x) * kThreads)
+    {
+        size_t const irow = reg / regs_per_irow16;
+        int const vwr = int(reg - irow * regs_per_irow16);
+        int const within = vwr & 31;
+        int const n = int(irow) * 4 + (within >> 3);
+        int const vr = (vwr >> 5) * 8 + (within & 7); // register of column n, counted over all of K
+        uint32_t const* src = in + size_t(n >> 1) * regs_per_irow8 + 16 * (n & 1);
+        uint32_t word = 0;
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+        {
+            int const s = d < 4 ? 2 * d : 2 * (d - 4) + 1;
+            int const kp = vr * 8 + s;
+            int const k = (kp & ~31) + c_perm4[kp & 31];
+            // position of row k in the W4A8 order: the inverse of its 32-row permutation in closed form
+            int const k8 = (k & ~31) + ((k >> 2) & 3) * 8 + ((k >> 4) & 1) * 4 + (k & 3);
+            int const e = k8 & 7;
+            int const dd = (e & 1) ? 4 + (e >> 1) : e >> 1;
+            uint32_t const w = __ldg(src + 32 * (k8 >> 7) + ((k8 & 127) >> 3));
+            word |= ((w >> (4 * dd)) & 0xFu) << (4 * d);
+        }
+        out[reg] = word;
+    }
 }
 
 // amax -> scale = amax * 2^-(bits-1), in place, plus the copy rounded to the activation type.
@@ -268,6 +307,24 @@ extern "C"
         else
             preprocess_kernel<8><<<grid, kThreads, 0, s>>>(static_cast<uint32_t*>(out),
                 static_cast<uint8_t const*>(in), int(k), int(n));
+        return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
+    }
+
+    int w4_relayout_w4a8_to_w4a16_device(void* out, const void* in, size_t k, size_t n, void* stream)
+    {
+        using namespace w4::prep;
+        if (!out || !in)
+            return W4_ERR_NULL_POINTER;
+        if (!shape_ok(long(k), long(n), 4) || k % 128 != 0 || n % 64 != 0)
+            return W4_ERR_BAD_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 15u)
+            return W4_ERR_MISALIGNED;
+        if (out == in)
+            return W4_ERR_UNSUPPORTED; // not an in-place transform
+        size_t const regs = k * n / 8;
+        unsigned const grid = unsigned(std::min<size_t>((regs + kThreads - 1) / kThreads, size_t(148) * 32));
+        relayout_w4a8_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint32_t*>(out),
+            static_cast<uint32_t const*>(in), int(k), int(n));
         return cudaGetLastError() == cudaSuccess ? W4_OK : W4_ERR_CUDA;
     }
 

@@ -237,10 +237,14 @@ def prepare_w4a8_layer(weight_w4a8, scales, zeros, act_dtype, device):
     """What a W4A8-AWQ layer's constants need once, at load time: the weight, laid out by the reference
     for fp8 activations (preprocess_weights_for_mixed_gemm with activation type float8_e4m3fn), is
     re-laid into the layout the kernels consume, and the float16 scales / zeros are cast to the
-    activation type. Returns (weight, scales, zeros) on ``device``."""
+    activation type. Returns (weight, scales, zeros) on ``device``. A weight that already sits on a
+    GPU is re-laid there (no round trip through the host)."""
     from . import quantize
-    w = weight_w4a8.detach().cpu().contiguous()
-    w = quantize.relayout_w4a8_weights(w.view(torch.int8)).to(device)
+    w = weight_w4a8.detach().contiguous().view(torch.int8)
+    if w.device.type == "cuda":
+        w = quantize.relayout_w4a8_weights_cuda(w).to(device)
+    else:
+        w = quantize.relayout_w4a8_weights(w).to(device)
     s = scales.to(device=device, dtype=act_dtype)
     z = None if zeros is None else zeros.to(device=device, dtype=act_dtype)
     return w, s, z

@@ -174,6 +174,22 @@ def preprocess_weights_for_mixed_gemm_cuda(row_major_quantized_weight: torch.Ten
     return out
 
 
+def relayout_w4a8_weights_cuda(w4a8_weight: torch.Tensor) -> torch.Tensor:
+    """relayout_w4a8_weights on a CUDA int8 tensor [K, N/2] or [E, K, N/2]; same bytes."""
+    t = w4a8_weight
+    _check_cuda_contiguous(t, "w4a8_weight")
+    if t.dtype != torch.int8 or t.dim() not in (2, 3):
+        raise RuntimeError("expected an int8 tensor [K, N/2] or [E, K, N/2]")
+    out = torch.empty_like(t)
+    mats = [(t, out)] if t.dim() == 2 else [(t[e], out[e]) for e in range(t.shape[0])]
+    with torch.cuda.device(t.device):
+        for src, dst in mats:
+            rc = _lib.lib().w4_relayout_w4a8_to_w4a16_device(_ptr(dst), _ptr(src), src.shape[0], src.shape[1] * 2,
+                                                             _stream(t))
+            _lib.check(rc, "relayout_w4a8_weights_cuda")
+    return out
+
+
 def symmetric_quantize_last_axis_of_batched_matrix_cuda(weight: torch.Tensor, quant_type,
                                                          return_unprocessed: bool = False):
     """symmetric_quantize on a CUDA tensor [K, N] (fp32 / fp16 / bf16):

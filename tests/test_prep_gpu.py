@@ -1,5 +1,5 @@
 """GPU: device-side quantise / layout kernels (w4_preprocess_weights_device,
-w4_symmetric_quantize_device) through the C ABI, byte for byte against the oracle, the committed
+w4_symmetric_quantize_device, w4_relayout_w4a8_to_w4a16_device) through the C ABI, byte for byte against the oracle, the committed
 golden vectors made from the reference's own code, and the host functions of the library."""
 import glob
 import os
@@ -60,6 +60,36 @@ def test_quantize_matches_oracle(bits, dtype, k, n):
     # and the library's own host path (what a CPU caller gets)
     p_host, s_host = Q.symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
     assert torch.equal(p.cpu(), p_host) and torch.equal(s.cpu(), s_host)
+
+
+@pytest.mark.parametrize("k,n", [(128, 64), (256, 192), (4096, 14336), (8192, 1024)])
+def test_w4a8_relayout_matches_host_and_oracle(k, n):
+    """W4A8-layout bytes -> the kernels' layout on the device: the bytes the host function gives,
+    which are the oracle's plain int4 layout of the same weights."""
+    rng = np.random.default_rng(k + n)
+    q = rng.integers(-128, 128, size=(k, n // 2), dtype=np.int8)
+    w4a8 = Q.preprocess_weights_for_mixed_gemm(torch.from_numpy(q), torch.quint4x2, torch.float8_e4m3fn)
+    out = Q.relayout_w4a8_weights_cuda(w4a8.cuda())
+    assert np.array_equal(out.cpu().numpy(), o.preprocess_weights(q, 4))
+    assert torch.equal(out.cpu(), Q.relayout_w4a8_weights(w4a8))
+
+
+def test_w4a8_relayout_experts_and_error_codes():
+    rng = np.random.default_rng(5)
+    q = rng.integers(-128, 128, size=(3, 256, 64), dtype=np.int8)
+    w4a8 = Q.preprocess_weights_for_mixed_gemm(torch.from_numpy(q), torch.quint4x2, torch.float8_e4m3fn)
+    out = Q.relayout_w4a8_weights_cuda(w4a8.cuda())
+    for e in range(3):
+        assert np.array_equal(out[e].cpu().numpy(), o.preprocess_weights(q[e], 4))
+    lib = pkg._lib.lib()
+    a = torch.zeros(128, 32, dtype=torch.int8, device="cuda")
+    b = torch.zeros_like(a)
+    assert lib.w4_relayout_w4a8_to_w4a16_device(None, a.data_ptr(), 128, 64, None) == pkg._lib.W4_ERR_NULL_POINTER
+    assert lib.w4_relayout_w4a8_to_w4a16_device(b.data_ptr(), a.data_ptr(), 64, 64, None) == pkg._lib.W4_ERR_BAD_SHAPE
+    assert lib.w4_relayout_w4a8_to_w4a16_device(b.data_ptr(), a.data_ptr(), 128, 32, None) == pkg._lib.W4_ERR_BAD_SHAPE
+    assert lib.w4_relayout_w4a8_to_w4a16_device(a.data_ptr(), a.data_ptr(), 128, 64, None) == pkg._lib.W4_ERR_UNSUPPORTED
+    assert lib.w4_relayout_w4a8_to_w4a16_device(b.data_ptr() + 4, a.data_ptr(), 128, 64, None) \
+        == pkg._lib.W4_ERR_MISALIGNED
 
 
 def test_round_trip_through_gemm():
