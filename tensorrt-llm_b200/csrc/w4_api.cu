@@ -126,7 +126,7 @@ extern "C"
 
     int w4_gemm_version(void)
     {
-        return 111;
+        return 112;
     }
 
     const char* w4_status_string(int status)

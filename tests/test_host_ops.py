@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(lib):
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/w4_gemm.h but not exported"
     assert set(pkg._lib.EXPORTS) <= declared
-    assert lib.w4_gemm_version() >= 111
+    assert lib.w4_gemm_version() >= 112
     assert pkg._lib.status_string(0) == "ok" and "null" in pkg._lib.status_string(-1)
 
 
