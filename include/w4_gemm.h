@@ -206,8 +206,30 @@ extern "C"
     size_t w4_gemm_workspace_bytes_max(int max_m, int n, int k, int group_size, int weight_bits, int act_dtype,
         int has_act_scale);
 
-    /* W4_REGIME_GEMV or W4_REGIME_GEMM for this shape. */
+    /* W4_REGIME_GEMV or W4_REGIME_GEMM for this shape: the cost model alone, a pure function of its
+     * arguments and the device's SM count. Wherever the library resolves W4_REGIME_AUTO itself (launches
+     * and workspace sizes alike) the environment variable W4_FORCE_REGIME = gemv | gemm, read once,
+     * overrides it - a debugging and A/B switch in the manner of the reference's
+     * FORCE_NCCL_ALL_REDUCE_STRATEGY (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:333). */
     int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits);
+
+    /* Logging. Levels and names are the reference logger's
+     * (cpp/include/tensorrt_llm/common/logger.h:41-48); the level is read once from W4_LOG_LEVEL or,
+     * when that is unset, from the reference's TLLM_LOG_LEVEL (TRACE, DEBUG / VERBOSE, INFO, WARNING,
+     * ERROR; cpp/tensorrt_llm/common/logger.cpp:30-46), default ERROR. Lines go to stderr:
+     * ERROR - a launch failed; WARNING - w4_gemm_launch refused its arguments; DEBUG - one line per
+     * w4_gemm_launch with the shape and the kernel taken. w4_set_log_level(level < 0) returns to
+     * the environment's setting. */
+    enum
+    {
+        W4_LOG_TRACE = 0,
+        W4_LOG_DEBUG = 10,
+        W4_LOG_INFO = 20,
+        W4_LOG_WARNING = 30,
+        W4_LOG_ERROR = 40
+    };
+    void w4_set_log_level(int level);
+    int w4_get_log_level(void);
 
     /* Reads and clears the device-side status word of the current device (synchronises the
      * device). 0, or W4_ERR_DEVICE_TIMEOUT when a kernel gave up a bounded wait. */

@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libw4gemm.so")
 
 W4_OK = 0
+W4_LOG_TRACE, W4_LOG_DEBUG, W4_LOG_INFO, W4_LOG_WARNING, W4_LOG_ERROR = 0, 10, 20, 30, 40
 W4_ERR_NULL_POINTER, W4_ERR_BAD_SHAPE, W4_ERR_BAD_GROUP, W4_ERR_BAD_DTYPE, W4_ERR_MISALIGNED = -1, -2, -3, -4, -5
 W4_ERR_UNSUPPORTED, W4_ERR_WORKSPACE, W4_ERR_CUDA, W4_ERR_BAD_REGIME = -6, -7, -8, -9
 W4_DTYPE_FP16, W4_DTYPE_BF16 = 0, 1
@@ -27,7 +28,7 @@ EXPORTS = (
     "w4_allreduce_workspace_bytes",
     "w4_gemm_workspace_bytes_max", "w4_gemm_run_host", "w4_gemm_launch_experts",
     "w4_preprocess_weights_w4a8", "w4_relayout_w4a8_to_w4a16", "w4_gemm_launch_push", "w4_gemm_allreduce",
-    "w4_relayout_w4a8_to_w4a16_device",
+    "w4_relayout_w4a8_to_w4a16_device", "w4_set_log_level", "w4_get_log_level",
 )
 
 
@@ -115,6 +116,8 @@ def lib() -> ctypes.CDLL:
         l.w4_pack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         l.w4_unpack_int4.restype = None
+        l.w4_set_log_level.argtypes = [ctypes.c_int]
+        l.w4_set_log_level.restype = None
         _lib = l
     return _lib
 

@@ -1,5 +1,10 @@
 // The C ABI declared in include/w4_gemm.h: argument validation, the M-based regime choice and
 // dispatch into the two kernel families. Nothing here allocates; only w4_gemm_run_host synchronises.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "w4_common.cuh"
@@ -112,11 +117,101 @@ bool aligned16(void const* p)
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }
 
+// Logger: the levels and level names of the reference's (cpp/include/tensorrt_llm/common/logger.h:41-48,
+// cpp/tensorrt_llm/common/logger.cpp:30-46), read once from W4_LOG_LEVEL or, failing that, from the
+// reference's own TLLM_LOG_LEVEL; ERROR when neither is set. Everything goes to stderr.
+std::atomic<int> g_log_level{-1};
+
+int level_from_name(char const* name)
+{
+    if (!name)
+        return -1;
+    if (!std::strcmp(name, "TRACE"))
+        return W4_LOG_TRACE;
+    if (!std::strcmp(name, "DEBUG") || !std::strcmp(name, "VERBOSE"))
+        return W4_LOG_DEBUG;
+    if (!std::strcmp(name, "INFO"))
+        return W4_LOG_INFO;
+    if (!std::strcmp(name, "WARNING"))
+        return W4_LOG_WARNING;
+    if (!std::strcmp(name, "ERROR"))
+        return W4_LOG_ERROR;
+    return -1;
+}
+
+int log_level()
+{
+    int level = g_log_level.load(std::memory_order_relaxed);
+    if (level < 0)
+    {
+        level = level_from_name(std::getenv("W4_LOG_LEVEL"));
+        if (level < 0)
+            level = level_from_name(std::getenv("TLLM_LOG_LEVEL"));
+        if (level < 0)
+            level = W4_LOG_ERROR;
+        g_log_level.store(level, std::memory_order_relaxed);
+    }
+    return level;
+}
+
+void log_line(int level, char const* fmt, ...)
+{
+    if (level < log_level())
+        return;
+    char const* name = level >= W4_LOG_ERROR ? "ERROR"
+        : level >= W4_LOG_WARNING            ? "WARNING"
+        : level >= W4_LOG_INFO               ? "INFO"
+        : level >= W4_LOG_DEBUG              ? "DEBUG"
+                                             : "TRACE";
+    char text[512];
+    va_list args;
+    va_start(args, fmt);
+    std::vsnprintf(text, sizeof text, fmt, args);
+    va_end(args);
+    std::fprintf(stderr, "[w4_gemm][%s] %s\n", name, text);
+}
+
+// W4_FORCE_REGIME = gemv | gemm overrides the cost model wherever the regime is left to the library
+// (launches and workspace sizes alike); read once. For debugging and A/B timing, like the reference's
+// FORCE_NCCL_ALL_REDUCE_STRATEGY (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:333).
+int forced_regime()
+{
+    static int const forced = []
+    {
+        char const* v = std::getenv("W4_FORCE_REGIME");
+        if (v && !std::strcmp(v, "gemv"))
+            return int(W4_REGIME_GEMV);
+        if (v && !std::strcmp(v, "gemm"))
+            return int(W4_REGIME_GEMM);
+        if (v && *v)
+            log_line(W4_LOG_WARNING, "W4_FORCE_REGIME=%s ignored (expected gemv or gemm)", v);
+        return int(W4_REGIME_AUTO);
+    }();
+    return forced;
+}
+
+int auto_regime(int m, int n, int k, int group_size, int weight_bits)
+{
+    int const f = forced_regime();
+    return f != W4_REGIME_AUTO ? f : w4_gemm_select_regime(m, n, k, group_size, weight_bits);
+}
+
 int resolve_regime(W4GemmParams const& p)
 {
     if (p.regime == W4_REGIME_GEMV || p.regime == W4_REGIME_GEMM)
         return p.regime;
-    return w4_gemm_select_regime(p.m, p.n, p.k, p.group_size, p.weight_bits);
+    return auto_regime(p.m, p.n, p.k, p.group_size, p.weight_bits);
+}
+
+void log_refusal(char const* entry, W4GemmParams const* p, int rc)
+{
+    if (log_level() > W4_LOG_WARNING)
+        return;
+    if (!p)
+        log_line(W4_LOG_WARNING, "%s refused: %s", entry, w4_status_string(rc));
+    else
+        log_line(W4_LOG_WARNING, "%s refused: %s (m=%d n=%d k=%d bits=%d group=%d regime=%d)", entry,
+            w4_status_string(rc), p->m, p->n, p->k, p->weight_bits, p->group_size, p->regime);
 }
 
 } // namespace
@@ -223,7 +318,7 @@ extern "C"
             return 0;
         int r = regime;
         if (r != W4_REGIME_GEMV && r != W4_REGIME_GEMM)
-            r = w4_gemm_select_regime(m, n, k, group_size, weight_bits);
+            r = auto_regime(m, n, k, group_size, weight_bits);
         if (r == W4_REGIME_GEMV)
             return 0;
         return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale, weight_bits);
@@ -249,17 +344,38 @@ extern "C"
         return best;
     }
 
+    void w4_set_log_level(int level)
+    {
+        g_log_level.store(level < 0 ? -1 : level, std::memory_order_relaxed); // negative: back to the environment
+    }
+
+    int w4_get_log_level(void)
+    {
+        return log_level();
+    }
+
     int w4_gemm_launch(const W4GemmParams* p, void* stream)
     {
-        int const rc = w4_gemm_validate(p);
+        int rc = w4_gemm_validate(p);
         if (rc != W4_OK)
+        {
+            log_refusal("w4_gemm_launch", p, rc);
             return rc;
+        }
         if (p->m == 0)
             return W4_OK;
         cudaStream_t const s = static_cast<cudaStream_t>(stream);
-        if (resolve_regime(*p) == W4_REGIME_GEMV)
-            return w4::launch_gemv(*p, s);
-        return w4::launch_gemm_tc(*p, s);
+        bool const gemv = resolve_regime(*p) == W4_REGIME_GEMV;
+        if (log_level() <= W4_LOG_DEBUG)
+            log_line(W4_LOG_DEBUG, "w4_gemm_launch m=%d n=%d k=%d bits=%d group=%d zeros=%d bias=%d act_scale=%d alpha=%g %s%s",
+                p->m, p->n, p->k, p->weight_bits, p->group_size, p->zeros != nullptr, p->bias != nullptr,
+                p->act_scale != nullptr, double(p->alpha), gemv ? "decode kernel" : "tensor-core kernel",
+                p->regime == W4_REGIME_AUTO ? " (chosen)" : " (requested)");
+        rc = gemv ? w4::launch_gemv(*p, s) : w4::launch_gemm_tc(*p, s);
+        if (rc != W4_OK)
+            log_line(W4_LOG_ERROR, "w4_gemm_launch failed: %s (m=%d n=%d k=%d bits=%d group=%d)", w4_status_string(rc),
+                p->m, p->n, p->k, p->weight_bits, p->group_size);
+        return rc;
     }
 
     int w4_gemm_launch_push(const W4GemmParams* p, const W4AllReduceParams* r, void* stream)

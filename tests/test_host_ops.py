@@ -182,3 +182,67 @@ def test_plugin_mirror_fields_and_serialisation():
         pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_HALF, pkg.FP8_ALPHA | pkg.INT8_WEIGHT, 128)
     with pytest.raises(RuntimeError):
         pkg.WeightOnlyQuantMatmulPlugin(0, 1)
+
+
+def test_logger_levels_and_refusal_line(lib, capfd):
+    """The logger takes the reference logger's level numbers; a refused launch prints one WARNING line
+    when the level allows it and nothing at the default level (no device is touched: validation fails
+    first)."""
+    p = W4GemmParams()
+    p.m, p.n, p.k, p.weight_bits, p.group_size, p.act_dtype = 4, 64, 100, 4, 0, pkg._lib.W4_DTYPE_FP16
+    try:
+        lib.w4_set_log_level(pkg._lib.W4_LOG_ERROR)
+        assert lib.w4_get_log_level() == 40
+        assert lib.w4_gemm_launch(ctypes.byref(p), None) == pkg._lib.W4_ERR_BAD_SHAPE
+        assert capfd.readouterr().err == ""
+        lib.w4_set_log_level(pkg._lib.W4_LOG_WARNING)
+        assert lib.w4_gemm_launch(ctypes.byref(p), None) == pkg._lib.W4_ERR_BAD_SHAPE
+        err = capfd.readouterr().err
+        assert err.startswith("[w4_gemm][WARNING] w4_gemm_launch refused:") and "k=100" in err
+        assert err.count("\n") == 1
+    finally:
+        lib.w4_set_log_level(-1)  # back to the environment's setting
+
+
+@pytest.mark.parametrize("env,expect", [({"W4_LOG_LEVEL": "DEBUG"}, 10), ({"TLLM_LOG_LEVEL": "VERBOSE"}, 10),
+                                        ({"TLLM_LOG_LEVEL": "INFO", "W4_LOG_LEVEL": "TRACE"}, 0),
+                                        ({"W4_LOG_LEVEL": "nonsense"}, 40), ({}, 40)])
+def test_log_level_from_environment(env, expect):
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(__file__), "..")
+    child_env = {k: v for k, v in os.environ.items() if k not in ("W4_LOG_LEVEL", "TLLM_LOG_LEVEL")}
+    child_env.update(env)
+    out = subprocess.check_output([sys.executable, "-c",
+                                   "import tensorrt_llm_b200 as p; print(p._lib.lib().w4_get_log_level())"],
+                                  cwd=root, env=child_env, text=True)
+    assert int(out.strip().splitlines()[-1]) == expect
+
+
+@pytest.mark.parametrize("force", ["gemv", "gemm", "other", None])
+def test_forced_regime_governs_workspace_sizes(lib, force):
+    """W4_FORCE_REGIME overrides the cost model wherever the library resolves the regime itself: seen
+    here through the workspace size of an automatic launch (0 for the decode kernel); the cost model's
+    own answer (w4_gemm_select_regime) is unchanged."""
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(__file__), "..")
+    child_env = {k: v for k, v in os.environ.items() if k != "W4_FORCE_REGIME"}
+    if force is not None:
+        child_env["W4_FORCE_REGIME"] = force
+    code = ("import tensorrt_llm_b200 as p; l = p._lib.lib(); "
+            "print(l.w4_gemm_workspace_bytes(1, 1280, 8192, 128, 4, 1, 1, 0), "
+            "l.w4_gemm_workspace_bytes(4096, 4096, 4096, 128, 4, 1, 1, 0), "
+            "l.w4_gemm_select_regime(1, 1280, 8192, 128, 4), l.w4_gemm_select_regime(4096, 4096, 4096, 128, 4))")
+    out = subprocess.check_output([sys.executable, "-c", code], cwd=root, env=child_env, text=True)
+    small, large, r_small, r_large = (int(x) for x in out.strip().splitlines()[-1].split())
+    assert (r_small, r_large) == (pkg.W4_REGIME_GEMV, pkg.W4_REGIME_GEMM)
+    gemm_small = lib.w4_gemm_workspace_bytes(1, 1280, 8192, 128, 4, 1, 1, pkg.W4_REGIME_GEMM)
+    gemm_large = lib.w4_gemm_workspace_bytes(4096, 4096, 4096, 128, 4, 1, 1, pkg.W4_REGIME_GEMM)
+    assert gemm_small > 0 and gemm_large > 0
+    if force == "gemv":
+        assert (small, large) == (0, 0)
+    elif force == "gemm":
+        assert (small, large) == (gemm_small, gemm_large)
+    else:
+        assert (small, large) == (0, gemm_large)
