@@ -222,3 +222,23 @@ def test_w4a8_awq_layer(dtype, m):
         assert plug.enqueue(inputs, [out3], ws) == 0
         torch.cuda.synchronize()
         assert torch.equal(out3, out)
+
+
+def test_debug_log_names_the_kernel_taken(capfd):
+    """At DEBUG the library prints one line per launch: the shape and which kernel ran."""
+    lib = pkg._lib.lib()
+    small = make_problem(2, 256, 512, 4, 128, torch.float16, zero=True, seed=1)
+    large = make_problem(300, 256, 512, 4, 128, torch.float16, zero=True, seed=2)
+    try:
+        lib.w4_set_log_level(pkg._lib.W4_LOG_DEBUG)
+        capfd.readouterr()
+        for p in (small, large):
+            out = ops.weight_only_groupwise_quant_matmul(_d(p["act"]), None, _d(p["processed"]), _d(p["scales"]),
+                                                         _d(p["zeros"]), None, 1.0, pkg.ZERO, 128)
+            _assert_close(out, p)
+        lines = [l for l in capfd.readouterr().err.splitlines() if l.startswith("[w4_gemm][DEBUG] w4_gemm_launch")]
+        assert len(lines) == 2
+        assert "m=2 n=256 k=512 bits=4 group=128" in lines[0] and "decode kernel (chosen)" in lines[0]
+        assert "m=300" in lines[1] and "tensor-core kernel (chosen)" in lines[1]
+    finally:
+        lib.w4_set_log_level(-1)
