@@ -580,7 +580,7 @@ def sweep(pkg, device, peaks, stream):
                 prob = Problem(device, max(SWEEP_MS), n, k, bits, group, dtype, zeros=grouped, prequant=grouped,
                                seed=k // 512 + n // 512 + bits + group, copies=copies_for(wbytes))
                 for m in SWEEP_MS:
-                    regime = pkg.ops.select_regime(m, n, k, group, bits)
+                    regime = pkg.ops.select_regime(m, n, k, group, bits, dtype)
                     fn, out = prob.launcher(m)
                     fn(0)
                     torch.cuda.synchronize()

@@ -213,6 +213,12 @@ extern "C"
      * FORCE_NCCL_ALL_REDUCE_STRATEGY (cpp/tensorrt_llm/plugins/ncclPlugin/allreducePlugin.cpp:333). */
     int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits);
 
+    /* The same with the activation type (W4_DTYPE_FP16 / W4_DTYPE_BF16), which is what the launches and
+     * the workspace sizes use: decode passes over int8 weights cost more with bf16 activations (a
+     * byte does not fit a bf16 mantissa and is multiplied as two nibble planes), so the switch to the
+     * tensor-core kernel comes earlier there. w4_gemm_select_regime answers for float16. */
+    int w4_gemm_select_regime_typed(int m, int n, int k, int group_size, int weight_bits, int act_dtype);
+
     /* Logging. Levels and names are the reference logger's
      * (cpp/include/tensorrt_llm/common/logger.h:41-48); the level is read once from W4_LOG_LEVEL or,
      * when that is unset, from the reference's TLLM_LOG_LEVEL (TRACE, DEBUG / VERBOSE, INFO, WARNING,

@@ -29,6 +29,7 @@ EXPORTS = (
     "w4_gemm_workspace_bytes_max", "w4_gemm_run_host", "w4_gemm_launch_experts",
     "w4_preprocess_weights_w4a8", "w4_relayout_w4a8_to_w4a16", "w4_gemm_launch_push", "w4_gemm_allreduce",
     "w4_relayout_w4a8_to_w4a16_device", "w4_set_log_level", "w4_get_log_level",
+    "w4_gemm_select_regime_typed",
 )
 
 
@@ -94,6 +95,7 @@ def lib() -> ctypes.CDLL:
         l.w4_gemm_workspace_bytes_max.restype = ctypes.c_size_t
         l.w4_gemm_workspace_bytes_max.argtypes = [ctypes.c_int] * 7
         l.w4_gemm_select_regime.argtypes = [ctypes.c_int] * 5
+        l.w4_gemm_select_regime_typed.argtypes = [ctypes.c_int] * 6
         l.w4_symmetric_quantize.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                             ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int]
         l.w4_preprocess_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,

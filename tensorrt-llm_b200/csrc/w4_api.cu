@@ -190,17 +190,17 @@ int forced_regime()
     return forced;
 }
 
-int auto_regime(int m, int n, int k, int group_size, int weight_bits)
+int auto_regime(int m, int n, int k, int group_size, int weight_bits, int act_dtype)
 {
     int const f = forced_regime();
-    return f != W4_REGIME_AUTO ? f : w4_gemm_select_regime(m, n, k, group_size, weight_bits);
+    return f != W4_REGIME_AUTO ? f : w4_gemm_select_regime_typed(m, n, k, group_size, weight_bits, act_dtype);
 }
 
 int resolve_regime(W4GemmParams const& p)
 {
     if (p.regime == W4_REGIME_GEMV || p.regime == W4_REGIME_GEMM)
         return p.regime;
-    return auto_regime(p.m, p.n, p.k, p.group_size, p.weight_bits);
+    return auto_regime(p.m, p.n, p.k, p.group_size, p.weight_bits, p.act_dtype);
 }
 
 void log_refusal(char const* entry, W4GemmParams const* p, int rc)
@@ -283,6 +283,11 @@ extern "C"
 
     int w4_gemm_select_regime(int m, int n, int k, int group_size, int weight_bits)
     {
+        return w4_gemm_select_regime_typed(m, n, k, group_size, weight_bits, W4_DTYPE_FP16);
+    }
+
+    int w4_gemm_select_regime_typed(int m, int n, int k, int group_size, int weight_bits, int act_dtype)
+    {
         (void) group_size;
         if (m <= 8)
             return W4_REGIME_GEMV; // one pass over the weights
@@ -291,7 +296,9 @@ extern "C"
         // an 8-row pass costs 4.2 us plus the weight bytes at 3.4 TB/s (config 2: 12.1 us; 4096 x 4096
         // int4: 6.6 us), a 16-row pass 6.3 us plus the bytes at 2.7 TB/s for int4 (config 2: 17.2 us;
         // 4096 x 1024: 6.8 us) and 3.5 us plus the bytes at 3.2 TB/s for int8, whose narrower units let
-        // a 16-row tile cover as much k as an 8-row one (4096 x 4096: 7.8 us; 4096 x 14336: 20-23 us).
+        // a 16-row tile cover as much k as an 8-row one (4096 x 4096: 7.8 us; 4096 x 14336: 20-23 us);
+        // bf16 activations with int8 weights need two mma planes per byte: 5.0 us plus the bytes at
+        // 3.1 TB/s (4096 x 1024: 6.4 us; 4096 x 4096: 9.6 us; 4096 x 14336: 23.6 us).
         // The tensor-core kernel's
         // estimate comes from its own per-step costs. The SM count is the current device's (148 when
         // no device is present).
@@ -304,7 +311,9 @@ extern "C"
             ++passes16;
             left -= left < 16 ? left : 16;
         }
-        double const pass16_us = weight_bits == 8 ? weight_mb / 3.2 + 3.5 : weight_mb / 2.7 + 6.3;
+        double const pass16_us = weight_bits == 8
+            ? (act_dtype == W4_DTYPE_BF16 ? weight_mb / 3.1 + 5.0 : weight_mb / 3.2 + 3.5)
+            : weight_mb / 2.7 + 6.3;
         double const gemv_us = passes16 * pass16_us + (left > 0 ? weight_mb / 3.4 + 4.2 : 0.0);
         double const gemm_us = w4::gemm_tc_estimate_us(m, n, k, sms, weight_bits);
         return gemv_us <= gemm_us ? W4_REGIME_GEMV : W4_REGIME_GEMM;
@@ -313,12 +322,11 @@ extern "C"
     size_t w4_gemm_workspace_bytes(int m, int n, int k, int group_size, int weight_bits, int act_dtype,
         int has_act_scale, int regime)
     {
-        (void) act_dtype;
         if (m <= 0)
             return 0;
         int r = regime;
         if (r != W4_REGIME_GEMV && r != W4_REGIME_GEMM)
-            r = auto_regime(m, n, k, group_size, weight_bits);
+            r = auto_regime(m, n, k, group_size, weight_bits, act_dtype);
         if (r == W4_REGIME_GEMV)
             return 0;
         return w4::gemm_tc_workspace_bytes(m, n, k, has_act_scale, weight_bits);

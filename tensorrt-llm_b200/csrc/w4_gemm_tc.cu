@@ -868,11 +868,12 @@ static int dispatch(W4GemmParams const& p, void const* act, DeviceInfo const& de
 // int4: up to 192 rows the step is bound by the conversion / hand-off pipeline, not by its tensor
 // work; 256 rows leave shared memory for three stages only and the step turns latency-bound. int8
 // stages carry 16 KB of weights instead of 8: four of them fit up to 128 rows, three at 192 rows
-// (4096 x 14336 x 4096: 546 us with 128-row tiles against 623 us with 192), two at 256.
+// (4096 x 14336 x 4096: 546 us with 128-row tiles against 623 us with 192), two at 256; with 64-row
+// tiles the int8 step is shorter (4096 x 14336 at 32 and 64 rows: 25 us for 32 steps).
 static double step_us(int bm, int bits)
 {
     if (bits == 8)
-        return bm <= 128 ? 0.70 : (bm == 192 ? 1.11 : 1.9);
+        return bm <= 64 ? 0.56 : (bm <= 128 ? 0.70 : (bm == 192 ? 1.11 : 1.9));
     return bm <= 128 ? 0.57 : (bm == 192 ? 0.70 : 1.05);
 }
 

@@ -43,8 +43,9 @@ def _require_cuda(t: torch.Tensor, name: str):
         raise RuntimeError(f"{name} must be contiguous")
 
 
-def select_regime(m: int, n: int, k: int, group_size: int, weight_bits: int) -> int:
-    return _lib.lib().w4_gemm_select_regime(m, n, k, group_size, weight_bits)
+def select_regime(m: int, n: int, k: int, group_size: int, weight_bits: int, dtype: torch.dtype = torch.float16) -> int:
+    """The kernel an automatic launch takes for this problem (activation type included)."""
+    return _lib.lib().w4_gemm_select_regime_typed(m, n, k, group_size, weight_bits, _DTYPES[dtype])
 
 
 def workspace_bytes(m: int, n: int, k: int, group_size: int, weight_bits: int, dtype: torch.dtype,

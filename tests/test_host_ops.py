@@ -164,6 +164,25 @@ def test_regime_heuristic(lib):
         assert lib.w4_gemm_select_regime(m, 4096, 14336, 128, 4) == pkg.W4_REGIME_GEMM
 
 
+def test_regime_heuristic_knows_the_activation_type(lib):
+    """int8 weights with bf16 activations: a decode pass costs more (two nibble planes), so two
+    16-row passes over a small matrix lose to the tensor-core kernel where float16 still takes them
+    (measured 12.5 against 9.7 us); int4 does not depend on the type; the untyped function answers
+    for float16; workspace sizes follow the typed answer."""
+    FP16, BF16 = pkg._lib.W4_DTYPE_FP16, pkg._lib.W4_DTYPE_BF16
+    typed = lib.w4_gemm_select_regime_typed
+    assert typed(32, 1024, 4096, 0, 8, FP16) == pkg.W4_REGIME_GEMV
+    assert typed(32, 1024, 4096, 0, 8, BF16) == pkg.W4_REGIME_GEMM
+    assert pkg.ops.select_regime(32, 1024, 4096, 0, 8, torch.bfloat16) == pkg.W4_REGIME_GEMM
+    for m in (1, 8, 16, 24, 32, 64, 300):
+        for n, k in ((1024, 4096), (4096, 4096), (14336, 4096)):
+            assert typed(m, n, k, 128, 4, FP16) == typed(m, n, k, 128, 4, BF16)
+            assert typed(m, n, k, 0, 8, FP16) == lib.w4_gemm_select_regime(m, n, k, 0, 8)
+            for dt in (FP16, BF16):
+                auto = lib.w4_gemm_workspace_bytes(m, n, k, 0, 8, dt, 1, pkg.W4_REGIME_AUTO)
+                assert auto == lib.w4_gemm_workspace_bytes(m, n, k, 0, 8, dt, 1, typed(m, n, k, 0, 8, dt))
+
+
 def test_plugin_mirror_fields_and_serialisation():
     g = pkg.WeightOnlyGroupwiseQuantMatmulPlugin(pkg.ops.TRT_BF16, pkg.ZERO | pkg.PRE_QUANT_SCALE | pkg.BIAS, 128, 1.0)
     assert (g.pre_quant_scale_idx, g.weight_idx, g.scales_idx, g.zeros_idx, g.bias_idx, g.nb_inputs) == (1, 2, 3, 4, 5, 6)
