@@ -6,10 +6,10 @@
 //
 // HBM-bound byte work. One CTA turns a tile of 64 k rows x 256 input bytes (512 int4 or 256 int8
 // columns) into 128 output lines of 128 bytes: the rows are read with coalesced 16-byte loads into
-// shared memory, every thread then builds output registers from the closed form of the four
-// reference passes (row permutation inside 16/32-row blocks, sub-byte transpose, column
-// interleave in 64-k tiles, bias + in-register shuffle) and a warp writes one whole output line
-// per store instruction.
+// shared memory; a thread then reads the 8 (int4) / 4 (int8) rows behind one output register as
+// 32-bit words, transposes the block of elements in registers and owns that register of 8 / 4
+// adjacent columns - the closed form of the four reference passes (row permutation inside 16/32-row
+// blocks, sub-byte transpose, column interleave in 64-k tiles, bias + in-register shuffle).
 #include <algorithm>
 
 #include "w4_common.cuh"
@@ -25,12 +25,67 @@ constexpr int kTileBytes = 256;   // input bytes per row per tile
 constexpr int kThreads = 256;
 constexpr int kSmemPitch = kTileBytes + 16; // padded row pitch of the staged tile
 
-__constant__ uint8_t c_perm8[16] = {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15};
-__constant__ uint8_t c_perm4[32] = {0, 1, 8, 9, 16, 17, 24, 25, 2, 3, 10, 11, 18, 19, 26, 27, 4, 5, 12, 13, 20, 21,
-    28, 29, 6, 7, 14, 15, 22, 23, 30, 31};
+// The reference's row permutations inside blocks of 16 (int8) / 32 (int4) rows,
+//   {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15} and
+//   {0, 1, 8, 9, 16, 17, 24, 25, 2, 3, 10, 11, 18, 19, 26, 27, 4, 5, ..., 22, 23, 30, 31},
+// are used in closed form: perm[a * E + s] = 2 * a + 8 * (s / 2) + s % 2 for a = 0..3, s = 0..E-1
+// (E = 4 / 8 elements per 32-bit register).
+
+// Transposes in registers: w[d] holds element c of row d at position c; afterwards w[c] holds
+// element d of column c at position d. int4: 8 x 8 nibbles (16-bit halves, bytes, then nibbles are
+// exchanged between register pairs), int8: 4 x 4 bytes.
+__device__ __forceinline__ void transpose_nibbles(uint32_t (&w)[8])
+{
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+    {
+        uint32_t const a = w[d], b = w[d + 4];
+        w[d] = __byte_perm(a, b, 0x5410);
+        w[d + 4] = __byte_perm(a, b, 0x7632);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+        int const d = (i & 1) + 4 * (i >> 1); // 0, 1, 4, 5
+        uint32_t const a = w[d], b = w[d + 2];
+        w[d] = __byte_perm(a, b, 0x6240);
+        w[d + 2] = __byte_perm(a, b, 0x7351);
+    }
+#pragma unroll
+    for (int d = 0; d < 8; d += 2)
+    {
+        uint32_t const a = w[d], b = w[d + 1];
+        w[d] = (a & 0x0F0F0F0Fu) | ((b & 0x0F0F0F0Fu) << 4);
+        w[d + 1] = ((a >> 4) & 0x0F0F0F0Fu) | (b & 0xF0F0F0F0u);
+    }
+}
+
+__device__ __forceinline__ void transpose_bytes(uint32_t (&w)[4])
+{
+#pragma unroll
+    for (int d = 0; d < 2; ++d)
+    {
+        uint32_t const a = w[d], b = w[d + 2];
+        w[d] = __byte_perm(a, b, 0x5410);
+        w[d + 2] = __byte_perm(a, b, 0x7632);
+    }
+#pragma unroll
+    for (int d = 0; d < 4; d += 2)
+    {
+        uint32_t const a = w[d], b = w[d + 1];
+        w[d] = __byte_perm(a, b, 0x6240);
+        w[d + 1] = __byte_perm(a, b, 0x7351);
+    }
+}
 
 // Output stage shared by both kernels: `tile` holds 64 rows of two's-complement weights (int4: two
 // per byte, even column in the low nibble) for `cols` columns starting at column n0.
+// A 32-bit word of the staged tile holds E = 8 (int4) / 4 (int8) adjacent columns of one row, an
+// output register E rows of one column. A thread therefore takes the E rows behind register vr -
+// in the register's element order - of one word position, transposes the E x E block in registers
+// and owns E finished output registers (register vr of E adjacent columns); the bias (+8 / +128
+// on two's complement) is one XOR per register. Lanes run over vr first, so a store instruction
+// writes runs of VT consecutive registers.
 template <int BITS>
 __device__ __forceinline__ void emit_tile(uint32_t* out, uint8_t const* tile, int k_tile, int n0, int cols, int K)
 {
@@ -38,32 +93,34 @@ __device__ __forceinline__ void emit_tile(uint32_t* out, uint8_t const* tile, in
     constexpr int VT = 64 / E;             // registers per 64-k tile of one column
     constexpr int IL = BITS == 8 ? 2 : 4;  // interleaved columns
     constexpr int GP = BITS == 8 ? 16 : 32;
-    int const irows = cols / IL;
+    constexpr uint32_t kBias = BITS == 8 ? 0x80808080u : 0x88888888u;
     size_t const regs_per_irow = size_t(K / E) * IL;
-    for (int r = threadIdx.x; r < irows * 32; r += kThreads)
+    int const words = cols / E; // staged words per row (cols is a multiple of 32)
+    for (int item = threadIdx.x; item < words * VT; item += kThreads)
     {
-        int const line = r >> 5, within = r & 31; // one 128-byte line = 32 registers = VT * IL
-        int const nl = line * IL + within / VT;   // column inside the tile
-        int const vr = within % VT;               // register of that column inside the k tile
-        uint32_t word = 0;
+        int const vr = item % VT, wq = item / VT;
+        uint32_t w[E];
 #pragma unroll
         for (int d = 0; d < E; ++d)
         {
+            // position d of the register holds source element s of the permuted column; the row of the
+            // tile behind position kp = vr * E + s of it: both of the reference's permutations (blocks
+            // of 16 / 32 rows) satisfy perm[(vr % 4) * E + s] = 2 * (vr % 4) + 8 * (s / 2) + s % 2
             int const s = BITS == 4 ? (d < 4 ? 2 * d : 2 * (d - 4) + 1) : (d == 1 ? 2 : (d == 2 ? 1 : d));
-            int const kp = vr * E + s;
-            int const kl = (kp / GP) * GP + (BITS == 8 ? c_perm8[kp % GP] : c_perm4[kp % GP]);
-            uint32_t u;
-            if (BITS == 8)
-                u = uint8_t(int(int8_t(tile[kl * kSmemPitch + nl])) + 128);
-            else
-            {
-                uint8_t const b = tile[kl * kSmemPitch + (nl >> 1)];
-                u = (((nl & 1) ? (b >> 4) : b) + 8u) & 0xFu; // sign-extended nibble + 8 == (nibble + 8) mod 16
-            }
-            word |= u << (BITS * d);
+            int const kl = GP * (vr >> 2) + 2 * (vr & 3) + 8 * (s >> 1) + (s & 1);
+            w[d] = *reinterpret_cast<uint32_t const*>(tile + kl * kSmemPitch + wq * 4);
         }
-        size_t const irow = size_t(n0 / IL + line);
-        out[irow * regs_per_irow + size_t(k_tile) * 32 + within] = word;
+        if constexpr (BITS == 4)
+            transpose_nibbles(w);
+        else
+            transpose_bytes(w);
+#pragma unroll
+        for (int c = 0; c < E; ++c)
+        {
+            int const nl = wq * E + c; // column inside the tile
+            size_t const irow = size_t(n0 / IL + nl / IL);
+            out[irow * regs_per_irow + size_t(k_tile) * 32 + (nl % IL) * VT + vr] = w[c] ^ kBias;
+        }
     }
 }
 
@@ -112,7 +169,7 @@ __global__ void __launch_bounds__(kThreads) relayout_w4a8_kernel(uint32_t* out, 
         {
             int const s = d < 4 ? 2 * d : 2 * (d - 4) + 1;
             int const kp = vr * 8 + s;
-            int const k = (kp & ~31) + c_perm4[kp & 31];
+            int const k = (kp & ~31) + 2 * (vr & 3) + 8 * (s >> 1) + (s & 1); // the int4 row permutation, closed form
             // position of row k in the W4A8 order: the inverse of its 32-row permutation in closed form
             int const k8 = (k & ~31) + ((k >> 2) & 3) * 8 + ((k >> 4) & 1) * 4 + (k & 3);
             int const e = k8 & 7;
