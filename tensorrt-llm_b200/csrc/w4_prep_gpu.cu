@@ -226,28 +226,63 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(__nv_bfloat16 const* p, flo
         Pair<__nv_bfloat16>::unpack2(w[i], x[2 * i], x[2 * i + 1]);
 }
 
-// Per-column max |w| over a slab of rows, eight columns per thread (16-byte loads); non-negative
-// floats order like their bit patterns, so the slabs are merged with an integer atomic max (the
-// result does not depend on the order).
+// Per-column max |w| over a slab of rows. A CTA is 64 column vectors (eight columns, one 16-byte load
+// each) x 4 row lanes: the lanes walk the slab four rows apart, four loads in flight per thread (with
+// one the pass is bound by the memory latency), and are merged through shared memory, so a slab
+// costs one atomic per column. Non-negative floats order like their bit patterns: the slabs are
+// merged with an integer atomic max, and the result does not depend on the order.
+constexpr int kAmaxVecs = 64, kAmaxLanes = 4, kAmaxRows = 128; // columns / 8, row lanes, rows per CTA
+
 template <typename W>
-__global__ void __launch_bounds__(256) column_amax_kernel(float* amax, W const* w, int K, int N, int rows_per_block)
+__global__ void __launch_bounds__(kAmaxVecs* kAmaxLanes) column_amax_kernel(float* amax, W const* w, int K, int N)
 {
-    int const c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-    if (c0 >= N) // n is a multiple of 32: a thread's eight columns are all inside or all outside
-        return;
-    int const r0 = blockIdx.y * rows_per_block, r1 = min(K, r0 + rows_per_block);
+    __shared__ float part[kAmaxLanes][kAmaxVecs * 8];
+    int const cv = threadIdx.x % kAmaxVecs, lane = threadIdx.x / kAmaxVecs;
+    int const c0 = (blockIdx.x * kAmaxVecs + cv) * 8;
+    bool const inside = c0 < N; // n is a multiple of 32: a thread's eight columns are all inside or all outside
+    int const r0 = blockIdx.y * kAmaxRows, r1 = min(K, r0 + kAmaxRows);
     float m[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = r0; r < r1; ++r)
+    if (inside)
     {
-        float x[8];
-        load8<W>(w + size_t(r) * N + c0, x);
+        int r = r0 + lane;
+        for (; r + 3 * kAmaxLanes < r1; r += 4 * kAmaxLanes)
+        {
+            float x[4][8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-            m[e] = fmaxf(m[e], fabsf(x[e]));
+            for (int j = 0; j < 4; ++j)
+                load8<W>(w + size_t(r + j * kAmaxLanes) * N + c0, x[j]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    m[e] = fmaxf(m[e], fabsf(x[j][e]));
+        }
+        for (; r < r1; r += kAmaxLanes)
+        {
+            float x[8];
+            load8<W>(w + size_t(r) * N + c0, x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                m[e] = fmaxf(m[e], fabsf(x[e]));
+        }
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e)
-        atomicMax(reinterpret_cast<int*>(amax) + c0 + e, __float_as_int(m[e]));
+        part[lane][cv * 8 + e] = m[e];
+    __syncthreads();
+    // one column per thread and step
+    for (int c = threadIdx.x; c < kAmaxVecs * 8; c += kAmaxVecs * kAmaxLanes)
+    {
+        int const col = blockIdx.x * kAmaxVecs * 8 + c;
+        if (col < N)
+        {
+            float v = part[0][c];
+#pragma unroll
+            for (int l = 1; l < kAmaxLanes; ++l)
+                v = fmaxf(v, part[l][c]);
+            atomicMax(reinterpret_cast<int*>(amax) + col, __float_as_int(v));
+        }
+    }
 }
 
 // Quantises a tile (q = clamp(int(round(w / scale))), round half away from zero, zero column -> 0),
@@ -266,42 +301,66 @@ __global__ void __launch_bounds__(kThreads)
     int const cols = min(kCols, N - n0); // a multiple of 32
     int const k_tile = blockIdx.y;
     int const lo = BITS == 8 ? -128 : -8, hi = BITS == 8 ? 127 : 7;
-    for (int i = threadIdx.x; i < kTileK * kVecPerRow; i += kThreads)
+    // A thread keeps its eight columns for the whole tile (kThreads is a multiple of kVecPerRow): the
+    // scales are loaded once, the rows come two at a time so that both loads are in flight together.
+    static_assert(kThreads % kVecPerRow == 0 && kTileK % (2 * (kThreads / kVecPerRow)) == 0, "row walk");
+    constexpr int kRowStep = kThreads / kVecPerRow;
+    int const c0 = (threadIdx.x % kVecPerRow) * 8;
+    if (c0 < cols)
     {
-        int const r = i / kVecPerRow, c0 = (i % kVecPerRow) * 8;
-        if (c0 >= cols)
-            continue;
-        size_t const row = size_t(k_tile) * kTileK + r;
-        float x[8];
-        load8<W>(w + row * N + n0 + c0, x);
         float4 const sa = __ldg(reinterpret_cast<float4 const*>(scales + n0 + c0));
         float4 const sb = __ldg(reinterpret_cast<float4 const*>(scales + n0 + c0) + 1);
         float const s[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
-        uint32_t qv[8];
+        float inv[8]; // 1 / scale, 0 for a zero column (every q is 0 there)
 #pragma unroll
         for (int e = 0; e < 8; ++e)
+            inv[e] = s[e] != 0.f ? __fdiv_rn(1.f, s[e]) : 0.f;
+        for (int rb = threadIdx.x / kVecPerRow; rb < kTileK; rb += 2 * kRowStep)
         {
-            float const v = s[e] != 0.f ? roundf(__fdiv_rn(x[e], s[e])) : 0.f;
-            qv[e] = uint32_t(max(lo, min(hi, int(v))));
-        }
-        if (BITS == 4)
-        {
-            uint32_t word = 0;
+            float x[2][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-                word |= (qv[e] & 0xFu) << (4 * e); // even column in the low nibble
-            *reinterpret_cast<uint32_t*>(tile + r * kSmemPitch + c0 / 2) = word;
-            if (unprocessed)
-                *reinterpret_cast<uint32_t*>(unprocessed + row * row_bytes + (n0 + c0) / 2) = word;
-        }
-        else
-        {
-            uint2 word;
-            word.x = (qv[0] & 0xFFu) | ((qv[1] & 0xFFu) << 8) | ((qv[2] & 0xFFu) << 16) | (qv[3] << 24);
-            word.y = (qv[4] & 0xFFu) | ((qv[5] & 0xFFu) << 8) | ((qv[6] & 0xFFu) << 16) | (qv[7] << 24);
-            *reinterpret_cast<uint2*>(tile + r * kSmemPitch + c0) = word;
-            if (unprocessed)
-                *reinterpret_cast<uint2*>(unprocessed + row * row_bytes + n0 + c0) = word;
+            for (int j = 0; j < 2; ++j)
+                load8<W>(w + (size_t(k_tile) * kTileK + rb + j * kRowStep) * N + n0 + c0, x[j]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+            {
+                int const r = rb + j * kRowStep;
+                size_t const row = size_t(k_tile) * kTileK + r;
+                uint32_t qv[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                {
+                    // q = round-half-away(w / s) with an IEEE division, as the reference computes it. The
+                    // product with the reciprocal is within 3 * 2^-24 * |w / s| <= 2.3e-5 of that
+                    // quotient, so wherever it is not within 1e-4 of a rounding boundary both round to
+                    // the same integer (and round-to-nearest-even equals round-half-away off the
+                    // boundary); the rare value near a boundary takes the division.
+                    float const r = x[j][e] * inv[e];
+                    int q = __float2int_rn(r);
+                    if (fabsf(r - float(q)) > 0.4999f)
+                        q = s[e] != 0.f ? int(roundf(__fdiv_rn(x[j][e], s[e]))) : 0;
+                    qv[e] = uint32_t(max(lo, min(hi, q)));
+                }
+                if (BITS == 4)
+                {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        word |= (qv[e] & 0xFu) << (4 * e); // even column in the low nibble
+                    *reinterpret_cast<uint32_t*>(tile + r * kSmemPitch + c0 / 2) = word;
+                    if (unprocessed)
+                        *reinterpret_cast<uint32_t*>(unprocessed + row * row_bytes + (n0 + c0) / 2) = word;
+                }
+                else
+                {
+                    uint2 word;
+                    word.x = (qv[0] & 0xFFu) | ((qv[1] & 0xFFu) << 8) | ((qv[2] & 0xFFu) << 16) | (qv[3] << 24);
+                    word.y = (qv[4] & 0xFFu) | ((qv[5] & 0xFFu) << 8) | ((qv[6] & 0xFFu) << 16) | (qv[7] << 24);
+                    *reinterpret_cast<uint2*>(tile + r * kSmemPitch + c0) = word;
+                    if (unprocessed)
+                        *reinterpret_cast<uint2*>(unprocessed + row * row_bytes + n0 + c0) = word;
+                }
+            }
         }
     }
     __syncthreads();
@@ -320,9 +379,8 @@ int quantize_typed(void* processed, void* unprocessed, float* scales, void* scal
 {
     if (cudaMemsetAsync(scales, 0, size_t(n) * sizeof(float), stream) != cudaSuccess)
         return W4_ERR_CUDA;
-    int const rows_per_block = 64;
-    dim3 const ga((n + 2047) / 2048, (k + rows_per_block - 1) / rows_per_block);
-    column_amax_kernel<W><<<ga, 256, 0, stream>>>(scales, w, k, n, rows_per_block);
+    dim3 const ga((n + kAmaxVecs * 8 - 1) / (kAmaxVecs * 8), (k + kAmaxRows - 1) / kAmaxRows);
+    column_amax_kernel<W><<<ga, kAmaxVecs * kAmaxLanes, 0, stream>>>(scales, w, k, n);
     finish_scales_kernel<<<(n + 255) / 256, 256, 0, stream>>>(scales, scales_t, scales_dtype, n,
         1.f / float(1 << (bits - 1)));
     int const cols_per_tile = kTileBytes * 8 / bits;
