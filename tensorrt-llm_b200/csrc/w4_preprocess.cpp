@@ -3,12 +3,14 @@
 // (cpp/tensorrt_llm/kernels/cutlass_kernels/cutlass_preprocessors.cpp:564-615, 652-762 of the
 // TensorRT-LLM tree); the bytes produced here are identical to its output on compute capability
 // 10.x. Instead of the reference's four passes over the matrix (row permute, sub-byte transpose,
-// column interleave, bias + register shuffle) the transform is evaluated in closed form, one output
-// 32-bit register at a time, and the registers are independent so the loop is split over threads.
+// column interleave, bias + register shuffle) the transform is evaluated in closed form: the rows
+// behind an output register are read as 32-bit words and an 8 x 8 nibble (4 x 4 byte) block is
+// transposed in registers; blocks are independent, so the loop is split over threads.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -20,6 +22,22 @@ namespace
 constexpr int kPerm8[16] = {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15};
 constexpr int kPerm4[32] = {0, 1, 8, 9, 16, 17, 24, 25, 2, 3, 10, 11, 18, 19, 26, 27, 4, 5, 12, 13, 20, 21, 28, 29, 6,
     7, 14, 15, 22, 23, 30, 31};
+
+// The closed form of both row permutations that the transforms below use.
+constexpr bool closed_form_matches_tables()
+{
+    for (int a = 0; a < 4; ++a)
+    {
+        for (int s = 0; s < 8; ++s)
+            if (kPerm4[a * 8 + s] != 2 * a + 8 * (s / 2) + s % 2)
+                return false;
+        for (int s = 0; s < 4; ++s)
+            if (kPerm8[a * 4 + s] != 2 * a + 8 * (s / 2) + s % 2)
+                return false;
+    }
+    return true;
+}
+static_assert(closed_form_matches_tables(), "perm[a * E + s] == 2 * a + 8 * (s / 2) + s % 2");
 
 bool shape_ok(size_t k, size_t n, int bits)
 {
@@ -52,47 +70,104 @@ void parallel_for(size_t count, size_t min_chunk, F&& body)
         t.join();
 }
 
-// in: [k, n*bits/8] two's-complement, row-major. out: same byte count, kernel layout.
+// w[d] holds element c of row d at position c; afterwards w[c] holds element d of column c at
+// position d. 8 x 8 nibbles (16-bit halves, bytes, then nibbles exchanged between register pairs) or
+// 4 x 4 bytes.
+inline void transpose_nibbles(uint32_t (&w)[8])
+{
+    for (int d = 0; d < 4; ++d)
+    {
+        uint32_t const a = w[d], b = w[d + 4];
+        w[d] = (a & 0x0000FFFFu) | (b << 16);
+        w[d + 4] = (a >> 16) | (b & 0xFFFF0000u);
+    }
+    for (int i = 0; i < 4; ++i)
+    {
+        int const d = (i & 1) + 4 * (i >> 1); // 0, 1, 4, 5
+        uint32_t const a = w[d], b = w[d + 2];
+        w[d] = (a & 0x00FF00FFu) | ((b & 0x00FF00FFu) << 8);
+        w[d + 2] = ((a >> 8) & 0x00FF00FFu) | (b & 0xFF00FF00u);
+    }
+    for (int d = 0; d < 8; d += 2)
+    {
+        uint32_t const a = w[d], b = w[d + 1];
+        w[d] = (a & 0x0F0F0F0Fu) | ((b & 0x0F0F0F0Fu) << 4);
+        w[d + 1] = ((a >> 4) & 0x0F0F0F0Fu) | (b & 0xF0F0F0F0u);
+    }
+}
+
+inline void transpose_bytes(uint32_t (&w)[4])
+{
+    for (int d = 0; d < 2; ++d)
+    {
+        uint32_t const a = w[d], b = w[d + 2];
+        w[d] = (a & 0x0000FFFFu) | (b << 16);
+        w[d + 2] = (a >> 16) | (b & 0xFFFF0000u);
+    }
+    for (int d = 0; d < 4; d += 2)
+    {
+        uint32_t const a = w[d], b = w[d + 1];
+        w[d] = (a & 0x00FF00FFu) | ((b & 0x00FF00FFu) << 8);
+        w[d + 1] = ((a >> 8) & 0x00FF00FFu) | (b & 0xFF00FF00u);
+    }
+}
+
+// One 64-row k tile x one 32-bit word column (E = 8 / 4 adjacent matrix columns): for every register
+// index vr of the tile, the E rows behind it - in the register's element order - are read as words,
+// the E x E block of elements is transposed and register vr of each of the E columns is written; the
+// bias (+8 / +128 on two's complement) is one XOR. Row of the tile behind element s of register vr:
+// both of the reference's row permutations (blocks of 16 / 32 rows, kPerm8 / kPerm4) satisfy
+// perm[(vr % 4) * E + s] = 2 * (vr % 4) + 8 * (s / 2) + s % 2.
+template <int BITS>
+void transform_words(uint32_t* dst, uint8_t const* in, size_t K, size_t N, size_t k_tile, size_t wq_lo, size_t wq_hi)
+{
+    constexpr int E = 32 / BITS, VT = 64 / E, IL = BITS == 8 ? 2 : 4, GP = BITS == 8 ? 16 : 32;
+    constexpr uint32_t kBias = BITS == 8 ? 0x80808080u : 0x88888888u;
+    size_t const in_row_bytes = N * BITS / 8;
+    size_t const regs_per_irow = (K / E) * IL;
+    uint8_t const* tile = in + k_tile * 64 * in_row_bytes;
+    for (size_t wq = wq_lo; wq < wq_hi; ++wq)
+        for (int vr = 0; vr < VT; ++vr)
+        {
+            uint32_t w[E];
+            for (int d = 0; d < E; ++d)
+            {
+                int const s = BITS == 4 ? (d < 4 ? 2 * d : 2 * (d - 4) + 1) : (d == 1 ? 2 : (d == 2 ? 1 : d));
+                int const kl = GP * (vr >> 2) + 2 * (vr & 3) + 8 * (s >> 1) + (s & 1);
+                std::memcpy(&w[d], tile + size_t(kl) * in_row_bytes + wq * 4, 4);
+            }
+            if constexpr (BITS == 4)
+                transpose_nibbles(w);
+            else
+                transpose_bytes(w);
+            for (int c = 0; c < E; ++c)
+            {
+                size_t const n = wq * E + size_t(c);
+                dst[(n / IL) * regs_per_irow + k_tile * 32 + (n % IL) * VT + size_t(vr)] = w[c] ^ kBias;
+            }
+        }
+}
+
+// in: [k, n*bits/8] two's-complement, row-major. out: same byte count, kernel layout. Work items are
+// (k tile, block of 16 words = one cache line per row), split over threads; every output register is
+// written exactly once.
 void transform(uint8_t* out, uint8_t const* in, size_t K, size_t N, int bits)
 {
-    size_t const E = 32 / bits;            // elements per 32-bit register
-    size_t const VT = 64 / E;              // registers per 64-wide k tile of one column
-    size_t const IL = bits == 8 ? 2 : 4;   // columns interleaved
-    size_t const Gp = bits == 8 ? 16 : 32; // rows per permutation block
-    int const* perm = bits == 8 ? kPerm8 : kPerm4;
-    size_t const regs_per_irow = (K / E) * IL;
-    size_t const num_regs = K * N / E;
-    size_t const in_row_bytes = N * bits / 8;
+    size_t const words = N * size_t(bits) / 32; // 32-bit words per input row
+    size_t const blocks = (words + 15) / 16;
+    size_t const k_tiles = K / 64;
     uint32_t* dst = reinterpret_cast<uint32_t*>(out);
-
-    parallel_for(num_regs, size_t(1) << 16,
+    parallel_for(k_tiles * blocks, 8,
         [=](size_t lo, size_t hi)
         {
-            for (size_t reg = lo; reg < hi; ++reg)
+            for (size_t item = lo; item < hi; ++item)
             {
-                size_t const irow = reg / regs_per_irow, vwr = reg % regs_per_irow;
-                size_t const tile = vwr / (VT * IL), within = vwr % (VT * IL);
-                size_t const n = irow * IL + within / VT;
-                size_t const vr = tile * VT + within % VT;
-                uint32_t word = 0;
-                for (size_t d = 0; d < E; ++d)
-                {
-                    // position d of the register holds source element s of the permuted column
-                    size_t const s = bits == 4 ? (d < 4 ? 2 * d : 2 * (d - 4) + 1) : (d == 1 ? 2 : (d == 2 ? 1 : d));
-                    size_t const kp = vr * E + s;
-                    size_t const k = (kp / Gp) * Gp + size_t(perm[kp % Gp]);
-                    uint32_t u;
-                    if (bits == 8)
-                        u = uint8_t(int(int8_t(in[k * in_row_bytes + n])) + 128);
-                    else
-                    {
-                        uint8_t const b = in[k * in_row_bytes + n / 2];
-                        int const v = (n & 1) ? (int8_t(b) >> 4) : (int8_t(b << 4) >> 4);
-                        u = uint32_t(v + 8) & 0xFu;
-                    }
-                    word |= u << (bits * d);
-                }
-                dst[reg] = word;
+                size_t const k_tile = item / blocks, b = item % blocks;
+                size_t const wq_lo = b * 16, wq_hi = std::min(words, wq_lo + 16);
+                if (bits == 4)
+                    transform_words<4>(dst, in, K, N, k_tile, wq_lo, wq_hi);
+                else
+                    transform_words<8>(dst, in, K, N, k_tile, wq_lo, wq_hi);
             }
         });
 }
@@ -207,17 +282,49 @@ extern "C" int w4_symmetric_quantize(int8_t* processed, int8_t* unprocessed, flo
         q = tmp.data();
     }
     // per-column amax in fp32, then scale = amax / 2^(bits-1); the unrounded fp32 scale quantises.
+    // (Row slabs in parallel, merged under a lock: a maximum does not depend on the order.)
     std::fill(scales, scales + n, 0.f);
-    for (size_t r = 0; r < k; ++r)
     {
-        float const* w = weight + r * n;
-        for (size_t c = 0; c < n; ++c)
-            scales[c] = std::max(scales[c], std::fabs(w[c]));
+        std::mutex merge;
+        parallel_for(k, 256,
+            [&, n](size_t r_lo, size_t r_hi)
+            {
+                std::vector<float> local(n, 0.f);
+                for (size_t r = r_lo; r < r_hi; ++r)
+                {
+                    float const* w = weight + r * n;
+                    for (size_t c = 0; c < n; ++c)
+                        local[c] = std::max(local[c], std::fabs(w[c]));
+                }
+                std::lock_guard<std::mutex> lock(merge);
+                for (size_t c = 0; c < n; ++c)
+                    scales[c] = std::max(scales[c], local[c]);
+            });
     }
     float const range = 1.f / float(1 << (bits - 1));
     for (size_t c = 0; c < n; ++c)
         scales[c] *= range;
     int const lo = bits == 8 ? -128 : -8, hi = bits == 8 ? 127 : 7;
+    // q = round-half-away(w / s) with an IEEE division, as C round() does in the reference. The product
+    // with the reciprocal is within 3 * 2^-24 * |w / s| <= 2.3e-5 of that quotient, so unless it lies
+    // within 1e-4 of a rounding boundary both round to the same integer (and round-to-nearest-even
+    // equals round-half-away off the boundary); near a boundary, or for anything that is not a
+    // number, the division decides.
+    std::vector<float> inv(n);
+    for (size_t c = 0; c < n; ++c)
+        inv[c] = scales[c] != 0.f ? 1.f / scales[c] : 0.f;
+    float const* inv_s = inv.data();
+    auto quantise = [=](float w, size_t c) -> int
+    {
+        float const r = w * inv_s[c];
+        int iv = int(std::lrintf(r));
+        if (!(std::fabs(r - float(iv)) <= 0.4999f))
+        {
+            float const s = scales[c];
+            iv = int(s != 0.f ? std::round(w / s) : 0.f);
+        }
+        return std::max(lo, std::min(hi, iv));
+    };
     parallel_for(k, 64,
         [=](size_t r_lo, size_t r_hi)
         {
@@ -225,19 +332,12 @@ extern "C" int w4_symmetric_quantize(int8_t* processed, int8_t* unprocessed, flo
             {
                 float const* w = weight + r * n;
                 int8_t* dst = q + r * row_bytes;
-                if (bits == 4)
-                    std::memset(dst, 0, row_bytes);
-                for (size_t c = 0; c < n; ++c)
-                {
-                    float const s = scales[c];
-                    // round half away from zero, as C round() does in the reference
-                    float const v = s != 0.f ? std::round(w[c] / s) : 0.f;
-                    int const iv = std::max(lo, std::min(hi, int(v)));
-                    if (bits == 8)
-                        dst[c] = int8_t(iv);
-                    else
-                        dst[c / 2] = int8_t(uint8_t(dst[c / 2]) | uint8_t((iv & 0xF) << (4 * (c & 1))));
-                }
+                if (bits == 8)
+                    for (size_t c = 0; c < n; ++c)
+                        dst[c] = int8_t(quantise(w[c], c));
+                else
+                    for (size_t c = 0; c < n; c += 2) // n is even: two columns per byte, even column low
+                        dst[c / 2] = int8_t(uint8_t((quantise(w[c], c) & 0xF) | ((quantise(w[c + 1], c + 1) & 0xF) << 4)));
             }
         });
     transform(reinterpret_cast<uint8_t*>(processed), reinterpret_cast<uint8_t const*>(q), k, n, bits);

@@ -87,3 +87,25 @@ def sample_cols(n, count=384, seed=0):
     g = torch.Generator().manual_seed(seed + 1)
     cols.update(int(x) for x in torch.randint(0, n, (count,), generator=g))
     return sorted(cols)
+
+
+def boundary_weights(bits, dtype, amax, k=128, n=64):
+    """[k, n] weights whose quotient w / scale sits on or next to a rounding boundary (m + 0.5): exact
+    ties where the scale is a power of two, values one unit in the last place either side, and the
+    same for scales that are not powers of two. Row 0 pins every column's maximum, hence the scale."""
+    half_range = 1 << (bits - 1)
+    scale = amax / half_range
+    g = torch.Generator().manual_seed(bits + int(amax * 1000))
+    m = torch.randint(-half_range, half_range, (k, n), generator=g).double()
+    sign = torch.where(m < 0, -1.0, 1.0)
+    w = ((m + 0.5 * sign) * scale).to(dtype)                      # quotient ~ m +- 0.5
+    nudge = torch.randint(-1, 2, (k, n), generator=g)             # -1, 0, +1 units in the last place
+    if dtype == torch.float32:
+        w = torch.where(nudge > 0, torch.nextafter(w, torch.full_like(w, 1e9)),
+                        torch.where(nudge < 0, torch.nextafter(w, torch.full_like(w, -1e9)), w))
+    else:
+        w = (w.view(torch.int16) + nudge.to(torch.int16)).view(dtype)
+    w = torch.where(torch.isfinite(w.float()), w.float(), torch.zeros(())).to(dtype)
+    w[0, :] = amax
+    w.clamp_(-amax, amax)
+    return w

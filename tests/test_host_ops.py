@@ -56,6 +56,21 @@ def test_host_ops_match_oracle(bits, K, N):
     assert torch.equal(p2, exp[1]) and torch.equal(s2, exp[2])
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("amax", [1.0, 1.3, 0.0371])
+def test_host_quantize_at_rounding_boundaries(bits, dtype, amax):
+    """The host quantiser multiplies with the reciprocal of the scale and lets the division decide
+    near a rounding boundary: on weights that sit on and next to the boundaries the result is still
+    the reference's round(w / scale), bit for bit (oracle: division and C round())."""
+    from _cases import boundary_weights
+    w = boundary_weights(bits, dtype, amax)
+    got = quantize._symmetric_quantize_last_axis_of_batched_matrix(w, _QT[bits])
+    exp = o.symmetric_quantize(w, bits)
+    for a, b in zip(got, exp):
+        assert torch.equal(a, b)
+
+
 def test_w4a8_layout_and_relayout():
     """preprocess_weights_for_mixed_gemm with an fp8 activation type gives the reference's W4A8 bytes
     (golden vectors made by the reference's code); relayout_w4a8_weights turns them into the layout

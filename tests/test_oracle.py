@@ -109,3 +109,17 @@ def test_floating_point_oracles_agree():
     tight = oracle_out(p)
     loose = o.groupwise_matmul_test_ref(p["act"], p["q"], p["scales"], p["zeros"], p["bias"], p["ps"], 128)
     assert float((tight.float() - loose.float()).abs().max()) <= o.tolerance(tight)
+
+
+@pytest.mark.skipif(o.ref_lib() is None, reason="oracle/_ref not built (reference tree absent)")
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_oracle_matches_reference_live_at_rounding_boundaries(bits, dtype):
+    """The quantiser's rounding (division, round half away from zero) on weights that sit on and next
+    to the boundaries m + 0.5: the oracle against the reference's own compiled code."""
+    from _cases import boundary_weights
+    for amax in (1.0, 1.3, 0.0371):
+        w = boundary_weights(bits, dtype, amax)
+        a, b = o.symmetric_quantize(w, bits), o.ref_symmetric_quantize(w, bits)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+        assert torch.equal(a[2].to(torch.float32), b[2].to(torch.float32))

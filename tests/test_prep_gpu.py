@@ -70,23 +70,8 @@ def test_quantize_at_rounding_boundaries(bits, dtype, amax):
     (power-of-two scale), values one unit in the last place either side, and the same for scales that
     are not powers of two. The kernel multiplies with the reciprocal and falls back to the division
     near a boundary; the result must still be the reference's division, bit for bit."""
-    k, n = 128, 64
-    half_range = 1 << (bits - 1)
-    scale = amax / half_range
-    g = torch.Generator().manual_seed(bits + int(amax * 1000))
-    m = torch.randint(-half_range, half_range, (k, n), generator=g).double()
-    sign = torch.where(m < 0, -1.0, 1.0)
-    w = ((m + 0.5 * sign) * scale).to(dtype)                      # quotient ~ m +- 0.5
-    nudge = torch.randint(-1, 2, (k, n), generator=g)             # -1, 0, +1 units in the last place
-    if dtype == torch.float32:
-        w = torch.where(nudge > 0, torch.nextafter(w, torch.full_like(w, 1e9)),
-                        torch.where(nudge < 0, torch.nextafter(w, torch.full_like(w, -1e9)), w))
-    else:
-        bits16 = w.view(torch.int16) + nudge.to(torch.int16)
-        w = bits16.view(dtype)
-    w = torch.where(torch.isfinite(w.float()), w.float(), torch.zeros(())).to(dtype)
-    w[0, :] = amax  # pins every column's maximum, hence the scale
-    w.clamp_(-amax, amax)
+    from _cases import boundary_weights
+    w = boundary_weights(bits, dtype, amax)
     u_ref, p_ref, s_ref = o.symmetric_quantize(w, bits)
     u, p, s = Q.symmetric_quantize_last_axis_of_batched_matrix_cuda(w.cuda(), _QT[bits], return_unprocessed=True)
     assert torch.equal(s.cpu().float(), s_ref.float())
