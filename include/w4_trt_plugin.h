@@ -16,7 +16,7 @@
  *                                 path (TensorRT is not part of this repository's build environment).
  *
  * Differences from the reference, on purpose: no tactic profiling at engine-build time (the regime
- * choice is a pure function, w4_gemm_select_regime), so the serialised tactic map is always empty
+ * choice is a pure function, w4_gemm_select_regime_typed), so the serialised tactic map is always empty
  * (count = 0) and engines are not byte-compatible with the reference's. W4A8-AWQ (FP8_ALPHA) is taken
  * for float16 plugins only, with int4 weights that the engine's emitter has re-laid
  * (w4_relayout_w4a8_to_w4a16): the scales and zeros of a W4A8 layer are float16 whatever the activation
