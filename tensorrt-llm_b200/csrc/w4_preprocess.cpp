@@ -7,6 +7,7 @@
 // behind an output register are read as 32-bit words and an 8 x 8 nibble (4 x 4 byte) block is
 // transposed in registers; blocks are independent, so the loop is split over threads.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -348,22 +349,33 @@ extern "C" int w4_pack_int4(int8_t* packed, const int8_t* unpacked, size_t num_p
 {
     if (!packed || !unpacked)
         return W4_ERR_NULL_POINTER;
-    for (size_t i = 0; i < num_packed_bytes; ++i)
-    {
-        int const a = unpacked[2 * i], b = unpacked[2 * i + 1];
-        if (a < -8 || a > 7 || b < -8 || b > 7)
-            return W4_ERR_BAD_DTYPE;
-        packed[i] = int8_t(uint8_t((a & 0xF) | ((b & 0xF) << 4)));
-    }
-    return W4_OK;
+    std::atomic<bool> out_of_range{false};
+    parallel_for(num_packed_bytes, size_t(1) << 20,
+        [&](size_t lo, size_t hi)
+        {
+            bool bad = false;
+            for (size_t i = lo; i < hi; ++i)
+            {
+                int const a = unpacked[2 * i], b = unpacked[2 * i + 1];
+                bad |= a < -8 || a > 7 || b < -8 || b > 7;
+                packed[i] = int8_t(uint8_t((a & 0xF) | ((b & 0xF) << 4)));
+            }
+            if (bad)
+                out_of_range.store(true, std::memory_order_relaxed);
+        });
+    return out_of_range.load() ? W4_ERR_BAD_DTYPE : W4_OK; // the packed bytes are unspecified then
 }
 
 extern "C" void w4_unpack_int4(int8_t* unpacked, const int8_t* packed, size_t num_packed_bytes)
 {
-    for (size_t i = 0; i < num_packed_bytes; ++i)
-    {
-        int8_t const b = packed[i];
-        unpacked[2 * i + 0] = int8_t(int8_t(uint8_t(b) << 4) >> 4);
-        unpacked[2 * i + 1] = int8_t(b >> 4);
-    }
+    parallel_for(num_packed_bytes, size_t(1) << 20,
+        [=](size_t lo, size_t hi)
+        {
+            for (size_t i = lo; i < hi; ++i)
+            {
+                int8_t const b = packed[i];
+                unpacked[2 * i + 0] = int8_t(int8_t(uint8_t(b) << 4) >> 4);
+                unpacked[2 * i + 1] = int8_t(b >> 4);
+            }
+        });
 }
